@@ -1,0 +1,208 @@
+// LayerNorm / RMSNorm forward for sm_100a.
+//
+// HBM-bound: one read of x and one write of y per element (plus 4 or 8 bytes
+// of statistics per row). The row lives in registers between the reduction
+// passes, so x is read from memory exactly once.
+#include "rowcfg.cuh"
+
+namespace evg {
+namespace {
+
+// LN = true : y = ((x-mean)*rstd)*w + b, two-pass variance (the rounding points
+//             of layernorm_forward_ref, ops/level1/layernorm/forward_ref.py:20-23)
+// LN = false: y = (x*rstd)*w          (rmsnorm_forward_ref, .../rmsnorm/forward_ref.py:19-21)
+template <typename T, int G, int VPT, bool LN>
+__global__ void __launch_bounds__(rowcfg_max_threads(G))
+norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
+                T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                int64_t rows, int cols, float eps) {
+  constexpr int N = Vec<T>::N;
+  extern __shared__ float smem[];
+  const int gid = threadIdx.x / G;
+  const int lig = threadIdx.x % G;
+  const int groups = blockDim.x / G;
+  const int nvec = cols / N;
+  float* scratch = smem + gid * (2 * (G / 32));
+  int phase = 0;
+
+  uint4 wv[VPT], bv[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int idx = lig + k * G;
+    wv[k] = make_uint4(0, 0, 0, 0);
+    bv[k] = make_uint4(0, 0, 0, 0);
+    if (idx < nvec) {
+      wv[k] = *reinterpret_cast<const uint4*>(w + (size_t)idx * N);
+      if constexpr (LN) bv[k] = *reinterpret_cast<const uint4*>(b + (size_t)idx * N);
+    }
+  }
+  const float inv_cols = 1.0f / (float)cols;
+
+  for (int64_t row = (int64_t)blockIdx.x * groups + gid; row < rows;
+       row += (int64_t)gridDim.x * groups) {
+    const T* xr = x + row * cols;
+    uint4 xv[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = lig + k * G;
+      xv[k] = make_uint4(0, 0, 0, 0);
+      if (idx < nvec) xv[k] = ld_vec(xr + (size_t)idx * N);
+    }
+    float mu = 0.f;
+    if constexpr (LN) {
+      float s[1] = {0.f};
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        float f[N];
+        unpack<T>(xv[k], f);
+#pragma unroll
+        for (int j = 0; j < N; ++j) s[0] += f[j];  // padded vectors are zero
+      }
+      group_allreduce<G, 1, SumOp>(s, scratch, phase, gid, lig);
+      mu = s[0] * inv_cols;
+    }
+    float q[1] = {0.f};
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = lig + k * G;
+      if (idx < nvec) {
+        float f[N];
+        unpack<T>(xv[k], f);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          const float d = f[j] - mu;
+          q[0] += d * d;
+        }
+      }
+    }
+    group_allreduce<G, 1, SumOp>(q, scratch, phase, gid, lig);
+    const float rs = 1.0f / sqrtf(q[0] * inv_cols + eps);
+    if (lig == 0) {
+      rstd_out[row] = rs;
+      if constexpr (LN) mean_out[row] = mu;
+    }
+    T* yr = y + row * cols;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = lig + k * G;
+      if (idx < nvec) {
+        float f[N], wf[N], o[N];
+        unpack<T>(xv[k], f);
+        unpack<T>(wv[k], wf);
+        if constexpr (LN) {
+          float bf[N];
+          unpack<T>(bv[k], bf);
+#pragma unroll
+          for (int j = 0; j < N; ++j)
+            o[j] = __fadd_rn(__fmul_rn(__fmul_rn(f[j] - mu, rs), wf[j]), bf[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < N; ++j) o[j] = __fmul_rn(__fmul_rn(f[j], rs), wf[j]);
+        }
+        st_vec(yr + (size_t)idx * N, pack<T>(o));
+      }
+    }
+  }
+}
+
+// Any width, any alignment: one block per row, three passes (the second and
+// third re-read the row, which the first pass left in L2).
+template <typename T, bool LN>
+__global__ void __launch_bounds__(1024, 1)
+norm_fwd_generic_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                        const T* __restrict__ b, T* __restrict__ y,
+                        float* __restrict__ mean_out, float* __restrict__ rstd_out, int64_t rows,
+                        int64_t cols, float eps) {
+  __shared__ float scratch[2 * 32];
+  int phase = 0;
+  const float inv_cols = 1.0f / (float)cols;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + row * cols;
+    float mu = 0.f;
+    if constexpr (LN) {
+      float s[1] = {0.f};
+      for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s[0] += to_f32<T>(xr[c]);
+      block_allreduce<1, SumOp>(s, scratch, phase);
+      mu = s[0] * inv_cols;
+    }
+    float q[1] = {0.f};
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float d = to_f32<T>(xr[c]) - mu;
+      q[0] += d * d;
+    }
+    block_allreduce<1, SumOp>(q, scratch, phase);
+    const float rs = 1.0f / sqrtf(q[0] * inv_cols + eps);
+    if (threadIdx.x == 0) {
+      rstd_out[row] = rs;
+      if constexpr (LN) mean_out[row] = mu;
+    }
+    T* yr = y + row * cols;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float xf = to_f32<T>(xr[c]);
+      float o = __fmul_rn(__fmul_rn(xf - mu, rs), to_f32<T>(w[c]));
+      if constexpr (LN) o = __fadd_rn(o, to_f32<T>(b[c]));
+      yr[c] = from_f32<T>(o);
+    }
+  }
+}
+
+template <typename T, bool LN>
+int launch_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                    int64_t rows, int64_t hidden, float eps, cudaStream_t stream) {
+  constexpr int N = Vec<T>::N;
+  const char* op = LN ? "layernorm_fwd" : "rmsnorm_fwd";
+  const bool vec_ok = hidden % N == 0 && aligned16(x) && aligned16(y) && aligned16(w) &&
+                      (!LN || aligned16(b)) && hidden < (int64_t)1 << 31;
+  RowCfg cfg;
+  if (vec_ok && !tune("rows.force_generic") && pick_rowcfg(op, hidden / N, cfg)) {
+    const int groups = cfg.threads / cfg.G;
+    const size_t smem = (size_t)groups * 2 * (cfg.G / 32 > 0 ? cfg.G / 32 : 1) * sizeof(float);
+#define EVG_X(g, v)                                                                           \
+  if (cfg.G == g && cfg.VPT == v) {                                                           \
+    auto kern = norm_fwd_kernel<T, g, v, LN>;                                                 \
+    const int grid = persistent_grid(kern, cfg.threads, smem, rows, groups);                  \
+    kern<<<grid, cfg.threads, smem, stream>>>((const T*)x, (const T*)w, (const T*)b, (T*)y,   \
+                                              mean, rstd, rows, (int)hidden, eps);            \
+    return check_launch(op);                                                                  \
+  }
+    EVG_ROWCFG_LIST(EVG_X)
+#undef EVG_X
+  }
+  auto kern = norm_fwd_generic_kernel<T, LN>;
+  const int threads = hidden >= 2048 ? 1024 : (hidden >= 256 ? 256 : 64);
+  const int grid = persistent_grid(kern, threads, 0, rows, 1);
+  kern<<<grid, threads, 0, stream>>>((const T*)x, (const T*)w, (const T*)b, (T*)y, mean, rstd,
+                                     rows, hidden, eps);
+  return check_launch(op);
+}
+
+}  // namespace
+}  // namespace evg
+
+using namespace evg;
+
+extern "C" int evg_layernorm_fwd(const void* x, const void* weight, const void* bias, void* y,
+                                 float* mean, float* rstd, int64_t rows, int64_t hidden, float eps,
+                                 int dtype, void* stream) {
+  if (!x || !weight || !bias || !y || !mean || !rstd)
+    return fail(EVG_ENULL, "layernorm_fwd: null pointer argument");
+  if (rows < 0 || hidden <= 0) return fail(EVG_EBADSHAPE, "layernorm_fwd: rows=%lld hidden=%lld",
+                                           (long long)rows, (long long)hidden);
+  if (rows == 0) return EVG_OK;
+  return EVG_DISPATCH_DTYPE(dtype, [&] {
+    return launch_norm_fwd<T, true>(x, weight, bias, y, mean, rstd, rows, hidden, eps,
+                                    (cudaStream_t)stream);
+  });
+}
+
+extern "C" int evg_rmsnorm_fwd(const void* x, const void* weight, void* y, float* rstd,
+                               int64_t rows, int64_t hidden, float eps, int dtype, void* stream) {
+  if (!x || !weight || !y || !rstd) return fail(EVG_ENULL, "rmsnorm_fwd: null pointer argument");
+  if (rows < 0 || hidden <= 0) return fail(EVG_EBADSHAPE, "rmsnorm_fwd: rows=%lld hidden=%lld",
+                                           (long long)rows, (long long)hidden);
+  if (rows == 0) return EVG_OK;
+  return EVG_DISPATCH_DTYPE(dtype, [&] {
+    return launch_norm_fwd<T, false>(x, weight, nullptr, y, nullptr, rstd, rows, hidden, eps,
+                                     (cudaStream_t)stream);
+  });
+}

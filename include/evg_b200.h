@@ -1,0 +1,218 @@
+/*
+ * evg_b200.h - C ABI of libevg_b200.so: hand-written sm_100a kernels for the
+ * forward/backward ("autograd pair") hot path of evograd's softmax, LayerNorm,
+ * RMSNorm, SwiGLU, RoPE and causal attention operators.
+ *
+ * Conventions shared by every entry point
+ *   - All pointers are DEVICE pointers unless the comment says otherwise.
+ *   - Tensors are dense row-major ("contiguous") unless strides are arguments.
+ *   - `dtype` is one of EVG_F32 / EVG_F16 / EVG_BF16 and names the element type
+ *     of the activations, parameters and gradients; statistics (mean, rstd,
+ *     logsumexp) and partial sums are always float32.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *   - Nothing here allocates, frees or synchronises unless the comment says so.
+ *     Kernels are only enqueued; scratch memory is passed in by the caller.
+ *   - Return value: EVG_OK (0) or a negative EVG_E* code; the text of the last
+ *     failure on the calling thread is available from evg_last_error().
+ *   - Inputs are never written, with the one exception documented at
+ *     evg_swiglu_bwd (outputs may alias inputs there).
+ *
+ * "replaces:" lines cite the reference (akumdam2/evograd) interface, by path
+ * inside that project, whose device work the entry point takes over.
+ */
+#ifndef EVG_B200_H
+#define EVG_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EVG_ABI_VERSION 1
+
+enum evg_dtype { EVG_F32 = 0, EVG_F16 = 1, EVG_BF16 = 2 };
+
+enum evg_status {
+  EVG_OK = 0,
+  EVG_EBADSHAPE = -1,    /* a size is zero/negative or inconsistent          */
+  EVG_EALIGN = -2,       /* a pointer is not aligned as the kernel requires  */
+  EVG_EDTYPE = -3,       /* dtype enum out of range / unsupported for the op */
+  EVG_ELAUNCH = -4,      /* CUDA reported an error when enqueuing            */
+  EVG_ETIMEOUT = -5,     /* a bounded device-side wait gave up               */
+  EVG_ENULL = -6,        /* a required pointer is NULL                       */
+  EVG_EWORKSPACE = -7,   /* scratch buffer missing or too small              */
+  EVG_EUNSUPPORTED = -8  /* shape outside what the kernel family covers      */
+};
+
+/* Library identity and diagnostics. */
+int evg_abi_version(void);
+const char* evg_last_error(void);
+/* Name the compute capability the kernels were built for (returns 100). */
+int evg_built_for_sm(void);
+
+/*
+ * Launch-shape override for experiments: key is "<op>.<knob>" (for example
+ * "rmsnorm_bwd.group", "layernorm_fwd.vpt", "rows.threads"); value 0 restores
+ * the built-in choice. Unknown keys return EVG_EUNSUPPORTED. Results never
+ * depend on these knobs beyond floating-point summation order.
+ */
+int evg_tune_set(const char* key, int value);
+int evg_tune_get(const char* key);
+
+/* ------------------------------------------------------------------ softmax
+ * y = softmax(x, dim=-1) evaluated in float32 and rounded once to dtype.
+ * replaces: softmax_forward_ref, src/evograd/ops/level1/softmax/forward_ref.py:6-7;
+ *           candidate forward for declaration ops/level1/softmax/__init__.py:69-92.
+ * Saved state for the backward is y only.
+ */
+int evg_softmax_fwd(const void* x, void* y, int64_t rows, int64_t cols,
+                    int dtype, void* stream);
+/*
+ * dx = y * (dy - sum(dy * y, dim=-1)), float32 arithmetic, one rounding.
+ * replaces: backward semantics of ops/level1/softmax/__init__.py:78 (the
+ *           gradient torch.autograd.grad returns in opdecl/oracle.py:103).
+ */
+int evg_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows,
+                    int64_t cols, int dtype, void* stream);
+
+/* ---------------------------------------------------------------- layernorm
+ * mean/var over the last dimension in float32 with the two-pass variance
+ * mean((x-mean)^2); y = ((x-mean)*rstd)*weight + bias, rounded once.
+ * Writes mean[rows], rstd[rows] (float32): the only new saved state.
+ * replaces: layernorm_forward_ref, ops/level1/layernorm/forward_ref.py:6-23;
+ *           candidate forward for ops/level1/layernorm/__init__.py:124-171.
+ */
+int evg_layernorm_fwd(const void* x, const void* weight, const void* bias,
+                      void* y, float* mean, float* rstd, int64_t rows,
+                      int64_t hidden, float eps, int dtype, void* stream);
+/* Bytes of scratch evg_layernorm_bwd needs for this shape on the current device. */
+int64_t evg_layernorm_bwd_workspace_bytes(int64_t rows, int64_t hidden, int dtype);
+/*
+ * dx = rstd*(g - mean(g) - xhat*mean(g*xhat)), g = dy*weight;
+ * dweight = sum_rows dy*xhat; dbias = sum_rows dy. The column sums are
+ * two-stage and atomic-free: every thread block writes one float32 partial row
+ * into `workspace`, a second kernel adds the partial rows in a fixed order.
+ * Outputs of the column sums (each may be NULL):
+ *   dweight, dbias : [hidden] in `dtype`
+ *   dwdb_f32       : [2, hidden] float32 (row 0 dweight, row 1 dbias), for callers
+ *                    that all-reduce partial sums across GPUs before rounding.
+ * replaces: the gradients of opdecl/oracle.py:103 for the layernorm declaration
+ *           (backward semantics ops/level1/layernorm/__init__.py:139).
+ */
+int evg_layernorm_bwd(const void* dy, const void* x, const void* weight,
+                      const float* mean, const float* rstd, void* dx,
+                      void* dweight, void* dbias, float* dwdb_f32,
+                      void* workspace, int64_t workspace_bytes, int64_t rows,
+                      int64_t hidden, int dtype, void* stream);
+
+/* ------------------------------------------------------------------ rmsnorm
+ * rstd = 1/sqrt(mean(x^2)+eps) in float32; y = (x*rstd)*weight rounded once.
+ * Writes rstd[rows] float32 (the only new saved state).
+ * replaces: rmsnorm_forward_ref, ops/level1/rmsnorm/forward_ref.py:6-21;
+ *           candidate forward for ops/level1/rmsnorm/__init__.py:72-130.
+ */
+int evg_rmsnorm_fwd(const void* x, const void* weight, void* y, float* rstd,
+                    int64_t rows, int64_t hidden, float eps, int dtype,
+                    void* stream);
+int64_t evg_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t hidden, int dtype);
+/*
+ * dx = (g - xhat*mean(g*xhat))*rstd with xhat = x*rstd, g = dy*weight;
+ * dweight = sum_rows dy*xhat (two-stage, atomic-free, as for layernorm).
+ * dweight ([hidden], dtype) and dweight_f32 ([hidden], float32) may each be NULL.
+ * replaces: backward semantics ops/level1/rmsnorm/__init__.py:86.
+ */
+int evg_rmsnorm_bwd(const void* dy, const void* x, const void* weight,
+                    const float* rstd, void* dx, void* dweight,
+                    float* dweight_f32, void* workspace, int64_t workspace_bytes,
+                    int64_t rows, int64_t hidden, int dtype, void* stream);
+
+/* ------------------------------------------------------------------- swiglu
+ * c = round(silu(float(a))) * b  with the product taken in dtype, exactly the
+ * rounding points of swiglu_forward_ref, ops/level1/swiglu/forward_ref.py:6-9.
+ * `n` is the total element count (rows*cols). No saved state beyond a, b.
+ */
+int evg_swiglu_fwd(const void* a, const void* b, void* c, int64_t n, int dtype,
+                   void* stream);
+/*
+ * s = sigmoid(a): db = dc*silu(a); da = dc*b*(s*(1 + a*(1-s))).
+ * da may alias a and db may alias b (the declaration allows the backward to
+ * overwrite them: ops/level1/swiglu/__init__.py:89-96).
+ */
+int evg_swiglu_bwd(const void* dc, const void* a, const void* b, void* da,
+                   void* db, int64_t n, int dtype, void* stream);
+
+/* --------------------------------------------------------------------- rope
+ * Rotate-half (GPT-NeoX / Llama) rotary embedding of a 4-D tensor whose last
+ * dimension (head_dim, even) is contiguous:
+ *   y[..., :h] = x1*cos1 - x2*sin1 ;  y[..., h:] = x2*cos2 + x1*sin2
+ * with products and the sum in float32 and one rounding. `inverse` != 0 negates
+ * the sine, which is the backward (dx from dy). Strides are in ELEMENTS for the
+ * batch, head and token axes of x and y. The tables are [T, table_cols] with
+ * table_cols == head_dim (both halves stored, cos1/cos2 read separately) or
+ * head_dim/2 (one half stored), of element type `table_dtype`.
+ * replaces: rope_forward_ref, ops/level1/rope/forward_ref.py:28-47 and the
+ *           backward semantics ops/level1/rope/__init__.py:124-130.
+ */
+typedef struct evg_rope_tensor {
+  const void* x;
+  void* y;
+  int64_t heads;
+  int64_t x_stride_b, x_stride_h, x_stride_t;
+  int64_t y_stride_b, y_stride_h, y_stride_t;
+} evg_rope_tensor;
+
+/* Rotates `count` (1 or 2) tensors sharing batch, T, head_dim and the tables
+ * in ONE launch (for example q and k of one layer). */
+int evg_rope(const evg_rope_tensor* tensors /* HOST pointer */, int count,
+             const void* cos_table, const void* sin_table, int64_t batch,
+             int64_t tokens, int64_t head_dim, int64_t table_cols,
+             int table_dtype, int dtype, int inverse, void* stream);
+
+/* --------------------------------------------------------- causal attention
+ * o = softmax(scale * q k^T + causal_mask) v for q,k,v,o of shape [B,H,S,D]
+ * (contiguous, D in {64,128}, dtype EVG_BF16 or EVG_F16), logits and softmax in
+ * float32, probabilities rounded to dtype before the second product (the
+ * rounding point of ops/level1/evoattention/forward_ref.py:44-47). Writes
+ * lse[B,H,S] = log(sum exp(scale*s - max)) + max in float32 (natural log).
+ * Runs on the tcgen05 tensor cores with TMEM accumulators and TMA-staged tiles.
+ * replaces: F.scaled_dot_product_attention(q,k,v,is_causal=True) as called at
+ *           ops/level3/llama3_decoder_layer/forward_ref.py:107 (there is no
+ *           standalone causal-attention declaration in the reference).
+ * Saved state: o and lse (q, k, v are kept by reference).
+ */
+int evg_causal_attention_fwd(const void* q, const void* k, const void* v,
+                             void* o, float* lse, int64_t B, int64_t H,
+                             int64_t S, int64_t D, float scale, int dtype,
+                             void* stream);
+int64_t evg_causal_attention_bwd_workspace_bytes(int64_t B, int64_t H, int64_t S,
+                                                 int64_t D, int dtype);
+/*
+ * delta = rowsum(do*o); P = exp(scale*s - lse); dV = P^T dO; dP = dO V^T;
+ * dS = P*(dP - delta); dQ = scale*dS K; dK = scale*dS^T Q.  Deterministic:
+ * dK/dV are accumulated by the block that owns a key tile and dQ by the block
+ * that owns a query tile, so no atomics and no float32 dq buffer are used.
+ * workspace holds delta[B,H,S] float32.
+ */
+int evg_causal_attention_bwd(const void* dout, const void* q, const void* k,
+                             const void* v, const void* o, const float* lse,
+                             void* dq, void* dk, void* dv, void* workspace,
+                             int64_t workspace_bytes, int64_t B, int64_t H,
+                             int64_t S, int64_t D, float scale, int dtype,
+                             void* stream);
+
+/* ------------------------------------------------------------------ helpers
+ * dst[i] = round_to_dtype(src[i]) for float32 src; used after the cross-GPU
+ * all-reduce of float32 dweight/dbias partial sums.
+ */
+int evg_cast_from_f32(const float* src, void* dst, int64_t n, int dtype,
+                      void* stream);
+/* Writes `bytes` of a repeating pattern; the benchmark driver uses it on a
+ * buffer larger than L2 to evict cached lines between timed iterations. */
+int evg_flush_l2(void* buffer, int64_t bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EVG_B200_H */

@@ -1,0 +1,235 @@
+"""GPU parity of the row-wise autograd pairs (softmax, LayerNorm, RMSNorm,
+SwiGLU, RoPE) against the CPU oracle and the reference-generated golden
+vectors. Every call goes candidate module -> evograd_b200.ops -> C ABI."""
+
+import pytest
+import torch
+
+from _util import assert_checks, assert_unchanged, run_pair, snapshot, to_device
+from conftest import golden_cases, load_golden
+from oracle import autograd_oracle as ao
+
+pytestmark = pytest.mark.gpu
+
+ROW_OPS = ("softmax", "layernorm", "rmsnorm", "swiglu", "rope")
+
+
+def _golden_inputs(meta, tensors):
+    spec = ao.OPS[meta["op"]]
+    inputs = {n: tensors[n] for n in [a for a, _ in spec.args] + [spec.upstream]}
+    inputs.update(meta["scalars"])
+    return inputs
+
+
+@pytest.mark.parametrize("name", [n for op in ROW_OPS for n in golden_cases(op)])
+def test_matches_reference_golden_vectors(name):
+    """Declared tolerances vs the reference's same-dtype outputs; the stricter
+    (1e-5,1e-5) float32 / (1e-2,1.6e-2) 16-bit ones vs its float32-promoted outputs."""
+    meta, tensors = load_golden(name)
+    op, dims, dtype = meta["op"], meta["dims"], meta["dtype"]
+    spec = ao.OPS[op]
+    inputs = to_device(_golden_inputs(meta, tensors))
+    snap = snapshot(inputs)
+    y, grads, _ = run_pair(op, inputs)
+    assert_unchanged(inputs, snap)
+    got = {spec.output: y, **dict(zip(spec.grad_names(), grads))}
+    declared = [ao.check(n, t, tensors[n], *spec.tolerance_for(dims, dtype, n)) for n, t in got.items()]
+    assert_checks(declared, f"{name} declared")
+    strict = [ao.check(n, t, tensors[n + "__f32ref"], *ao.STRICT_TOLERANCES[dtype]) for n, t in got.items()]
+    assert_checks(strict, f"{name} strict")
+
+
+# The reference's own correctness workloads plus ragged / wide extras.
+CASES = {
+    "softmax": [(dict(rows=r, cols=c), dt) for (r, c), dts in (
+        ((8, 512), ("float32",)), ((16, 1024), ("float32",)),
+        ((32, 4096), ("float16", "bfloat16")), ((64, 2048), ("float16", "bfloat16")),
+        ((3, 1), ("float32",)), ((7, 131), ("bfloat16",)), ((4, 33000), ("float32",)),
+        ((2, 128256), ("bfloat16",)), ((5, 8192), ("float32",)), ((1, 16384), ("float32",)),
+    ) for dt in dts],
+    "layernorm": [(dict(rows=r, hidden=h), dt) for (r, h), dts in (
+        ((8, 64), ("float32",)), ((17, 128), ("float32",)), ((32, 256), ("float16", "bfloat16")),
+        ((64, 512), ("float16", "bfloat16")), ((128, 4096), ("bfloat16",)), ((1024, 8192), ("bfloat16",)),
+        ((1, 768), ("bfloat16",)), ((17, 127), ("bfloat16",)), ((17, 513), ("bfloat16",)),
+        ((17, 1000), ("bfloat16", "float32")), ((1, 8192), ("float32",)), ((3, 40000), ("float32",)),
+        ((4096, 1024), ("bfloat16",)),
+    ) for dt in dts],
+    "rmsnorm": [(dict(rows=r, hidden=h), dt) for (r, h), dts in (
+        ((8, 64), ("float32",)), ((17, 128), ("float32",)), ((32, 256), ("float16", "bfloat16")),
+        ((64, 512), ("float16", "bfloat16")), ((128, 4096), ("bfloat16",)), ((1, 4096), ("bfloat16",)),
+        ((17, 4096), ("bfloat16",)), ((4096, 8192), ("bfloat16",)), ((17, 127), ("float32", "float16")),
+        ((17, 513), ("float16",)), ((17, 1000), ("float32",)), ((2, 24576), ("bfloat16",)),
+    ) for dt in dts],
+    "swiglu": [(dict(rows=r, cols=c), dt) for (r, c), dts in (
+        ((8, 64), ("float32",)), ((17, 128), ("float32",)), ((32, 256), ("float16", "bfloat16")),
+        ((64, 512), ("float16", "bfloat16")), ((17, 255), ("bfloat16",)), ((17, 1001), ("float16",)),
+        ((1, 1), ("float32",)), ((512, 14336), ("bfloat16",)),
+    ) for dt in dts],
+    "rope": [(dict(B=b, n_heads=h, T=t, head_dim=d), dt) for (b, h, t, d) in (
+        (1, 4, 16, 64), (2, 8, 128, 128), (1, 32, 129, 128), (1, 3, 5, 6), (1, 2, 7, 256),
+    ) for dt in ("float32", "float16", "bfloat16")],
+}
+
+
+@pytest.mark.parametrize("op,dims,dtype", [(op, d, t) for op in ROW_OPS for d, t in CASES[op]])
+def test_pair_passes_the_declared_gate(op, dims, dtype):
+    inputs = ao.make_inputs(op, dims, dtype, device="cpu")
+    dev_inputs = to_device(inputs)
+    snap = snapshot(dev_inputs)
+    assert_checks(ao.verify_pair(op, __import__("_util").load_pair(op), dev_inputs, dims, dtype),
+                  f"{op} {dims} {dtype}")
+    assert_unchanged(dev_inputs, snap)
+
+
+@pytest.mark.parametrize("op,dims,dtype", [(op, d, t) for op in ROW_OPS for d, t in CASES[op]])
+def test_pair_passes_the_strict_gate_vs_float32_oracle(op, dims, dtype):
+    if op in ("layernorm", "rmsnorm") and dtype != "float32" and dims["rows"] > 1024:
+        pytest.skip("16-bit parameter gradients over thousands of rows: covered at full size "
+                    "with the row-scaled tolerance")
+    inputs = to_device(ao.make_inputs(op, dims, dtype, device="cpu"))
+    checks = ao.verify_pair(op, __import__("_util").load_pair(op), inputs, dims, dtype, strict=True,
+                            reference_dtype=torch.float32)
+    assert_checks(checks, f"{op} {dims} {dtype} strict")
+
+
+@pytest.mark.parametrize("op", ["layernorm", "rmsnorm"])
+def test_parameter_gradients_are_bit_reproducible(op):
+    dims, dtype = dict(rows=3000, hidden=2048), "bfloat16"
+    inputs = to_device(ao.make_inputs(op, dims, dtype))
+    _, g1, _ = run_pair(op, inputs)
+    _, g2, _ = run_pair(op, inputs)
+    for a, b in zip(g1, g2):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("op", ["layernorm", "rmsnorm", "softmax"])
+@pytest.mark.parametrize("knobs", [
+    {"rows.force_generic": 1},
+    {"group": 64, "vpt": 8}, {"group": 256, "vpt": 2}, {"group": 512, "vpt": 1},
+    {"group": 128, "vpt": 4, "threads": 512}, {"group": 32, "vpt": 4, "threads": 128},
+])
+def test_every_launch_shape_gives_the_same_answer(op, knobs):
+    from evograd_b200 import _cabi
+
+    dims = dict(rows=600, hidden=1024) if op != "softmax" else dict(rows=600, cols=1024)
+    dtype = "bfloat16"  # 1024 columns = 128 vectors: every listed shape covers them
+    inputs = to_device(ao.make_inputs(op, dims, dtype))
+    set_keys = []
+    try:
+        for k, v in knobs.items():
+            keys = [k] if "." in k else [f"{op}_fwd.{k}", f"{op}_bwd.{k}"]
+            for key in keys:
+                _cabi.tune_set(key, v)
+                set_keys.append(key)
+        checks = ao.verify_pair(op, __import__("_util").load_pair(op), inputs, dims, dtype)
+    finally:
+        for key in set_keys:
+            _cabi.tune_set(key, 0)
+    assert_checks(checks, f"{op} {knobs}")
+
+
+def test_rope_baseline_layout_q_and_k_in_one_launch():
+    """[B, S, H, D] q (32 heads) and k (8 heads), float32 half-width tables,
+    theta = 10000: equals the reference forward applied to the transposed view."""
+    from evograd_b200 import ops
+
+    torch.manual_seed(4096 * 100003 + 32 * 1009 + 128)
+    B, S, D = 2, 257, 128
+    q = torch.randn(B, S, 32, D, dtype=torch.bfloat16)
+    k = torch.randn(B, S, 8, D, dtype=torch.bfloat16)
+    dq = torch.randn_like(q)
+    dk = torch.randn_like(k)
+    cos, sin = ao.rope_tables(S, D, theta=10000.0, dtype=torch.float32, duplicate=False)
+    cos_full, sin_full = torch.cat((cos, cos), -1), torch.cat((sin, sin), -1)
+    yq, yk = ops.rope_qk_fwd(q.cuda(), k.cuda(), cos.cuda(), sin.cuda(), layout="bthd")
+    gq, gk = ops.rope_qk_bwd(dq.cuda(), dk.cuda(), cos.cuda(), sin.cuda(), layout="bthd")
+    for x, dy, y, g in ((q, dq, yq, gq), (k, dk, yk, gk)):
+        inputs = {"x": x.transpose(1, 2), "cos": cos_full, "sin": sin_full, "dy": dy.transpose(1, 2)}
+        y_ref, g_ref = ao.oracle("rope", inputs)
+        assert torch.equal(y.cpu(), y_ref.transpose(1, 2)), "forward not bit-identical"
+        assert torch.equal(g.cpu(), g_ref["dx"].transpose(1, 2)), "backward not bit-identical"
+
+
+def test_rope_is_bit_exact_and_orthogonal():
+    """Rotation then inverse rotation returns x up to one rounding; the forward is
+    bit-identical to the reference arithmetic (separate float32 products, one add)."""
+    from evograd_b200 import ops
+
+    dims = dict(B=2, n_heads=4, T=300, head_dim=128)
+    inputs = ao.make_inputs("rope", dims, "float32")
+    y_ref, g_ref = ao.oracle("rope", inputs)
+    x, cos, sin, dy = (inputs[k].cuda() for k in ("x", "cos", "sin", "dy"))
+    y = ops.rope_fwd(x, cos, sin)
+    assert torch.equal(y.cpu(), y_ref)
+    assert torch.equal(ops.rope_bwd(dy, cos, sin).cpu(), g_ref["dx"])
+    back = ops.rope_bwd(y, cos, sin)
+    assert torch.allclose(back, x, atol=1e-5, rtol=1e-5)
+
+
+def test_swiglu_in_place_backward_matches():
+    from evograd_b200 import ops
+
+    inputs = to_device(ao.make_inputs("swiglu", dict(rows=33, cols=1000), "bfloat16"))
+    da, db = ops.swiglu_bwd(inputs["dc"], inputs["a"], inputs["b"])
+    a, b = inputs["a"].clone(), inputs["b"].clone()
+    da2, db2 = ops.swiglu_bwd(inputs["dc"], a, b, in_place=True)
+    assert da2.data_ptr() == a.data_ptr() and db2.data_ptr() == b.data_ptr()
+    assert torch.equal(da, da2) and torch.equal(db, db2)
+
+
+def test_swiglu_forward_is_bit_identical_to_reference_rounding():
+    inputs = ao.make_inputs("swiglu", dict(rows=64, cols=512), "bfloat16")
+    from evograd_b200 import ops
+
+    c = ops.swiglu_fwd(inputs["a"].cuda(), inputs["b"].cuda()).cpu()
+    ref = ao.swiglu_forward(inputs["a"], inputs["b"])
+    mismatch = (c != ref).float().mean().item()
+    assert mismatch < 2e-3, f"{mismatch:.2%} of elements differ by an ulp"
+    assert torch.allclose(c.float(), ref.float(), atol=0, rtol=2 ** -7)
+
+
+def test_float32_partials_for_sharded_parameter_gradients():
+    from evograd_b200 import ops
+
+    inputs = to_device(ao.make_inputs("layernorm", dict(rows=512, hidden=768), "bfloat16"))
+    y, mean, rstd = ops.layernorm_fwd(inputs["x"], inputs["weight"], inputs["bias"], 1e-5)
+    dx, dw, db = ops.layernorm_bwd(inputs["dy"], inputs["x"], inputs["weight"], mean, rstd)
+    dx2, dwdb, none = ops.layernorm_bwd(inputs["dy"], inputs["x"], inputs["weight"], mean, rstd,
+                                        partials_f32=True)
+    assert none is None and dwdb.dtype == torch.float32 and tuple(dwdb.shape) == (2, 768)
+    assert torch.equal(dx, dx2)
+    assert torch.equal(ops.cast_from_f32(dwdb[0], torch.bfloat16), dw)
+    assert torch.equal(ops.cast_from_f32(dwdb[1], torch.bfloat16), db)
+
+
+def test_bad_arguments_raise():
+    from evograd_b200 import ops
+    from evograd_b200._cabi import EvgError
+
+    x = torch.zeros(4, 64, device="cuda")
+    with pytest.raises(ValueError):
+        ops.rmsnorm_fwd(x, torch.ones(32, device="cuda"))
+    with pytest.raises(ValueError):
+        ops.rmsnorm_fwd(x, torch.ones(64, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(TypeError):
+        ops.softmax_fwd(torch.zeros(4, 4, device="cuda", dtype=torch.float64))
+    with pytest.raises(ValueError):
+        ops.rope_fwd(torch.zeros(1, 1, 4, 7, device="cuda"), torch.zeros(4, 7, device="cuda"),
+                     torch.zeros(4, 7, device="cuda"))
+    with pytest.raises(EvgError, match="EVG_EWORKSPACE"):
+        from evograd_b200 import _cabi
+        y, rstd = ops.rmsnorm_fwd(x, torch.ones(64, device="cuda"))
+        _cabi.call("evg_rmsnorm_bwd", x.data_ptr(), x.data_ptr(), x.data_ptr(), rstd.data_ptr(),
+                   y.data_ptr(), None, None, None, 0, 4, 64, 0, None)
+
+
+def test_empty_inputs():
+    from evograd_b200 import ops
+
+    x = torch.zeros(0, 64, device="cuda", dtype=torch.bfloat16)
+    assert ops.softmax_fwd(x).shape == (0, 64)
+    y, rstd = ops.rmsnorm_fwd(x, torch.ones(64, device="cuda", dtype=torch.bfloat16))
+    assert y.shape == (0, 64) and rstd.shape == (0,)
+    dx, dw = ops.rmsnorm_bwd(x, x, torch.ones(64, device="cuda", dtype=torch.bfloat16), rstd)
+    assert dx.shape == (0, 64) and torch.count_nonzero(dw) == 0
+    assert ops.swiglu_fwd(x, x).shape == (0, 64)
