@@ -105,6 +105,7 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_void_p],
     ),
+    "evg_device_status": (c_int, [c_int]),
     "evg_cast_from_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "evg_flush_l2": (c_int, [c_void_p, c_int64, c_void_p]),
 }

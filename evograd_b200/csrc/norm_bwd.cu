@@ -261,7 +261,7 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
                       aligned16(w) && hidden < (int64_t)1 << 31;
   RowCfg cfg;
   bool launched = false;
-  if (vec_ok && !tune("rows.force_generic") && pick_rowcfg(op, hidden / N, cfg)) {
+  if (vec_ok && !tune("rows.force_generic") && pick_rowcfg(op, hidden / N, cfg, 512, LN)) {
     const int groups = cfg.threads / cfg.G;
     const size_t smem =
         ((size_t)groups * 2 * NV * (cfg.G / 32) + (size_t)NV * hidden) * sizeof(float);

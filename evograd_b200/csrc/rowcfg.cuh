@@ -37,7 +37,11 @@ inline bool rowcfg_listed(int G, int VPT) {
 
 // Returns false when no register-resident shape fits (use the generic kernel).
 // `op` prefixes the tuning keys ("<op>.group", "<op>.vpt", "<op>.threads").
-inline bool pick_rowcfg(const char* op, int64_t nvec, RowCfg& cfg) {
+// `prefer_threads` is the default block size (0: one group of >= 256 threads);
+// `narrow` prefers (256, 2) over (128, 4) for 512-vector rows, which halves the
+// per-thread accumulator count of kernels that keep two column sums.
+inline bool pick_rowcfg(const char* op, int64_t nvec, RowCfg& cfg, int prefer_threads = 0,
+                        bool narrow = false) {
   if (nvec <= 0 || nvec > 8192) return false;
   char key[96];
   snprintf(key, sizeof(key), "%s.group", op);
@@ -53,13 +57,18 @@ inline bool pick_rowcfg(const char* op, int64_t nvec, RowCfg& cfg) {
   else if (nvec <= 64) { G = 32; V = 2; }
   else if (nvec <= 128) { G = 32; V = 4; }
   else if (nvec <= 256) { G = 64; V = 4; }
+  else if (nvec <= 512 && narrow) { G = 256; V = 2; }
   else if (nvec <= 512) { G = 128; V = 4; }
   else if (nvec <= 1024) { G = 256; V = 4; }
   else if (nvec <= 2048) { G = 512; V = 4; }
   else if (nvec <= 4096) { G = 1024; V = 4; }
   else { G = 1024; V = 8; }
   int threads = G >= 256 ? G : 256;
-  if (ft > 0 && ft % G == 0 && ft <= rowcfg_max_threads(G) && ft / G <= 15) threads = ft;
+  if (prefer_threads > 0 && prefer_threads % G == 0 && prefer_threads <= rowcfg_max_threads(G) &&
+      (G == 32 || prefer_threads / G <= 15))
+    threads = prefer_threads;
+  if (ft > 0 && ft % G == 0 && ft <= rowcfg_max_threads(G) && (G == 32 || ft / G <= 15))
+    threads = ft;
   cfg.G = G; cfg.VPT = V; cfg.threads = threads;
   return true;
 }

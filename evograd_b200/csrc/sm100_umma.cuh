@@ -1,0 +1,218 @@
+// Inline-PTX building blocks for Blackwell (sm_100a) tensor-core kernels:
+// mbarriers with bounded waits, TMA tile loads, tensor-memory (TMEM) allocation
+// and access, tcgen05.mma issue with shared-memory / TMEM operands.
+//
+// Every wait in this file gives up after a cycle budget and records the fact
+// in an abort word, after which all later waits return immediately, so a kernel
+// built from these pieces always runs to its end, frees its TMEM and returns.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace evg {
+namespace umma {
+
+// ------------------------------------------------------------------ host side
+// Encodes a TMA descriptor for a dense [outer, rows, cols] tensor of 16-bit
+// elements (fmt 0 = float16, 1 = bfloat16) whose tiles are [box_rows x 64] with
+// the 128-byte swizzle that the tcgen05 shared-memory descriptors below expect.
+// Returns false on failure.
+bool encode_tile_map_16bit(CUtensorMap* map, const void* base, int fmt, uint64_t cols,
+                           uint64_t rows, uint64_t outer, uint32_t box_rows);
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------- device side
+
+constexpr uint32_t kAtomBytesPerRow = 128;  // one swizzle atom row: 64 x 16-bit
+constexpr uint32_t kAtomGroupBytes = 1024;  // 8 rows of an atom
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// Abort protocol shared by all waits of a block.
+struct WaitCtx {
+  volatile int* abort_flag;   // shared memory word, 0 until a wait times out
+  int* device_status;         // global sticky status word
+  long long limit_cycles;
+};
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Waits for the phase with the given parity to complete, at most
+// ctx.limit_cycles; on timeout sets the abort word (code identifies the wait).
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
+                                          int code) {
+  if (*ctx.abort_flag) return;
+  if (mbar_try_wait(bar, parity)) return;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*ctx.abort_flag) return;
+    if (clock64() - start > ctx.limit_cycles) {
+      *ctx.abort_flag = code;
+      atomicCAS(ctx.device_status, 0, code);
+      return;
+    }
+  }
+}
+
+// TMA: global -> shared tile load, completion counted on an mbarrier.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1,
+                                            int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// Tensor memory. alloc/dealloc/relinquish are warp-collective.
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_slot)),
+               "r"(columns)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// 32 lanes x 32 columns of 32-bit: thread i of the warp gets lane (base+i),
+// register j is column (col+j).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+      "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
+// Field layout: start address [0,14), leading byte offset [16,30), stride byte
+// offset [32,46) (all in 16-byte units), version [46,48), layout type [61,64).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes,
+                                                    uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// A tile is stored as [cols/64] swizzle-atom columns, each [rows x 64] 16-bit
+// elements (rows * 128 bytes), 1024-byte aligned.
+//
+// K-major use (the contraction runs along the tile's columns): k-step `ks`
+// (16 elements) lives in atom column ks/4 at byte offset (ks%4)*32; 8-row
+// groups are 1024 bytes apart; the leading offset is unused for swizzled
+// K-major operands and is set to the conventional 1.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_saddr, uint32_t rows, int ks) {
+  const uint32_t addr = tile_saddr + (uint32_t)(ks >> 2) * rows * kAtomBytesPerRow + (ks & 3) * 32;
+  return smem_desc_sw128(addr, 16, kAtomGroupBytes);
+}
+// MN-major use (the contraction runs along the tile's ROWS, the columns are the
+// operand's M/N extent): k-step `ks` covers rows [16ks, 16ks+16); the next 64
+// columns are one atom column (rows*128 bytes) further on; 8-row groups are
+// 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_saddr, uint32_t rows, int ks) {
+  const uint32_t addr = tile_saddr + (uint32_t)ks * 16 * kAtomBytesPerRow;
+  return smem_desc_sw128(addr, rows * kAtomBytesPerRow, kAtomGroupBytes);
+}
+
+// Instruction descriptor for kind::f16 with float32 accumulation.
+// fmt: 0 = f16, 1 = bf16. *_mn: 1 when that operand is MN-major.
+__host__ __device__ constexpr uint32_t instr_desc_f16(int fmt, int m, int n, int a_mn, int b_mn) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)a_mn << 15) |
+         ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]; A holds two 16-bit elements per 32-bit column.
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Makes `bar` complete one arrival when every MMA issued so far by this thread
+// has finished (implies tcgen05.fence::before_thread_sync).
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+
+#endif  // __CUDACC__
+}  // namespace umma
+}  // namespace evg

@@ -66,6 +66,8 @@ def softmax_fwd(x: torch.Tensor) -> torch.Tensor:
     cols = x.shape[-1]
     x2 = _rows_view(x, cols)
     y = torch.empty_like(x2)
+    if x2.numel() == 0:
+        return y.view(x.shape)
     with torch.cuda.device(dev):
         call("evg_softmax_fwd", x2.data_ptr(), y.data_ptr(), x2.shape[0], cols, _dtype_enum(x),
              _stream(dev))
@@ -78,6 +80,8 @@ def softmax_bwd(y: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
     cols = y.shape[-1]
     y2, g2 = _rows_view(y, cols), _rows_view(dy, cols)
     dx = torch.empty_like(y2)
+    if y2.numel() == 0:
+        return dx.view(y.shape)
     with torch.cuda.device(dev):
         call("evg_softmax_bwd", y2.data_ptr(), g2.data_ptr(), dx.data_ptr(), y2.shape[0], cols,
              _dtype_enum(y), _stream(dev))
@@ -103,6 +107,8 @@ def layernorm_fwd(x, weight, bias, eps: float = 1e-5):
     y = torch.empty_like(x2)
     mean = torch.empty(rows, device=dev, dtype=torch.float32)
     rstd = torch.empty(rows, device=dev, dtype=torch.float32)
+    if rows == 0:
+        return y.view(x.shape), mean, rstd
     with torch.cuda.device(dev):
         call("evg_layernorm_fwd", x2.data_ptr(), weight.contiguous().data_ptr(),
              bias.contiguous().data_ptr(), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows,
@@ -162,6 +168,8 @@ def rmsnorm_fwd(x, weight, eps: float = 1e-5):
     rows = x2.shape[0]
     y = torch.empty_like(x2)
     rstd = torch.empty(rows, device=dev, dtype=torch.float32)
+    if rows == 0:
+        return y.view(x.shape), rstd
     with torch.cuda.device(dev):
         call("evg_rmsnorm_fwd", x2.data_ptr(), weight.contiguous().data_ptr(), y.data_ptr(),
              rstd.data_ptr(), rows, hidden, float(eps), _dtype_enum(x), _stream(dev))
@@ -214,6 +222,8 @@ def swiglu_fwd(a, b):
     _same("a", a, "b", b)
     a2, b2 = a.contiguous(), b.contiguous()
     c = torch.empty_like(a2)
+    if a2.numel() == 0:
+        return c
     with torch.cuda.device(dev):
         call("evg_swiglu_fwd", a2.data_ptr(), b2.data_ptr(), c.data_ptr(), a2.numel(),
              _dtype_enum(a), _stream(dev))
@@ -234,6 +244,8 @@ def swiglu_bwd(dc, a, b, *, in_place: bool = False):
     else:
         a2, b2 = a.contiguous(), b.contiguous()
         da, db = torch.empty_like(a2), torch.empty_like(b2)
+    if a2.numel() == 0:
+        return da, db
     with torch.cuda.device(dev):
         call("evg_swiglu_bwd", dc2.data_ptr(), a2.data_ptr(), b2.data_ptr(), da.data_ptr(),
              db.data_ptr(), a2.numel(), _dtype_enum(a), _stream(dev))
@@ -346,6 +358,12 @@ def causal_attention_bwd(do, q, k, v, o, lse, scale: float | None = None):
              dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws_bytes, B, H, S, D, float(scale), en,
              _stream(dev))
     return dq, dk, dv
+
+
+def device_status(reset: bool = True) -> None:
+    """Synchronise and raise :class:`EvgError` (EVG_ETIMEOUT) if a bounded wait inside
+    an attention kernel gave up since the last reset."""
+    call("evg_device_status", 1 if reset else 0)
 
 
 def flush_l2(buffer: torch.Tensor) -> None:

@@ -202,6 +202,15 @@ int evg_causal_attention_bwd(const void* dout, const void* q, const void* k,
                              int64_t S, int64_t D, float scale, int dtype,
                              void* stream);
 
+/*
+ * Synchronises the current device (the one exception to "nothing synchronises")
+ * and reports the sticky device-side status of the attention kernels: every
+ * wait inside them is bounded, and a wait that gives up records its identity,
+ * lets the kernel finish and is reported here as EVG_ETIMEOUT (results of that
+ * launch are then undefined). reset != 0 clears the status after reading it.
+ */
+int evg_device_status(int reset);
+
 /* ------------------------------------------------------------------ helpers
  * dst[i] = round_to_dtype(src[i]) for float32 src; used after the cross-GPU
  * all-reduce of float32 dweight/dbias partial sums.
