@@ -1,0 +1,600 @@
+#!/usr/bin/env python
+"""Benchmark driver for the autograd-pair hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference      # the reference's CPU autograd path
+
+A step is one forward + one backward of an operator pair over one batch of
+seeded synthetic inputs of the shape the baseline configuration names. The
+headline workload is LayerNorm bf16 [16384, 4096]; the other operators are
+reported under ``per_op`` in the same JSON line (``--workload X`` makes X the
+headline instead). Prints ONE JSON line on rank 0.
+
+What is timed
+    value     device-resident inputs, K steps between two CUDA events on the
+              launching stream, barrier + synchronise on both sides, max over
+              ranks. Inputs rotate through enough buffer sets that nothing a
+              step reads is still in L2 from the previous use.
+    e2e       the same step through the public pair API starting from pinned HOST
+              buffers: host->device copies of the inputs and device->host copies
+              of every result are inside the timed region.
+    roofline  algorithmic bytes of the dominant launch / its device time,
+              measured with CUDA events inside the timed loop, against the
+              measured peak in MEASURED_PEAKS.json (stated fallback if absent).
+    cpu_baseline / --impl reference
+              the oracle port of the reference's CPU autograd path (the same
+              forward under torch.autograd.grad) on the host cores.
+Multi-GPU: weak scaling. Every rank processes a full-size shard (global rows =
+N x 16384); LayerNorm/RMSNorm all-reduce their float32 dweight/dbias partial
+sums over NCCL, everything else exchanges nothing.
+"""
+
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import math
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+BF16, F32 = torch.bfloat16, torch.float32
+MB = 1 << 20
+
+
+# --------------------------------------------------------------------------
+# workloads: shapes, seeds and input distributions of the baseline configs
+def _gen(device, seed):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return g
+
+
+def _randn(shape, dtype, device, g, scale=1.0, shift=0.0):
+    t = torch.randn(shape, device=device, dtype=torch.float32, generator=g)
+    if scale != 1.0 or shift != 0.0:
+        t = t * scale + shift
+    return t.to(dtype)
+
+
+class Workload:
+    name = ""
+    dtype = "bf16"
+    bound = "hbm"
+    collective = False
+    kernels_per_step = 0
+    pair = None  # operator whose candidate module provides fwd / bwd
+
+    def __init__(self, device):
+        self.device = device
+        self._pair = None
+
+    # The candidate module is imported on first use, so the CPU reference arm
+    # never touches the CUDA library.
+    @property
+    def fwd(self):
+        if self._pair is None:
+            self._pair = _load_pair(self.pair)
+        return self._pair[0]
+
+    @property
+    def bwd(self):
+        if self._pair is None:
+            self._pair = _load_pair(self.pair)
+        return self._pair[1]
+
+    # bytes (HBM-bound) or FLOPs (tensor-bound) that one fwd / bwd must move
+    fwd_work = 0
+    bwd_work = 0
+
+    @property
+    def step_work(self):
+        return self.fwd_work + self.bwd_work
+
+
+def _load_pair(op):
+    path = os.path.join(ROOT, "evograd_b200", "pairs", f"{op}.py")
+    spec = importlib.util.spec_from_file_location(f"bench_pair_{op}", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return getattr(mod, f"{op}_forward_with_saved"), getattr(mod, f"{op}_backward_from_saved")
+
+
+class SoftmaxWL(Workload):
+    name, dtype, kernels_per_step, pair = "softmax_f32_4096x1024", "f32", 2, "softmax"
+    rows, cols = 4096, 1024
+
+    def __init__(self, device):
+        super().__init__(device)
+        nb = self.rows * self.cols * 4
+        self.fwd_work, self.bwd_work = 2 * nb, 3 * nb
+
+    def make(self, device, salt=0):
+        g = _gen(device, self.rows * 100003 + self.cols + salt)
+        return {"x": _randn((self.rows, self.cols), F32, device, g),
+                "dy": _randn((self.rows, self.cols), F32, device, g)}
+
+    def inputs_of(self, s):
+        return [s["x"], s["dy"]]
+
+    def step(self, s, timer=None):
+        run = timer.run if timer else (lambda _n, f: f())
+        y, saved = run("fwd", lambda: self.fwd(s["x"]))
+        (dx,) = run("bwd", lambda: self.bwd(s["dy"], saved))
+        return [y, dx]
+
+    def cpu_step(self, s):
+        from oracle import autograd_oracle as ao
+        return ao.oracle("softmax", s)
+
+    def config(self):
+        return {"workload": self.name, "shape": [self.rows, self.cols], "saved": "y"}
+
+
+class NormWL(Workload):
+    kind = "layernorm"
+    rows, hidden, eps = 16384, 4096, 1e-5
+    collective = True
+
+    def __init__(self, device, group=None):
+        super().__init__(device)
+        nb = self.rows * self.hidden * 2
+        self.fwd_work, self.bwd_work = 2 * nb, 3 * nb
+        self.name = f"{self.kind}_bf16_{self.rows}x{self.hidden}"
+        self.pair = self.kind
+        self.world = torch.distributed.get_world_size() if torch.distributed.is_initialized() else 1
+        self.sharded = None
+        if self.world > 1:
+            from evograd_b200.sharded import ShardedNorm
+
+            self.sharded = ShardedNorm(self.kind, group)
+        # fwd 1 kernel; bwd 2 (row kernel + column reduce); sharded adds the rounding kernel
+        self.kernels_per_step = 3 + (1 if self.world > 1 else 0)
+
+    def make(self, device, salt=0):
+        g = _gen(device, self.rows * 100000 + self.hidden + salt)
+        s = {"x": _randn((self.rows, self.hidden), BF16, device, g),
+             "weight": _randn((self.hidden,), BF16, device, g, 0.1, 1.0)}
+        if self.kind == "layernorm":
+            s["bias"] = _randn((self.hidden,), BF16, device, g, 0.1, 0.0)
+        s["dy"] = _randn((self.rows, self.hidden), BF16, device, g)
+        s["eps"] = self.eps
+        return s
+
+    def inputs_of(self, s):
+        return [s[k] for k in ("x", "weight", "bias", "dy") if k in s]
+
+    def step(self, s, timer=None):
+        run = timer.run if timer else (lambda _n, f: f())
+        ln = self.kind == "layernorm"
+        if self.sharded is not None:
+            y, saved = run("fwd", lambda: self.sharded.forward_with_saved(
+                s["x"], s["weight"], s.get("bias"), self.eps))
+            grads = run("bwd", lambda: self.sharded.backward_from_saved(s["dy"], saved))
+        else:
+            args = (s["x"], s["weight"], s["bias"], self.eps) if ln else (s["x"], s["weight"], self.eps)
+            y, saved = run("fwd", lambda: self.fwd(*args))
+            grads = run("bwd", lambda: self.bwd(s["dy"], saved))
+        return [y, *grads]
+
+    def cpu_step(self, s):
+        from oracle import autograd_oracle as ao
+        return ao.oracle(self.kind, s)
+
+    def config(self):
+        return {"workload": self.name, "shape": [self.rows, self.hidden], "eps": self.eps,
+                "saved": "mean,rstd f32" if self.kind == "layernorm" else "rstd f32"}
+
+
+class LayerNormWL(NormWL):
+    kind = "layernorm"
+
+
+class RMSNormWL(NormWL):
+    kind, rows, eps = "rmsnorm", 32768, 1e-6
+
+
+class SwiGLUWL(Workload):
+    name, kernels_per_step, pair = "swiglu_bf16_32768x14336", 2, "swiglu"
+    rows, cols = 32768, 14336
+
+    def __init__(self, device):
+        super().__init__(device)
+        nb = self.rows * self.cols * 2
+        self.fwd_work, self.bwd_work = 3 * nb, 5 * nb
+
+    def make(self, device, salt=0):
+        g = _gen(device, self.rows * 100003 + self.cols + salt)
+        return {k: _randn((self.rows, self.cols), BF16, device, g) for k in ("a", "b", "dc")}
+
+    def inputs_of(self, s):
+        return [s["a"], s["b"], s["dc"]]
+
+    def step(self, s, timer=None):
+        run = timer.run if timer else (lambda _n, f: f())
+        c, saved = run("fwd", lambda: self.fwd(s["a"], s["b"]))
+        da, db = run("bwd", lambda: self.bwd(s["dc"], saved))
+        return [c, da, db]
+
+    def cpu_step(self, s):
+        from oracle import autograd_oracle as ao
+        return ao.oracle("swiglu", s)
+
+    def config(self):
+        return {"workload": self.name, "shape": [self.rows, self.cols], "saved": "a,b by reference"}
+
+
+class RopeWL(Workload):
+    name, kernels_per_step = "rope_bf16_qk_8x4096x32x128", 2
+    B, S, H, D, theta = 8, 4096, 32, 128, 10000.0
+
+    def __init__(self, device):
+        super().__init__(device)
+        nb = self.B * self.S * self.H * self.D * 2
+        self.fwd_work, self.bwd_work = 4 * nb, 4 * nb  # q and k, read + write each way
+
+    def make(self, device, salt=0):
+        g = _gen(device, self.S * 100003 + self.H * 1009 + self.D + salt)
+        shape = (self.B, self.S, self.H, self.D)
+        s = {k: _randn(shape, BF16, device, g) for k in ("q", "k", "dq_out", "dk_out")}
+        pos = torch.arange(self.S, device=device, dtype=F32)[:, None]
+        inv = self.theta ** (-torch.arange(0, self.D, 2, device=device, dtype=F32) / self.D)
+        s["cos"], s["sin"] = (pos * inv[None]).cos(), (pos * inv[None]).sin()  # f32 [S, D/2]
+        return s
+
+    def inputs_of(self, s):
+        return [s["q"], s["k"], s["dq_out"], s["dk_out"], s["cos"], s["sin"]]
+
+    def step(self, s, timer=None):
+        from evograd_b200 import ops
+        run = timer.run if timer else (lambda _n, f: f())
+        yq, yk = run("fwd", lambda: ops.rope_qk_fwd(s["q"], s["k"], s["cos"], s["sin"], layout="bthd"))
+        gq, gk = run("bwd", lambda: ops.rope_qk_bwd(s["dq_out"], s["dk_out"], s["cos"], s["sin"],
+                                                   layout="bthd"))
+        return [yq, yk, gq, gk]
+
+    def cpu_step(self, s):
+        from oracle import autograd_oracle as ao
+        cos = torch.cat((s["cos"], s["cos"]), -1)
+        sin = torch.cat((s["sin"], s["sin"]), -1)
+        out = []
+        for x, dy in ((s["q"], s["dq_out"]), (s["k"], s["dk_out"])):
+            out.append(ao.oracle("rope", {"x": x.transpose(1, 2), "cos": cos, "sin": sin,
+                                          "dy": dy.transpose(1, 2)}))
+        return out
+
+    def config(self):
+        return {"workload": self.name, "shape": [self.B, self.S, self.H, self.D],
+                "tables": "f32 [4096,64]", "theta": self.theta, "saved": "none"}
+
+
+class AttentionWL(Workload):
+    name, bound, kernels_per_step, pair = "causal_attention_bf16_4x32x8192x128", "tensor", 4, \
+        "causal_attention"
+    B, H, S, D = 4, 32, 8192, 128
+
+    def __init__(self, device):
+        super().__init__(device)
+        fwd = 4 * self.B * self.H * self.S * self.S * self.D * 0.5  # causal-halved
+        self.fwd_work, self.bwd_work = fwd, 2.5 * fwd
+
+    def make(self, device, salt=0):
+        g = _gen(device, (((4 * 131 + 32) * 131 + 8192) * 131) + 128 + salt)
+        shape = (self.B, self.H, self.S, self.D)
+        return {k: _randn(shape, BF16, device, g) for k in ("q", "k", "v", "do")}
+
+    def inputs_of(self, s):
+        return [s["q"], s["k"], s["v"], s["do"]]
+
+    def step(self, s, timer=None):
+        run = timer.run if timer else (lambda _n, f: f())
+        o, saved = run("fwd", lambda: self.fwd(s["q"], s["k"], s["v"]))
+        dq, dk, dv = run("bwd", lambda: self.bwd(s["do"], saved))
+        return [o, dq, dk, dv]
+
+    def cpu_step(self, s, heads=2):
+        from oracle import autograd_oracle as ao
+        sl = {k: v[:1, :heads] for k, v in s.items()}
+        return ao.oracle("causal_attention", sl, forward=ao.causal_attention_forward_sdpa)
+
+    def config(self):
+        return {"workload": self.name, "shape": [self.B, self.H, self.S, self.D],
+                "scale": 1 / math.sqrt(self.D), "saved": "o, lse f32"}
+
+
+WORKLOADS = {"softmax": SoftmaxWL, "layernorm": LayerNormWL, "rmsnorm": RMSNormWL,
+             "swiglu": SwiGLUWL, "rope": RopeWL, "attention": AttentionWL}
+
+
+# --------------------------------------------------------------------------
+def _dist_setup(n_gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    if n_gpus != world:
+        if rank == 0:
+            print(f"[bench] --gpus {n_gpus} but WORLD_SIZE={world}; launch with torch.distributed.run",
+                  file=sys.stderr)
+        if world == 1 and n_gpus > 1:
+            raise SystemExit(2)
+    return world, rank, local
+
+
+def _barrier_fn(world):
+    if world <= 1:
+        return None
+    return lambda: torch.distributed.barrier()
+
+
+def _max_over_ranks(ms, world):
+    if world <= 1:
+        return ms
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def measure_device(wl, steps, warmup, world, sections=True):
+    """value leg: returns (ms for `steps` steps [max over ranks], section totals, launches)."""
+    from evograd_b200.timing import SectionTimer, rotation_count, time_steps
+
+    device = torch.device("cuda", torch.cuda.current_device())
+    probe = wl.make(device)
+    set_bytes = sum(t.numel() * t.element_size() for t in wl.inputs_of(probe))
+    n_sets = 1 if set_bytes > 2 * torch.cuda.get_device_properties(device).L2_cache_size \
+        else rotation_count(set_bytes)
+    sets = [probe] + [wl.make(device, salt=i) for i in range(1, n_sets)]
+    timer = SectionTimer() if sections else None
+    live = [None]
+
+    def step(i):
+        live[0] = wl.step(sets[i % n_sets], timer if (timer and i >= warmup) else None)
+
+    ms = time_steps(step, steps, warmup, barrier=_barrier_fn(world))
+    ms = _max_over_ranks(ms, world)
+    totals = timer.totals_ms() if timer else {}
+    del sets, live
+    torch.cuda.empty_cache()
+    return ms, totals, wl.kernels_per_step * steps, n_sets
+
+
+def measure_e2e(wl, steps, warmup, world):
+    """e2e leg: pinned host inputs -> H2D -> fwd -> bwd -> D2H of every result."""
+    from evograd_b200.timing import time_steps
+
+    device = torch.device("cuda", torch.cuda.current_device())
+    dev_set = wl.make(device)
+    host = {k: (v.cpu().pin_memory() if torch.is_tensor(v) else v) for k, v in dev_set.items()}
+    outs = wl.step(dev_set)
+    host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+    h2d = sum(v.numel() * v.element_size() for v in host.values() if torch.is_tensor(v))
+    d2h = sum(o.numel() * o.element_size() for o in host_out)
+    del outs
+
+    def step(_i):
+        for k, v in host.items():
+            if torch.is_tensor(v):
+                dev_set[k].copy_(v, non_blocking=True)
+        results = wl.step(dev_set)
+        for dst, src in zip(host_out, results):
+            dst.copy_(src, non_blocking=True)
+
+    ms = time_steps(step, steps, warmup, barrier=_barrier_fn(world))
+    ms = _max_over_ranks(ms, world)
+    del dev_set, host, host_out
+    torch.cuda.empty_cache()
+    return ms, h2d, d2h
+
+
+def measure_cpu(wl, budget_s=12.0, max_reps=10, threads=None):
+    """Reference CPU path (oracle port) on the host cores; returns (s/step, reps, cores)."""
+    if threads:
+        torch.set_num_threads(threads)
+    s = wl.make(torch.device("cpu"))
+    s = {k: v for k, v in s.items()}
+    t0 = time.perf_counter()
+    wl.cpu_step(s)  # warm-up
+    first = time.perf_counter() - t0
+    reps = max(1, min(max_reps, int(budget_s / max(first, 1e-3))))
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        wl.cpu_step(s)
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    return times[len(times) // 2], reps, torch.get_num_threads()
+
+
+def _rate(work, ms):
+    """GB/s for bytes, TFLOP/s for FLOPs: both are work / (ms * 1e6) / 1e3... in their unit."""
+    return work / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+
+
+def per_op_entry(wl, steps, warmup, world, peaks):
+    ms, totals, _launches, n_sets = measure_device(wl, steps, warmup, world)
+    step_ms = ms / steps
+    fwd_ms = totals["fwd"][0] / totals["fwd"][1]
+    bwd_ms = totals["bwd"][0] / totals["bwd"][1]
+    e = {"step_ms": round(step_ms, 4), "fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
+         "buffer_sets": n_sets}
+    if wl.bound == "hbm":
+        peak = peaks["hbm_gbs"]
+        e.update({"algorithmic_MB": round(wl.step_work / 1e6, 1),
+                  "gbs": round(_rate(wl.step_work, step_ms) * world, 1),
+                  "fwd_gbs": round(_rate(wl.fwd_work, fwd_ms), 1),
+                  "bwd_gbs": round(_rate(wl.bwd_work, bwd_ms), 1),
+                  "frac_of_hbm_peak": round(_rate(wl.step_work, step_ms) / peak, 4)})
+    else:
+        peak = peaks["bf16_tflops_sustained"]
+        e.update({"fwd_tflops": round(wl.fwd_work / (fwd_ms * 1e-3) / 1e12, 1),
+                  "bwd_tflops": round(wl.bwd_work / (bwd_ms * 1e-3) / 1e12, 1),
+                  "tflops": round(wl.step_work / (step_ms * 1e-3) / 1e12 * world, 1),
+                  "bwd_frac_of_bf16_peak": round(wl.bwd_work / (bwd_ms * 1e-3) / 1e12 / peak, 4)})
+    return e
+
+
+def run_ours(args):
+    from evograd_b200 import _cabi  # noqa: F401  (fails loudly if the library is missing)
+    from evograd_b200.timing import ClockSampler, measured_peaks
+
+    world, rank, local = _dist_setup(args.gpus)
+    device = torch.device("cuda", torch.cuda.current_device())
+    peaks, peak_source = measured_peaks()
+    wl = WORKLOADS[args.workload](device)
+
+    with ClockSampler(local) as clocks:
+        ms, totals, launches, n_sets = measure_device(wl, args.steps, args.warmup, world)
+    step_ms = ms / args.steps
+    if wl.bound == "hbm":
+        metric = f"fwd+bwd achieved HBM GB/s ({wl.name})"
+        unit, value = "GB/s", _rate(wl.step_work, step_ms) * world
+    else:
+        metric = f"fwd+bwd TFLOP/s ({wl.name}; attention bwd TFLOP/s under per_op)"
+        unit, value = "TFLOP/s", wl.step_work / (step_ms * 1e-3) / 1e12 * world
+
+    # roofline of the dominant launch: the backward (largest share of the step)
+    bwd_total, bwd_n = totals["bwd"]
+    bwd_ms = bwd_total / bwd_n
+    if wl.bound == "hbm":
+        achieved, peak, runit = _rate(wl.bwd_work, bwd_ms), peaks["hbm_gbs"], "GB/s"
+    else:
+        achieved, peak, runit = wl.bwd_work / (bwd_ms * 1e-3) / 1e12, peaks["bf16_tflops_sustained"], "TFLOP/s"
+    roofline = {"kernel": f"{args.workload} backward", "bound": wl.bound, "achieved": round(achieved, 1),
+                "peak": peak, "unit": runit, "frac": round(achieved / peak, 4),
+                "peak_source": f"of {peak_source}", "per_launch_ms": round(bwd_ms, 4),
+                "traffic": TRAFFIC_NCU.get(args.workload)}
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms, h2d, d2h = measure_e2e(wl, e2e_steps, max(3, min(args.warmup, 3)), world)
+    e2e_step_ms = e2e_ms / e2e_steps
+    e2e_value = (_rate(wl.step_work, e2e_step_ms) if wl.bound == "hbm"
+                 else wl.step_work / (e2e_step_ms * 1e-3) / 1e12) * world
+
+    line = {
+        "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(step_ms, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": wl.dtype, "data": "synthetic",
+        "config": {**wl.config(), "l2": f"{n_sets} rotating input set(s), each pass reads data not in L2",
+                   "parallelism": f"rows x{world}" if world > 1 else "1 gpu",
+                   "launch": "eager, current stream"},
+        "e2e": {"value": round(e2e_value, 2), "unit": unit, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_step_ms, 4), "steps": e2e_steps},
+        "gpu_launches": launches,
+        "roofline": roofline,
+        "clocks": clocks.summary(),
+    }
+
+    if not args.no_per_op:
+        per_op = {}
+        for name, cls in WORKLOADS.items():
+            w2 = wl if name == args.workload else cls(device)
+            per_op[name] = per_op_entry(w2, max(3, args.steps // 2), max(3, args.warmup), world, peaks)
+            del w2
+            torch.cuda.empty_cache()
+        line["per_op"] = per_op
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        sec, reps, cores = measure_cpu(wl)
+        cpu_val = (wl.step_work / sec / 1e9) if wl.bound == "hbm" else wl.step_work / sec / 1e12
+        sample = f"full {wl.name} step x{reps} (median)"
+        if args.workload == "attention":
+            cpu_val = cpu_val * 2 / (wl.B * wl.H)
+            sample = f"2 of {wl.B * wl.H} (batch, head) units x{reps}, rate scaled per unit"
+        line["cpu_baseline"] = {"value": round(cpu_val, 3), "unit": unit, "cores": cores,
+                                "kind": "port", "sample": sample, "s_per_step": round(sec, 4)}
+
+    from evograd_b200 import ops
+    ops.device_status()
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per backward launch from the ncu
+# captures summarised under profiles/ (None until a capture exists).
+TRAFFIC_NCU = {}
+
+
+def run_reference(args):
+    """The reference's own implementation of the path: its CPU autograd oracle
+    (restated in oracle/), all host threads, on the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = WORKLOADS[args.workload](torch.device("cpu"))
+    s = wl.make(torch.device("cpu"))
+    for _ in range(min(args.warmup, 1)):
+        wl.cpu_step(s)
+    steps = max(1, args.steps)
+    # bound the whole run to a few minutes
+    t0 = time.perf_counter()
+    wl.cpu_step(s)
+    one = time.perf_counter() - t0
+    steps = max(1, min(steps, int(150.0 / max(one, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        wl.cpu_step(s)
+    sec = (time.perf_counter() - t0) / steps
+    hbm = wl.bound == "hbm"
+    unit = "GB/s" if hbm else "TFLOP/s"
+    work = wl.step_work
+    sample = f"full {wl.name} step"
+    if args.workload == "attention":
+        work = work * 2 / (wl.B * wl.H)
+        sample = f"2 of {wl.B * wl.H} (batch, head) units per step"
+    value = work / sec / (1e9 if hbm else 1e12)
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference",
+        "metric": (f"fwd+bwd achieved HBM GB/s ({wl.name})" if hbm
+                   else f"fwd+bwd TFLOP/s ({wl.name}; attention bwd TFLOP/s under per_op)"),
+        "value": round(value, 4), "unit": unit, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 1) + 1, "ms_per_step": round(sec * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+        "data": "synthetic", "config": {**wl.config(), "device": "host CPU"},
+        "cpu_baseline": {"value": round(value, 4), "unit": unit, "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": unit, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="layernorm")
+    ap.add_argument("--no-per-op", action="store_true", help="skip the per-operator table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,120 @@
+"""Sharding of the autograd pairs across ranks (one process per GPU).
+
+The operators partition into independent units, so the only data exchanged
+between ranks is the float32 parameter-gradient partial sums of LayerNorm /
+RMSNorm (``[2, hidden]`` / ``[hidden]`` floats per step):
+
+    softmax, swiglu     contiguous row blocks, no exchange
+    rope                contiguous batch blocks, tables replicated, no exchange
+    layernorm, rmsnorm  contiguous row blocks; every rank forms float32
+                        dweight/dbias over ITS rows, one all_reduce(SUM), and only
+                        then rounds to the parameter dtype (rounding before the sum
+                        would not match a single-device float32 accumulation)
+    causal attention    contiguous blocks of the B*H (batch, head) units, no exchange
+
+The reference has no distributed path (its ``--gpus`` runs independent searches);
+this launcher is new. The local kernels are injected so that the host logic
+(partitioning, reduction, rounding order) can be exercised with ``gloo`` ranks
+on CPU against the oracle, while production uses ``evograd_b200.ops``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+def block_range(total: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous ``[start, stop)`` of ``total`` units for ``rank``; the first
+    ``total % world`` ranks get one extra unit, so sizes differ by at most one."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} for world size {world}")
+    if total < 0:
+        raise ValueError("total must be non-negative")
+    base, extra = divmod(total, world)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def _world(group) -> tuple[int, int]:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size(group), dist.get_rank(group)
+    return 1, 0
+
+
+@dataclass
+class NormKernels:
+    """The local (single-device) entry points a :class:`ShardedNorm` drives."""
+
+    layernorm_fwd: object
+    layernorm_bwd: object  # (dy, x, w, mean, rstd, partials_f32=True) -> (dx, dwdb_f32, None)
+    rmsnorm_fwd: object
+    rmsnorm_bwd: object  # (dy, x, w, rstd, partials_f32=True) -> (dx, dw_f32)
+    cast_from_f32: object
+
+    @staticmethod
+    def cuda() -> "NormKernels":
+        from . import ops
+
+        return NormKernels(ops.layernorm_fwd, ops.layernorm_bwd, ops.rmsnorm_fwd, ops.rmsnorm_bwd,
+                           ops.cast_from_f32)
+
+
+class ShardedNorm:
+    """LayerNorm / RMSNorm autograd pair over a row shard with the cross-rank
+    parameter-gradient reduction. ``kind`` is "layernorm" or "rmsnorm"."""
+
+    def __init__(self, kind: str, group=None, kernels: NormKernels | None = None):
+        if kind not in ("layernorm", "rmsnorm"):
+            raise ValueError(f"kind must be layernorm or rmsnorm, got {kind!r}")
+        self.kind = kind
+        self.group = group
+        self.k = kernels or NormKernels.cuda()
+        self.collectives = 0  # all_reduce calls issued so far
+
+    def forward_with_saved(self, x_shard, weight, bias=None, eps: float = 1e-5):
+        if self.kind == "layernorm":
+            if bias is None:
+                raise ValueError("layernorm needs a bias")
+            y, mean, rstd = self.k.layernorm_fwd(x_shard, weight, bias, eps)
+            return y, (x_shard, weight, mean, rstd)
+        y, rstd = self.k.rmsnorm_fwd(x_shard, weight, eps)
+        return y, (x_shard, weight, rstd)
+
+    def backward_from_saved(self, dy_shard, saved):
+        """Returns ``(dx_shard, dweight[, dbias])`` with the parameter gradients
+        summed over ALL ranks' rows and rounded once, identical on every rank."""
+        world, _ = _world(self.group)
+        if self.kind == "layernorm":
+            x, weight, mean, rstd = saved
+            dx, partial, _ = self.k.layernorm_bwd(dy_shard, x, weight, mean, rstd, partials_f32=True)
+        else:
+            x, weight, rstd = saved
+            dx, partial = self.k.rmsnorm_bwd(dy_shard, x, weight, rstd, partials_f32=True)
+        if partial.dtype != torch.float32:
+            raise TypeError("local backward must return float32 partial sums")
+        if world > 1:
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+            self.collectives += 1
+        rounded = self.k.cast_from_f32(partial, weight.dtype)
+        if self.kind == "layernorm":
+            return dx, rounded[0], rounded[1]
+        return dx, rounded
+
+
+def shard_rows(t: torch.Tensor, group=None) -> torch.Tensor:
+    """This rank's contiguous row block of a ``[rows, ...]`` tensor."""
+    world, rank = _world(group)
+    a, b = block_range(t.shape[0], world, rank)
+    return t[a:b]
+
+
+def shard_heads(t: torch.Tensor, group=None) -> torch.Tensor:
+    """This rank's block of (batch, head) units of a ``[B, H, S, D]`` tensor,
+    returned as ``[1, units, S, D]``."""
+    world, rank = _world(group)
+    B, H = t.shape[0], t.shape[1]
+    a, b = block_range(B * H, world, rank)
+    return t.reshape(1, B * H, *t.shape[2:])[:, a:b]
