@@ -95,6 +95,20 @@ class Workload:
     fwd_work = 0
     bwd_work = 0
 
+    def forward(self, s):
+        """-> (list of output tensors, saved state)"""
+        raise NotImplementedError
+
+    def backward(self, s, saved):
+        """-> list of gradient tensors"""
+        raise NotImplementedError
+
+    def step(self, s, timer=None):
+        run = timer.run if timer else (lambda _n, f: f())
+        outs, saved = run("fwd", lambda: self.forward(s))
+        grads = run("bwd", lambda: self.backward(s, saved))
+        return [*outs, *grads]
+
     @property
     def step_work(self):
         return self.fwd_work + self.bwd_work
@@ -125,11 +139,12 @@ class SoftmaxWL(Workload):
     def inputs_of(self, s):
         return [s["x"], s["dy"]]
 
-    def step(self, s, timer=None):
-        run = timer.run if timer else (lambda _n, f: f())
-        y, saved = run("fwd", lambda: self.fwd(s["x"]))
-        (dx,) = run("bwd", lambda: self.bwd(s["dy"], saved))
-        return [y, dx]
+    def forward(self, s):
+        y, saved = self.fwd(s["x"])
+        return [y], saved
+
+    def backward(self, s, saved):
+        return list(self.bwd(s["dy"], saved))
 
     def cpu_step(self, s):
         from oracle import autograd_oracle as ao
@@ -172,18 +187,19 @@ class NormWL(Workload):
     def inputs_of(self, s):
         return [s[k] for k in ("x", "weight", "bias", "dy") if k in s]
 
-    def step(self, s, timer=None):
-        run = timer.run if timer else (lambda _n, f: f())
-        ln = self.kind == "layernorm"
+    def forward(self, s):
         if self.sharded is not None:
-            y, saved = run("fwd", lambda: self.sharded.forward_with_saved(
-                s["x"], s["weight"], s.get("bias"), self.eps))
-            grads = run("bwd", lambda: self.sharded.backward_from_saved(s["dy"], saved))
+            y, saved = self.sharded.forward_with_saved(s["x"], s["weight"], s.get("bias"), self.eps)
+        elif self.kind == "layernorm":
+            y, saved = self.fwd(s["x"], s["weight"], s["bias"], self.eps)
         else:
-            args = (s["x"], s["weight"], s["bias"], self.eps) if ln else (s["x"], s["weight"], self.eps)
-            y, saved = run("fwd", lambda: self.fwd(*args))
-            grads = run("bwd", lambda: self.bwd(s["dy"], saved))
-        return [y, *grads]
+            y, saved = self.fwd(s["x"], s["weight"], self.eps)
+        return [y], saved
+
+    def backward(self, s, saved):
+        if self.sharded is not None:
+            return list(self.sharded.backward_from_saved(s["dy"], saved))
+        return list(self.bwd(s["dy"], saved))
 
     def cpu_step(self, s):
         from oracle import autograd_oracle as ao
@@ -218,11 +234,12 @@ class SwiGLUWL(Workload):
     def inputs_of(self, s):
         return [s["a"], s["b"], s["dc"]]
 
-    def step(self, s, timer=None):
-        run = timer.run if timer else (lambda _n, f: f())
-        c, saved = run("fwd", lambda: self.fwd(s["a"], s["b"]))
-        da, db = run("bwd", lambda: self.bwd(s["dc"], saved))
-        return [c, da, db]
+    def forward(self, s):
+        c, saved = self.fwd(s["a"], s["b"])
+        return [c], saved
+
+    def backward(self, s, saved):
+        return list(self.bwd(s["dc"], saved))
 
     def cpu_step(self, s):
         from oracle import autograd_oracle as ao
@@ -253,13 +270,13 @@ class RopeWL(Workload):
     def inputs_of(self, s):
         return [s["q"], s["k"], s["dq_out"], s["dk_out"], s["cos"], s["sin"]]
 
-    def step(self, s, timer=None):
+    def forward(self, s):
         from evograd_b200 import ops
-        run = timer.run if timer else (lambda _n, f: f())
-        yq, yk = run("fwd", lambda: ops.rope_qk_fwd(s["q"], s["k"], s["cos"], s["sin"], layout="bthd"))
-        gq, gk = run("bwd", lambda: ops.rope_qk_bwd(s["dq_out"], s["dk_out"], s["cos"], s["sin"],
-                                                   layout="bthd"))
-        return [yq, yk, gq, gk]
+        return list(ops.rope_qk_fwd(s["q"], s["k"], s["cos"], s["sin"], layout="bthd")), None
+
+    def backward(self, s, saved):
+        from evograd_b200 import ops
+        return list(ops.rope_qk_bwd(s["dq_out"], s["dk_out"], s["cos"], s["sin"], layout="bthd"))
 
     def cpu_step(self, s):
         from oracle import autograd_oracle as ao
@@ -294,11 +311,12 @@ class AttentionWL(Workload):
     def inputs_of(self, s):
         return [s["q"], s["k"], s["v"], s["do"]]
 
-    def step(self, s, timer=None):
-        run = timer.run if timer else (lambda _n, f: f())
-        o, saved = run("fwd", lambda: self.fwd(s["q"], s["k"], s["v"]))
-        dq, dk, dv = run("bwd", lambda: self.bwd(s["do"], saved))
-        return [o, dq, dk, dv]
+    def forward(self, s):
+        o, saved = self.fwd(s["q"], s["k"], s["v"])
+        return [o], saved
+
+    def backward(self, s, saved):
+        return list(self.bwd(s["do"], saved))
 
     def cpu_step(self, s, heads=2):
         from oracle import autograd_oracle as ao
@@ -350,14 +368,10 @@ def _max_over_ranks(ms, world):
 
 def measure_device(wl, steps, warmup, world, sections=True):
     """value leg: returns (ms for `steps` steps [max over ranks], section totals, launches)."""
-    from evograd_b200.timing import SectionTimer, rotation_count, time_steps
+    from evograd_b200.timing import SectionTimer, time_steps
 
-    device = torch.device("cuda", torch.cuda.current_device())
-    probe = wl.make(device)
-    set_bytes = sum(t.numel() * t.element_size() for t in wl.inputs_of(probe))
-    n_sets = 1 if set_bytes > 2 * torch.cuda.get_device_properties(device).L2_cache_size \
-        else rotation_count(set_bytes)
-    sets = [probe] + [wl.make(device, salt=i) for i in range(1, n_sets)]
+    sets = _make_sets(wl)
+    n_sets = len(sets)
     timer = SectionTimer() if sections else None
     live = [None]
 
@@ -370,6 +384,56 @@ def measure_device(wl, steps, warmup, world, sections=True):
     del sets, live
     torch.cuda.empty_cache()
     return ms, totals, wl.kernels_per_step * steps, n_sets
+
+
+def _make_sets(wl):
+    from evograd_b200.timing import rotation_count
+
+    device = torch.device("cuda", torch.cuda.current_device())
+    probe = wl.make(device)
+    set_bytes = sum(t.numel() * t.element_size() for t in wl.inputs_of(probe))
+    n_sets = 1 if set_bytes > 2 * torch.cuda.get_device_properties(device).L2_cache_size \
+        else rotation_count(set_bytes)
+    return [probe] + [wl.make(device, salt=i) for i in range(1, n_sets)]
+
+
+def measure_graphs(wl, steps, warmup, world):
+    """Per-operator leg with launch overhead removed: one CUDA graph per input
+    set for the full step, the forward alone and the backward alone; K replays
+    of each are timed. Returns (step_ms, fwd_ms, bwd_ms, n_sets) per launch."""
+    from evograd_b200.timing import time_steps
+
+    sets = _make_sets(wl)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):  # warm-up outside capture (lazy init, attributes)
+        for s_ in sets[:1]:
+            wl.step(s_)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g_step, g_fwd, g_bwd, keep = [], [], [], []
+    for s_ in sets:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            keep.append(wl.step(s_))
+        g_step.append(g)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            outs, saved = wl.forward(s_)
+        keep.append(outs)
+        g_fwd.append(g)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            keep.append(wl.backward(s_, saved))
+        g_bwd.append(g)
+    n = len(sets)
+    res = []
+    for graphs in (g_step, g_fwd, g_bwd):
+        ms = time_steps(lambda i: graphs[i % n].replay(), steps, warmup, barrier=_barrier_fn(world))
+        res.append(_max_over_ranks(ms, world) / steps)
+    del g_step, g_fwd, g_bwd, keep, sets
+    torch.cuda.empty_cache()
+    return res[0], res[1], res[2], n
 
 
 def measure_e2e(wl, steps, warmup, world):
@@ -425,12 +489,20 @@ def _rate(work, ms):
 
 
 def per_op_entry(wl, steps, warmup, world, peaks):
-    ms, totals, _launches, n_sets = measure_device(wl, steps, warmup, world)
-    step_ms = ms / steps
-    fwd_ms = totals["fwd"][0] / totals["fwd"][1]
-    bwd_ms = totals["bwd"][0] / totals["bwd"][1]
-    e = {"step_ms": round(step_ms, 4), "fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4),
-         "buffer_sets": n_sets}
+    launch = "cuda graph replay"
+    try:
+        if world > 1 and wl.collective:
+            raise RuntimeError("collective inside the step: timed eagerly")
+        step_ms, fwd_ms, bwd_ms, n_sets = measure_graphs(wl, steps, warmup, world)
+    except Exception as exc:  # capture refused: time the same calls eagerly
+        launch = f"eager ({type(exc).__name__})"
+        torch.cuda.synchronize()
+        ms, totals, _launches, n_sets = measure_device(wl, steps, warmup, world)
+        step_ms = ms / steps
+        fwd_ms = totals["fwd"][0] / totals["fwd"][1]
+        bwd_ms = totals["bwd"][0] / totals["bwd"][1]
+    e = {"step_ms": round(step_ms, 5), "fwd_ms": round(fwd_ms, 5), "bwd_ms": round(bwd_ms, 5),
+         "buffer_sets": n_sets, "launch": launch}
     if wl.bound == "hbm":
         peak = peaks["hbm_gbs"]
         e.update({"algorithmic_MB": round(wl.step_work / 1e6, 1),
@@ -478,11 +550,15 @@ def run_ours(args):
                 "peak_source": f"of {peak_source}", "per_launch_ms": round(bwd_ms, 4),
                 "traffic": TRAFFIC_NCU.get(args.workload)}
 
-    e2e_steps = max(3, min(args.steps, 10))
-    e2e_ms, h2d, d2h = measure_e2e(wl, e2e_steps, max(3, min(args.warmup, 3)), world)
-    e2e_step_ms = e2e_ms / e2e_steps
-    e2e_value = (_rate(wl.step_work, e2e_step_ms) if wl.bound == "hbm"
-                 else wl.step_work / (e2e_step_ms * 1e-3) / 1e12) * world
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(3, min(args.steps, 10))
+        e2e_ms, h2d, d2h = measure_e2e(wl, e2e_steps, max(3, min(args.warmup, 3)), world)
+        e2e_step_ms = e2e_ms / e2e_steps
+        e2e_value = (_rate(wl.step_work, e2e_step_ms) if wl.bound == "hbm"
+                     else wl.step_work / (e2e_step_ms * 1e-3) / 1e12) * world
+        e2e = {"value": round(e2e_value, 2), "unit": unit, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_step_ms, 4), "steps": e2e_steps}
 
     line = {
         "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world,
@@ -492,8 +568,7 @@ def run_ours(args):
         "config": {**wl.config(), "l2": f"{n_sets} rotating input set(s), each pass reads data not in L2",
                    "parallelism": f"rows x{world}" if world > 1 else "1 gpu",
                    "launch": "eager, current stream"},
-        "e2e": {"value": round(e2e_value, 2), "unit": unit, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_step_ms, 4), "steps": e2e_steps},
+        "e2e": e2e,
         "gpu_launches": launches,
         "roofline": roofline,
         "clocks": clocks.summary(),
@@ -587,6 +662,7 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="layernorm")
     ap.add_argument("--no-per-op", action="store_true", help="skip the per-operator table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -30,14 +30,10 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
   float* colbuf = smem + groups * (2 * NV * (G / 32));
   int phase = 0;
 
-  uint4 wv[VPT];
   float acc_w[VPT][N];
   float acc_b[LN ? VPT : 1][N];
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
-    const int idx = lig + k * G;
-    wv[k] = make_uint4(0, 0, 0, 0);
-    if (idx < nvec) wv[k] = *reinterpret_cast<const uint4*>(w + (size_t)idx * N);
 #pragma unroll
     for (int j = 0; j < N; ++j) {
       acc_w[k][j] = 0.f;
@@ -45,20 +41,33 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
     }
   }
   const float inv_cols = 1.0f / (float)cols;
+  const int64_t stride = (int64_t)gridDim.x * groups;
 
-  for (int64_t row = (int64_t)blockIdx.x * groups + gid; row < rows;
-       row += (int64_t)gridDim.x * groups) {
-    const T* xr = x + row * cols;
-    const T* gr = dy + row * cols;
-    uint4 xv[VPT], gv[VPT];
+  // Software pipeline: the loads of the next row are issued before the current
+  // row is reduced, so x/dy requests stay in flight through the whole loop body.
+  int64_t row = (int64_t)blockIdx.x * groups + gid;
+  uint4 xv[VPT], gv[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int idx = lig + k * G;
+    xv[k] = make_uint4(0, 0, 0, 0);
+    gv[k] = make_uint4(0, 0, 0, 0);
+    if (row < rows && idx < nvec) {
+      xv[k] = ld_vec(x + row * cols + (size_t)idx * N);
+      gv[k] = ld_vec(dy + row * cols + (size_t)idx * N);
+    }
+  }
+  while (row < rows) {
+    const int64_t nrow = row + stride;
+    uint4 xn[VPT], gn[VPT];
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int idx = lig + k * G;
-      xv[k] = make_uint4(0, 0, 0, 0);
-      gv[k] = make_uint4(0, 0, 0, 0);
-      if (idx < nvec) {
-        xv[k] = ld_vec(xr + (size_t)idx * N);
-        gv[k] = ld_vec(gr + (size_t)idx * N);
+      xn[k] = make_uint4(0, 0, 0, 0);
+      gn[k] = make_uint4(0, 0, 0, 0);
+      if (nrow < rows && idx < nvec) {
+        xn[k] = ld_vec(x + nrow * cols + (size_t)idx * N);
+        gn[k] = ld_vec(dy + nrow * cols + (size_t)idx * N);
       }
     }
     const float rs = rstd[row];
@@ -76,7 +85,7 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
         float xf[N], gf[N], wf[N];
         unpack<T>(xv[k], xf);
         unpack<T>(gv[k], gf);
-        unpack<T>(wv[k], wf);
+        unpack<T>(__ldg(reinterpret_cast<const uint4*>(w + (size_t)idx * N)), wf);
 #pragma unroll
         for (int j = 0; j < N; ++j) {
           const float xh = (xf[j] - mu) * rs;
@@ -99,7 +108,7 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
         float xf[N], gf[N], wf[N], o[N];
         unpack<T>(xv[k], xf);
         unpack<T>(gv[k], gf);
-        unpack<T>(wv[k], wf);
+        unpack<T>(__ldg(reinterpret_cast<const uint4*>(w + (size_t)idx * N)), wf);
 #pragma unroll
         for (int j = 0; j < N; ++j) {
           const float xh = (xf[j] - mu) * rs;
@@ -111,6 +120,12 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
         st_vec(dr + (size_t)idx * N, pack<T>(o));
       }
     }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      xv[k] = xn[k];
+      gv[k] = gn[k];
+    }
+    row = nrow;
   }
 
   // Fold the groups of this block in group order, then write one partial row.

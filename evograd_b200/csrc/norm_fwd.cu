@@ -12,7 +12,7 @@ namespace {
 //             of layernorm_forward_ref, ops/level1/layernorm/forward_ref.py:20-23)
 // LN = false: y = (x*rstd)*w          (rmsnorm_forward_ref, .../rmsnorm/forward_ref.py:19-21)
 template <typename T, int G, int VPT, bool LN>
-__global__ void __launch_bounds__(rowcfg_max_threads(G))
+__global__ void __launch_bounds__(rowcfg_max_threads(G), G > 512 ? 1 : 2)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
                 T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                 int64_t rows, int cols, float eps) {
@@ -24,29 +24,28 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __res
   const int nvec = cols / N;
   float* scratch = smem + gid * (2 * (G / 32));
   int phase = 0;
+  const float inv_cols = 1.0f / (float)cols;
+  const int64_t stride = (int64_t)gridDim.x * groups;
 
-  uint4 wv[VPT], bv[VPT];
+  // The next row is requested before the current one is reduced, so loads stay
+  // in flight during the reduction and store phases. weight/bias are re-read
+  // through L1 where they are used instead of being pinned in registers.
+  int64_t row = (int64_t)blockIdx.x * groups + gid;
+  uint4 xv[VPT];
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int idx = lig + k * G;
-    wv[k] = make_uint4(0, 0, 0, 0);
-    bv[k] = make_uint4(0, 0, 0, 0);
-    if (idx < nvec) {
-      wv[k] = *reinterpret_cast<const uint4*>(w + (size_t)idx * N);
-      if constexpr (LN) bv[k] = *reinterpret_cast<const uint4*>(b + (size_t)idx * N);
-    }
+    xv[k] = make_uint4(0, 0, 0, 0);
+    if (row < rows && idx < nvec) xv[k] = ld_vec(x + row * cols + (size_t)idx * N);
   }
-  const float inv_cols = 1.0f / (float)cols;
-
-  for (int64_t row = (int64_t)blockIdx.x * groups + gid; row < rows;
-       row += (int64_t)gridDim.x * groups) {
-    const T* xr = x + row * cols;
-    uint4 xv[VPT];
+  while (row < rows) {
+    const int64_t nrow = row + stride;
+    uint4 xn[VPT];
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int idx = lig + k * G;
-      xv[k] = make_uint4(0, 0, 0, 0);
-      if (idx < nvec) xv[k] = ld_vec(xr + (size_t)idx * N);
+      xn[k] = make_uint4(0, 0, 0, 0);
+      if (nrow < rows && idx < nvec) xn[k] = ld_vec(x + nrow * cols + (size_t)idx * N);
     }
     float mu = 0.f;
     if constexpr (LN) {
@@ -88,10 +87,10 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __res
       if (idx < nvec) {
         float f[N], wf[N], o[N];
         unpack<T>(xv[k], f);
-        unpack<T>(wv[k], wf);
+        unpack<T>(__ldg(reinterpret_cast<const uint4*>(w + (size_t)idx * N)), wf);
         if constexpr (LN) {
           float bf[N];
-          unpack<T>(bv[k], bf);
+          unpack<T>(__ldg(reinterpret_cast<const uint4*>(b + (size_t)idx * N)), bf);
 #pragma unroll
           for (int j = 0; j < N; ++j)
             o[j] = __fadd_rn(__fmul_rn(__fmul_rn(f[j] - mu, rs), wf[j]), bf[j]);
@@ -102,6 +101,9 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __res
         st_vec(yr + (size_t)idx * N, pack<T>(o));
       }
     }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) xv[k] = xn[k];
+    row = nrow;
   }
 }
 

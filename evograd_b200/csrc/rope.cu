@@ -65,6 +65,7 @@ template <typename T, typename TT>
 __global__ void __launch_bounds__(kThreads)
 rope_vec_kernel(const RopeArgs args) {
   constexpr int N = Vec<T>::N;
+  constexpr int U = 2;  // independent work items in flight per thread
   const RopeTensor& tz = args.t[blockIdx.y];
   const int half = args.head_dim / 2;
   const int hv = half / N;  // vectors per half row
@@ -76,38 +77,56 @@ rope_vec_kernel(const RopeArgs args) {
   // Walk the faster-varying of (head, token) first so neighbouring threads
   // touch neighbouring memory whichever layout the caller uses.
   const bool head_inner = tz.xs_h < tz.xs_t;
-  for (int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; item < tz.items;
-       item += (int64_t)gridDim.x * blockDim.x) {
-    const int i = (int)(item % hv);
-    int64_t r = item / hv;
-    int64_t h, t;
-    if (head_inner) { h = r % tz.heads; r /= tz.heads; t = r % args.tokens; r /= args.tokens; }
-    else { t = r % args.tokens; r /= args.tokens; h = r % tz.heads; r /= tz.heads; }
-    const int64_t b = r;
-    const T* xr = x + b * tz.xs_b + h * tz.xs_h + t * tz.xs_t + i * N;
-    const uint4 v1 = ld_vec(xr);
-    const uint4 v2 = ld_vec(xr + half);
-    float c1[N], s1[N], c2[N], s2[N];
-    const TT* crow = ct + t * args.table_cols + i * N;
-    const TT* srow = st + t * args.table_cols + i * N;
-    load_table<TT, N>(crow, c1);
-    load_table<TT, N>(srow, s1);
-    if (full) {
-      load_table<TT, N>(crow + half, c2);
-      load_table<TT, N>(srow + half, s2);
-    } else {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < tz.items;
+       base += stride * U) {
+    uint4 v1[U], v2[U];
+    int64_t yoff[U], trow[U];
+    int iv[U];
 #pragma unroll
-      for (int j = 0; j < N; ++j) { c2[j] = c1[j]; s2[j] = s1[j]; }
+    for (int u = 0; u < U; ++u) {
+      const int64_t item = base + u * stride;
+      if (item < tz.items) {
+        const int i = (int)(item % hv);
+        int64_t r = item / hv;
+        int64_t h, t;
+        if (head_inner) { h = r % tz.heads; r /= tz.heads; t = r % args.tokens; r /= args.tokens; }
+        else { t = r % args.tokens; r /= args.tokens; h = r % tz.heads; r /= tz.heads; }
+        const int64_t b = r;
+        const T* xr = x + b * tz.xs_b + h * tz.xs_h + t * tz.xs_t + i * N;
+        v1[u] = ld_vec(xr);
+        v2[u] = ld_vec(xr + half);
+        yoff[u] = b * tz.ys_b + h * tz.ys_h + t * tz.ys_t + i * N;
+        trow[u] = t * args.table_cols + i * N;
+        iv[u] = i;
+      }
     }
-    float x1[N], x2[N], o1[N], o2[N];
-    unpack<T>(v1, x1);
-    unpack<T>(v2, x2);
 #pragma unroll
-    for (int j = 0; j < N; ++j)
-      rotate(x1[j], x2[j], c1[j], s1[j], c2[j], s2[j], args.inverse != 0, o1[j], o2[j]);
-    T* yr = y + b * tz.ys_b + h * tz.ys_h + t * tz.ys_t + i * N;
-    st_vec(yr, pack<T>(o1));
-    st_vec(yr + half, pack<T>(o2));
+    for (int u = 0; u < U; ++u) {
+      const int64_t item = base + u * stride;
+      if (item < tz.items) {
+        float c1[N], s1[N], c2[N], s2[N];
+        load_table<TT, N>(ct + trow[u], c1);
+        load_table<TT, N>(st + trow[u], s1);
+        if (full) {
+          load_table<TT, N>(ct + trow[u] + half, c2);
+          load_table<TT, N>(st + trow[u] + half, s2);
+        } else {
+#pragma unroll
+          for (int j = 0; j < N; ++j) { c2[j] = c1[j]; s2[j] = s1[j]; }
+        }
+        float x1[N], x2[N], o1[N], o2[N];
+        unpack<T>(v1[u], x1);
+        unpack<T>(v2[u], x2);
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+          rotate(x1[j], x2[j], c1[j], s1[j], c2[j], s2[j], args.inverse != 0, o1[j], o2[j]);
+        T* yr = y + yoff[u];
+        st_vec(yr, pack<T>(o1));
+        st_vec(yr + half, pack<T>(o2));
+      }
+    }
+    (void)iv;
   }
 }
 
@@ -161,8 +180,8 @@ int launch_rope(RopeArgs& args, cudaStream_t stream) {
   }
   if (max_items == 0) return EVG_OK;
   int per_sm = tune("rope.blocks_per_sm");
-  if (per_sm <= 0) per_sm = 8;
-  int64_t blocks = (max_items + kThreads - 1) / kThreads;
+  if (per_sm <= 0) per_sm = 16;
+  int64_t blocks = (max_items + 2 * kThreads - 1) / (2 * kThreads);
   const int64_t cap = (int64_t)device_info().sm_count * per_sm;
   if (blocks > cap) blocks = cap;
   dim3 grid((unsigned)blocks, (unsigned)args.count);

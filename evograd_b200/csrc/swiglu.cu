@@ -6,7 +6,8 @@
 namespace evg {
 namespace {
 
-constexpr int kUnroll = 2;
+constexpr int kUnrollFwd = 4;  // two input streams
+constexpr int kUnrollBwd = 2;  // three input streams
 constexpr int kThreads = 256;
 
 __device__ __forceinline__ float sigmoid_f32(float a) { return 1.0f / (1.0f + __expf(-a)); }
@@ -39,10 +40,10 @@ swiglu_fwd_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restric
   constexpr int N = Vec<T>::N;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec;
-       base += stride * kUnroll) {
-    uint4 av[kUnroll], bv[kUnroll];
+       base += stride * kUnrollFwd) {
+    uint4 av[kUnrollFwd], bv[kUnrollFwd];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kUnrollFwd; ++u) {
       const int64_t v = base + u * stride;
       if (v < nvec) {
         av[u] = ld_vec(a + v * N);
@@ -50,7 +51,7 @@ swiglu_fwd_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restric
       }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kUnrollFwd; ++u) {
       const int64_t v = base + u * stride;
       if (v < nvec) {
         float af[N], bf[N], o[N];
@@ -70,10 +71,10 @@ swiglu_bwd_kernel(const T* dc, const T* a, const T* b, T* da, T* db, int64_t nve
   constexpr int N = Vec<T>::N;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec;
-       base += stride * kUnroll) {
-    uint4 cv[kUnroll], av[kUnroll], bv[kUnroll];
+       base += stride * kUnrollBwd) {
+    uint4 cv[kUnrollBwd], av[kUnrollBwd], bv[kUnrollBwd];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kUnrollBwd; ++u) {
       const int64_t v = base + u * stride;
       if (v < nvec) {
         cv[u] = ld_vec(dc + v * N);
@@ -84,7 +85,7 @@ swiglu_bwd_kernel(const T* dc, const T* a, const T* b, T* da, T* db, int64_t nve
       }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kUnrollBwd; ++u) {
       const int64_t v = base + u * stride;
       if (v < nvec) {
         float cf[N], af[N], bf[N], oa[N], ob[N];
@@ -140,11 +141,11 @@ extern "C" int evg_swiglu_fwd(const void* a, const void* b, void* c, int64_t n, 
     constexpr int N = Vec<T>::N;
     cudaStream_t st = (cudaStream_t)stream;
     int per_sm = tune("swiglu.blocks_per_sm");
-    if (per_sm <= 0) per_sm = 8;
+    if (per_sm <= 0) per_sm = 32;
     const bool vec_ok = aligned16(a) && aligned16(b) && aligned16(c);
     const int64_t nvec = vec_ok ? n / N : 0;
     if (nvec > 0) {
-      swiglu_fwd_kernel<T><<<flat_grid((nvec + kUnroll - 1) / kUnroll, per_sm), kThreads, 0, st>>>(
+      swiglu_fwd_kernel<T><<<flat_grid((nvec + kUnrollFwd - 1) / kUnrollFwd, per_sm), kThreads, 0, st>>>(
           (const T*)a, (const T*)b, (T*)c, nvec);
     }
     if (nvec * N < n) {
@@ -164,11 +165,11 @@ extern "C" int evg_swiglu_bwd(const void* dc, const void* a, const void* b, void
     constexpr int N = Vec<T>::N;
     cudaStream_t st = (cudaStream_t)stream;
     int per_sm = tune("swiglu.blocks_per_sm");
-    if (per_sm <= 0) per_sm = 8;
+    if (per_sm <= 0) per_sm = 32;
     const bool vec_ok = aligned16(dc) && aligned16(a) && aligned16(b) && aligned16(da) && aligned16(db);
     const int64_t nvec = vec_ok ? n / N : 0;
     if (nvec > 0) {
-      swiglu_bwd_kernel<T><<<flat_grid((nvec + kUnroll - 1) / kUnroll, per_sm), kThreads, 0, st>>>(
+      swiglu_bwd_kernel<T><<<flat_grid((nvec + kUnrollBwd - 1) / kUnrollBwd, per_sm), kThreads, 0, st>>>(
           (const T*)dc, (const T*)a, (const T*)b, (T*)da, (T*)db, nvec);
     }
     if (nvec * N < n) {
