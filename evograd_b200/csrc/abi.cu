@@ -26,7 +26,7 @@ const char* const kTuneKeys[] = {
     "layernorm_fwd.threads",    "layernorm_bwd.group",    "layernorm_bwd.vpt",
     "layernorm_bwd.threads",    "rmsnorm_fwd.group",      "rmsnorm_fwd.vpt",
     "rmsnorm_fwd.threads",      "rmsnorm_bwd.group",      "rmsnorm_bwd.vpt",
-    "rmsnorm_bwd.threads",      "attention.variant",      "attention.wait_limit",
+    "rmsnorm_bwd.threads",      "attention.variant",      "rope.generic",      "attention.wait_limit",
 };
 }  // namespace
 

@@ -13,22 +13,37 @@ namespace {
 
 // Workspace layout (float32): [NP][blocks][cols], NP = 2 (dweight, dbias) for
 // LayerNorm and 1 (dweight) for RMSNorm.
+// Like the forward, this kernel is limited by instruction issue rather than HBM
+// on B200: x-hat and dy are unpacked to float32 registers once per row, weight
+// is staged in shared memory as float32 ([q * nvec + idx] float4 layout, read
+// conflict-free), and every per-element step is a single fused multiply-add.
 template <typename T, int G, int VPT, bool LN>
 __global__ void __launch_bounds__(rowcfg_max_threads(G))
 norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                 const float* __restrict__ mean, const float* __restrict__ rstd,
                 T* __restrict__ dx, float* __restrict__ partial, int64_t rows, int cols) {
   constexpr int N = Vec<T>::N;
+  constexpr int Q = N / 4;
   constexpr int NV = LN ? 2 : 1;
-  extern __shared__ float smem[];
+  extern __shared__ float4 smem4[];
   const int gid = threadIdx.x / G;
   const int lig = threadIdx.x % G;
   const int groups = blockDim.x / G;
   const int nvec = cols / N;
-  // smem: [groups][2][NV][G/32] reduction scratch, then [NV][cols] column buffer
-  float* scratch = smem + gid * (2 * NV * (G / 32));
-  float* colbuf = smem + groups * (2 * NV * (G / 32));
+  // smem: weight as float32 [Q][nvec] float4; then the [NV][cols] column
+  // buffer; then [groups][2][NV][G/32] reduction scratch.
+  float4* w4 = smem4;
+  float* colbuf = reinterpret_cast<float*>(smem4 + (size_t)Q * nvec);
+  float* scratch = colbuf + (size_t)NV * cols + gid * (2 * NV * (G / 32));
   int phase = 0;
+  for (int idx = threadIdx.x; idx < nvec; idx += blockDim.x) {
+    float f[N];
+    unpack<T>(*reinterpret_cast<const uint4*>(w + (size_t)idx * N), f);
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+      w4[q * nvec + idx] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+  }
+  __syncthreads();
 
   float acc_w[VPT][N];
   float acc_b[LN ? VPT : 1][N];
@@ -41,91 +56,80 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
     }
   }
   const float inv_cols = 1.0f / (float)cols;
-  const int64_t stride = (int64_t)gridDim.x * groups;
 
-  // Software pipeline: the loads of the next row are issued before the current
-  // row is reduced, so x/dy requests stay in flight through the whole loop body.
-  int64_t row = (int64_t)blockIdx.x * groups + gid;
-  uint4 xv[VPT], gv[VPT];
-#pragma unroll
-  for (int k = 0; k < VPT; ++k) {
-    const int idx = lig + k * G;
-    xv[k] = make_uint4(0, 0, 0, 0);
-    gv[k] = make_uint4(0, 0, 0, 0);
-    if (row < rows && idx < nvec) {
-      xv[k] = ld_vec(x + row * cols + (size_t)idx * N);
-      gv[k] = ld_vec(dy + row * cols + (size_t)idx * N);
-    }
-  }
-  while (row < rows) {
-    const int64_t nrow = row + stride;
-    uint4 xn[VPT], gn[VPT];
+  for (int64_t row = (int64_t)blockIdx.x * groups + gid; row < rows;
+       row += (int64_t)gridDim.x * groups) {
+    const T* xr = x + row * cols;
+    const T* gr = dy + row * cols;
+    uint4 xv[VPT], gv[VPT];
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int idx = lig + k * G;
-      xn[k] = make_uint4(0, 0, 0, 0);
-      gn[k] = make_uint4(0, 0, 0, 0);
-      if (nrow < rows && idx < nvec) {
-        xn[k] = ld_vec(x + nrow * cols + (size_t)idx * N);
-        gn[k] = ld_vec(dy + nrow * cols + (size_t)idx * N);
+      xv[k] = make_uint4(0, 0, 0, 0);
+      gv[k] = make_uint4(0, 0, 0, 0);
+      if (idx < nvec) {
+        xv[k] = ld_vec(xr + (size_t)idx * N);
+        gv[k] = ld_vec(gr + (size_t)idx * N);
       }
     }
     const float rs = rstd[row];
-    float mu = 0.f;
-    if constexpr (LN) mu = mean[row];
+    float nmr = 0.f;
+    if constexpr (LN) nmr = -mean[row] * rs;
 
-    // c[0] = sum g*xhat, c[1] = sum g  (g = dy*w; padded vectors contribute 0)
+    // xh = (x - mean) * rstd, gy = dy; c[0] = sum g*xh, c[1] = sum g with g = dy*w.
+    // Padded vectors have dy = 0, so they add nothing to any sum.
+    float xh[VPT][N], gy[VPT][N];
     float c[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) c[i] = 0.f;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int idx = lig + k * G;
-      if (idx < nvec) {
-        float xf[N], gf[N], wf[N];
-        unpack<T>(xv[k], xf);
-        unpack<T>(gv[k], gf);
-        unpack<T>(__ldg(reinterpret_cast<const uint4*>(w + (size_t)idx * N)), wf);
+      unpack<T>(xv[k], xh[k]);
+      unpack<T>(gv[k], gy[k]);
+      const int sidx = idx < nvec ? idx : 0;
 #pragma unroll
-        for (int j = 0; j < N; ++j) {
-          const float xh = (xf[j] - mu) * rs;
-          const float g = gf[j] * wf[j];
-          c[0] += g * xh;
+      for (int qq = 0; qq < Q; ++qq) {
+        const float4 wv = w4[qq * nvec + sidx];
+        const float wj[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int e = 4 * qq + j;
+          xh[k][e] = LN ? fmaf(xh[k][e], rs, nmr) : xh[k][e] * rs;
+          const float g = gy[k][e] * wj[j];
+          c[0] = fmaf(g, xh[k][e], c[0]);
           if constexpr (LN) c[1] += g;
         }
       }
     }
     group_allreduce<G, NV, SumOp>(c, scratch, phase, gid, lig);
-    const float m_gx = c[0] * inv_cols;
-    float m_g = 0.f;
-    if constexpr (LN) m_g = c[1] * inv_cols;
+    // dx = rs*g - rs*mean(g) - rs*mean(g*xh)*xh
+    const float a_x = -rs * (c[0] * inv_cols);
+    float a_0 = 0.f;
+    if constexpr (LN) a_0 = -rs * (c[1] * inv_cols);
 
     T* dr = dx + row * cols;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int idx = lig + k * G;
       if (idx < nvec) {
-        float xf[N], gf[N], wf[N], o[N];
-        unpack<T>(xv[k], xf);
-        unpack<T>(gv[k], gf);
-        unpack<T>(__ldg(reinterpret_cast<const uint4*>(w + (size_t)idx * N)), wf);
+        float o[N];
 #pragma unroll
-        for (int j = 0; j < N; ++j) {
-          const float xh = (xf[j] - mu) * rs;
-          const float g = gf[j] * wf[j];
-          o[j] = (g - m_g - xh * m_gx) * rs;
-          acc_w[k][j] += gf[j] * xh;
-          if constexpr (LN) acc_b[k][j] += gf[j];
+        for (int qq = 0; qq < Q; ++qq) {
+          const float4 wv = w4[qq * nvec + idx];
+          const float wj[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int e = 4 * qq + j;
+            const float g = gy[k][e] * wj[j];
+            o[e] = fmaf(xh[k][e], a_x, fmaf(g, rs, a_0));
+            acc_w[k][e] = fmaf(gy[k][e], xh[k][e], acc_w[k][e]);
+            if constexpr (LN) acc_b[k][e] += gy[k][e];
+          }
         }
         st_vec(dr + (size_t)idx * N, pack<T>(o));
       }
     }
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-      xv[k] = xn[k];
-      gv[k] = gn[k];
-    }
-    row = nrow;
   }
 
   // Fold the groups of this block in group order, then write one partial row.
@@ -279,7 +283,7 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
   if (vec_ok && !tune("rows.force_generic") && pick_rowcfg(op, hidden / N, cfg, 512, LN)) {
     const int groups = cfg.threads / cfg.G;
     const size_t smem =
-        ((size_t)groups * 2 * NV * (cfg.G / 32) + (size_t)NV * hidden) * sizeof(float);
+        ((size_t)groups * 2 * NV * (cfg.G / 32) + (size_t)(NV + 1) * hidden) * sizeof(float);
     if (smem <= (size_t)device_info().max_smem_optin) {
 #define EVG_X(g, v)                                                                            \
   if (!launched && cfg.G == g && cfg.VPT == v) {                                               \

@@ -11,71 +11,79 @@ namespace {
 // LN = true : y = ((x-mean)*rstd)*w + b, two-pass variance (the rounding points
 //             of layernorm_forward_ref, ops/level1/layernorm/forward_ref.py:20-23)
 // LN = false: y = (x*rstd)*w          (rmsnorm_forward_ref, .../rmsnorm/forward_ref.py:19-21)
+// On B200 these kernels are bounded by instruction issue before HBM (about 22
+// thread-instructions per element are available at full bandwidth), so the row
+// is unpacked to float32 registers ONCE and weight/bias are staged in shared
+// memory as float32, laid out so that consecutive threads read consecutive
+// float4 (slot q of vector idx lives at [q * nvec + idx]).
 template <typename T, int G, int VPT, bool LN>
 __global__ void __launch_bounds__(rowcfg_max_threads(G), G > 512 ? 1 : 2)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
                 T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                 int64_t rows, int cols, float eps) {
   constexpr int N = Vec<T>::N;
-  extern __shared__ float smem[];
+  constexpr int Q = N / 4;  // float4 slots per 128-bit input vector
+  extern __shared__ float4 smem4[];
   const int gid = threadIdx.x / G;
   const int lig = threadIdx.x % G;
   const int groups = blockDim.x / G;
   const int nvec = cols / N;
-  float* scratch = smem + gid * (2 * (G / 32));
+  float4* w4 = smem4;                              // [Q][nvec]
+  float4* b4 = smem4 + (size_t)Q * nvec;           // [Q][nvec] (LayerNorm only)
+  float* scratch = reinterpret_cast<float*>(smem4 + (size_t)(LN ? 2 : 1) * Q * nvec) +
+                   gid * (2 * (G / 32));
   int phase = 0;
-  const float inv_cols = 1.0f / (float)cols;
-  const int64_t stride = (int64_t)gridDim.x * groups;
-
-  // The next row is requested before the current one is reduced, so loads stay
-  // in flight during the reduction and store phases. weight/bias are re-read
-  // through L1 where they are used instead of being pinned in registers.
-  int64_t row = (int64_t)blockIdx.x * groups + gid;
-  uint4 xv[VPT];
+  for (int idx = threadIdx.x; idx < nvec; idx += blockDim.x) {
+    float f[N];
+    unpack<T>(*reinterpret_cast<const uint4*>(w + (size_t)idx * N), f);
 #pragma unroll
-  for (int k = 0; k < VPT; ++k) {
-    const int idx = lig + k * G;
-    xv[k] = make_uint4(0, 0, 0, 0);
-    if (row < rows && idx < nvec) xv[k] = ld_vec(x + row * cols + (size_t)idx * N);
+    for (int q = 0; q < Q; ++q)
+      w4[q * nvec + idx] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+    if constexpr (LN) {
+      unpack<T>(*reinterpret_cast<const uint4*>(b + (size_t)idx * N), f);
+#pragma unroll
+      for (int q = 0; q < Q; ++q)
+        b4[q * nvec + idx] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+    }
   }
-  while (row < rows) {
-    const int64_t nrow = row + stride;
-    uint4 xn[VPT];
+  __syncthreads();
+  const float inv_cols = 1.0f / (float)cols;
+
+  for (int64_t row = (int64_t)blockIdx.x * groups + gid; row < rows;
+       row += (int64_t)gridDim.x * groups) {
+    const T* xr = x + row * cols;
+    float xf[VPT][N];
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int idx = lig + k * G;
-      xn[k] = make_uint4(0, 0, 0, 0);
-      if (nrow < rows && idx < nvec) xn[k] = ld_vec(x + nrow * cols + (size_t)idx * N);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (idx < nvec) v = ld_vec(xr + (size_t)idx * N);
+      unpack<T>(v, xf[k]);  // padded vectors unpack to zeros
     }
     float mu = 0.f;
     if constexpr (LN) {
       float s[1] = {0.f};
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        float f[N];
-        unpack<T>(xv[k], f);
+      for (int k = 0; k < VPT; ++k)
 #pragma unroll
-        for (int j = 0; j < N; ++j) s[0] += f[j];  // padded vectors are zero
-      }
+        for (int j = 0; j < N; ++j) s[0] += xf[k][j];
       group_allreduce<G, 1, SumOp>(s, scratch, phase, gid, lig);
       mu = s[0] * inv_cols;
     }
     float q[1] = {0.f};
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
-      const int idx = lig + k * G;
-      if (idx < nvec) {
-        float f[N];
-        unpack<T>(xv[k], f);
+      if (lig + k * G < nvec) {
 #pragma unroll
         for (int j = 0; j < N; ++j) {
-          const float d = f[j] - mu;
-          q[0] += d * d;
+          const float d = xf[k][j] - mu;
+          q[0] = fmaf(d, d, q[0]);
         }
       }
     }
     group_allreduce<G, 1, SumOp>(q, scratch, phase, gid, lig);
     const float rs = 1.0f / sqrtf(q[0] * inv_cols + eps);
+    const float nmr = -mu * rs;
     if (lig == 0) {
       rstd_out[row] = rs;
       if constexpr (LN) mean_out[row] = mu;
@@ -85,25 +93,25 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __res
     for (int k = 0; k < VPT; ++k) {
       const int idx = lig + k * G;
       if (idx < nvec) {
-        float f[N], wf[N], o[N];
-        unpack<T>(xv[k], f);
-        unpack<T>(__ldg(reinterpret_cast<const uint4*>(w + (size_t)idx * N)), wf);
-        if constexpr (LN) {
-          float bf[N];
-          unpack<T>(__ldg(reinterpret_cast<const uint4*>(b + (size_t)idx * N)), bf);
+        float o[N];
 #pragma unroll
-          for (int j = 0; j < N; ++j)
-            o[j] = __fadd_rn(__fmul_rn(__fmul_rn(f[j] - mu, rs), wf[j]), bf[j]);
-        } else {
+        for (int qq = 0; qq < Q; ++qq) {
+          const float4 wv = w4[qq * nvec + idx];
+          const float wj[4] = {wv.x, wv.y, wv.z, wv.w};
+          if constexpr (LN) {
+            const float4 bv = b4[qq * nvec + idx];
+            const float bj[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
-          for (int j = 0; j < N; ++j) o[j] = __fmul_rn(__fmul_rn(f[j], rs), wf[j]);
+            for (int j = 0; j < 4; ++j)
+              o[4 * qq + j] = fmaf(fmaf(xf[k][4 * qq + j], rs, nmr), wj[j], bj[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[4 * qq + j] = (xf[k][4 * qq + j] * rs) * wj[j];
+          }
         }
         st_vec(yr + (size_t)idx * N, pack<T>(o));
       }
     }
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) xv[k] = xn[k];
-    row = nrow;
   }
 }
 
@@ -158,10 +166,13 @@ int launch_norm_fwd(const void* x, const void* w, const void* b, void* y, float*
   RowCfg cfg;
   if (vec_ok && !tune("rows.force_generic") && pick_rowcfg(op, hidden / N, cfg)) {
     const int groups = cfg.threads / cfg.G;
-    const size_t smem = (size_t)groups * 2 * (cfg.G / 32 > 0 ? cfg.G / 32 : 1) * sizeof(float);
+    const size_t smem = (size_t)(LN ? 2 : 1) * hidden * sizeof(float) +
+                        (size_t)groups * 2 * (cfg.G / 32) * sizeof(float);
 #define EVG_X(g, v)                                                                           \
-  if (cfg.G == g && cfg.VPT == v) {                                                           \
+  if (cfg.G == g && cfg.VPT == v && smem <= (size_t)device_info().max_smem_optin) {           \
     auto kern = norm_fwd_kernel<T, g, v, LN>;                                                 \
+    if (smem > 48 * 1024)                                                                     \
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
     const int grid = persistent_grid(kern, cfg.threads, smem, rows, groups);                  \
     kern<<<grid, cfg.threads, smem, stream>>>((const T*)x, (const T*)w, (const T*)b, (T*)y,   \
                                               mean, rstd, rows, (int)hidden, eps);            \

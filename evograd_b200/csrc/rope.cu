@@ -130,6 +130,74 @@ rope_vec_kernel(const RopeArgs args) {
   }
 }
 
+// Fast path when a half row is a power-of-two number of vectors: a thread owns
+// one (token, vector) position, loads its cos/sin values ONCE and then walks
+// over (batch, head) pairs, so the table traffic and its unpacking are amortised
+// over every pair the thread visits and no per-element index division is left.
+// grid = (token tiles, chunks of (batch, head) pairs, tensors).
+template <typename T, typename TT>
+__global__ void __launch_bounds__(kThreads)
+rope_tile_kernel(const RopeArgs args, int hv_log2, int pairs_per_chunk) {
+  constexpr int N = Vec<T>::N;
+  constexpr int U = 4;  // (batch, head) pairs in flight per thread
+  const RopeTensor& tz = args.t[blockIdx.z];
+  const int half = args.head_dim / 2;
+  const int hv = 1 << hv_log2;
+  const int i = threadIdx.x & (hv - 1);
+  const int64_t t = (int64_t)blockIdx.x * (kThreads >> hv_log2) + (threadIdx.x >> hv_log2);
+  if (t >= args.tokens) return;
+  const int64_t pairs = args.batch * tz.heads;
+  int64_t n = (int64_t)blockIdx.y * pairs_per_chunk;
+  const int64_t n_end = min(n + (int64_t)pairs_per_chunk, pairs);
+  if (n >= n_end) return;
+
+  float c1[N], s1[N], c2[N], s2[N];
+  {
+    const TT* crow = (const TT*)args.cos + t * args.table_cols + i * N;
+    const TT* srow = (const TT*)args.sin + t * args.table_cols + i * N;
+    load_table<TT, N>(crow, c1);
+    load_table<TT, N>(srow, s1);
+    if (args.table_cols == args.head_dim) {
+      load_table<TT, N>(crow + half, c2);
+      load_table<TT, N>(srow + half, s2);
+    } else {
+#pragma unroll
+      for (int j = 0; j < N; ++j) { c2[j] = c1[j]; s2[j] = s1[j]; }
+    }
+  }
+  const T* x = (const T*)tz.x + t * tz.xs_t + i * N;
+  T* y = (T*)tz.y + t * tz.ys_t + i * N;
+  const bool inverse = args.inverse != 0;
+  int64_t b = n / tz.heads, h = n % tz.heads;
+  for (; n < n_end; n += U) {
+    uint4 v1[U], v2[U];
+    int64_t yo[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (n + u < n_end) {
+        const T* xr = x + b * tz.xs_b + h * tz.xs_h;
+        v1[u] = ld_vec(xr);
+        v2[u] = ld_vec(xr + half);
+        yo[u] = b * tz.ys_b + h * tz.ys_h;
+        if (++h == tz.heads) { h = 0; ++b; }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (n + u < n_end) {
+        float x1[N], x2[N], o1[N], o2[N];
+        unpack<T>(v1[u], x1);
+        unpack<T>(v2[u], x2);
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+          rotate(x1[j], x2[j], c1[j], s1[j], c2[j], s2[j], inverse, o1[j], o2[j]);
+        st_vec(y + yo[u], pack<T>(o1));
+        st_vec(y + yo[u] + half, pack<T>(o2));
+      }
+    }
+  }
+}
+
 // Scalar path for head sizes or alignments the vector path does not cover.
 template <typename T, typename TT>
 __global__ void __launch_bounds__(kThreads)
@@ -172,6 +240,32 @@ int launch_rope(RopeArgs& args, cudaStream_t stream) {
     vec_ok = vec_ok && aligned16(t.x) && aligned16(t.y) && t.xs_b % N == 0 && t.xs_h % N == 0 &&
              t.xs_t % N == 0 && t.ys_b % N == 0 && t.ys_h % N == 0 && t.ys_t % N == 0;
   }
+  int per_sm = tune("rope.blocks_per_sm");
+  if (per_sm <= 0) per_sm = 16;
+  const int64_t cap = (int64_t)device_info().sm_count * per_sm;
+  const int hv = vec_ok ? half / N : 0;
+  if (vec_ok && hv >= 1 && hv <= 64 && (hv & (hv - 1)) == 0 && !tune("rope.generic")) {
+    int hv_log2 = 0;
+    while ((1 << hv_log2) < hv) ++hv_log2;
+    const int tokens_per_block = kThreads >> hv_log2;
+    const int64_t tiles = (args.tokens + tokens_per_block - 1) / tokens_per_block;
+    int64_t max_pairs = 0;
+    for (int i = 0; i < args.count; ++i)
+      max_pairs = args.batch * args.t[i].heads > max_pairs ? args.batch * args.t[i].heads : max_pairs;
+    if (tiles == 0 || max_pairs == 0) return EVG_OK;
+    // enough chunks to fill the machine, but at least 4 pairs per thread
+    int64_t chunks = (cap + tiles * args.count - 1) / (tiles * args.count);
+    if (chunks > (max_pairs + 3) / 4) chunks = (max_pairs + 3) / 4;
+    if (chunks < 1) chunks = 1;
+    if (chunks > 65535) chunks = 65535;
+    const int pairs_per_chunk = (int)((max_pairs + chunks - 1) / chunks);
+    chunks = (max_pairs + pairs_per_chunk - 1) / pairs_per_chunk;
+    if (tiles <= 0x7fffffff) {
+      dim3 grid((unsigned)tiles, (unsigned)chunks, (unsigned)args.count);
+      rope_tile_kernel<T, TT><<<grid, kThreads, 0, stream>>>(args, hv_log2, pairs_per_chunk);
+      return check_launch("rope");
+    }
+  }
   const int unit = vec_ok ? N : 1;
   int64_t max_items = 0;
   for (int i = 0; i < args.count; ++i) {
@@ -179,10 +273,7 @@ int launch_rope(RopeArgs& args, cudaStream_t stream) {
     if (args.t[i].items > max_items) max_items = args.t[i].items;
   }
   if (max_items == 0) return EVG_OK;
-  int per_sm = tune("rope.blocks_per_sm");
-  if (per_sm <= 0) per_sm = 16;
   int64_t blocks = (max_items + 2 * kThreads - 1) / (2 * kThreads);
-  const int64_t cap = (int64_t)device_info().sm_count * per_sm;
   if (blocks > cap) blocks = cap;
   dim3 grid((unsigned)blocks, (unsigned)args.count);
   if (vec_ok) rope_vec_kernel<T, TT><<<grid, kThreads, 0, stream>>>(args);
