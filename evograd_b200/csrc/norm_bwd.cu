@@ -6,6 +6,8 @@
 //            registers and writes ONE partial row per block to the workspace;
 //   stage 2  a small kernel adds the partial rows in a fixed order and rounds.
 // The result is bit-reproducible from run to run for a given launch shape.
+#include <mutex>
+
 #include "rowcfg.cuh"
 
 namespace evg {
@@ -365,6 +367,79 @@ extern "C" int evg_rmsnorm_bwd(const void* dy, const void* x, const void* weight
   return EVG_DISPATCH_DTYPE(dtype, [&] {
     return launch_norm_bwd<T, false>(dy, x, weight, nullptr, rstd, dx, dweight, nullptr,
                                      dweight_f32, workspace, workspace_bytes, rows, hidden,
+                                     (cudaStream_t)stream);
+  });
+}
+
+// ------------------------------------------------------------------------
+// RMSNorm backward for callers that cannot obtain device memory.
+//
+// The partial-sum rows of the two-stage dweight reduction live in a fixed array
+// that is part of the library image, so this entry point performs no device
+// allocation of any kind. See the header for the limits and the sharing rules.
+namespace {
+
+constexpr int64_t kNoAllocMaxHidden = 8192;
+constexpr int64_t kNoAllocMaxBlocks = 320;
+constexpr int64_t kNoAllocFloats = kNoAllocMaxBlocks * kNoAllocMaxHidden;  // 10 MiB
+
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
+
+std::mutex g_noalloc_mutex;
+float* g_noalloc_ptr[64] = {};  // device address of the array, per device ordinal
+
+// In host code the array's name only stands for the symbol; the address a kernel
+// can use has to be asked for, once per device, with that device current.
+int noalloc_scratch_address(float** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return fail(EVG_ELAUNCH, "rmsnorm_bwd_noalloc: cannot identify the current device");
+  }
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (err != cudaSuccess || !p) {
+      cudaGetLastError();
+      return fail(EVG_ELAUNCH, "rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s",
+                  cudaGetErrorString(err));
+    }
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return EVG_OK;
+}
+
+}  // namespace
+
+extern "C" int evg_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* weight,
+                                       const float* rstd, void* dx, void* dweight,
+                                       float* dweight_f32, int64_t rows, int64_t hidden,
+                                       int dtype, void* stream) {
+  if (!dy || !x || !weight || !rstd || !dx)
+    return fail(EVG_ENULL, "rmsnorm_bwd_noalloc: null pointer argument");
+  if (rows <= 0 || hidden <= 0)
+    return fail(EVG_EBADSHAPE, "rmsnorm_bwd_noalloc: rows=%lld hidden=%lld (rows must be >= 1)",
+                (long long)rows, (long long)hidden);
+  if (hidden > kNoAllocMaxHidden)
+    return fail(EVG_EUNSUPPORTED,
+                "rmsnorm_bwd_noalloc: hidden=%lld exceeds the built-in scratch (max hidden %lld); "
+                "use evg_rmsnorm_bwd with a caller-provided workspace",
+                (long long)hidden, (long long)kNoAllocMaxHidden);
+  const int64_t need = norm_bwd_workspace<float, false>(rows, hidden);
+  const int64_t have = kNoAllocFloats * (int64_t)sizeof(float);
+  if (need > have)
+    return fail(EVG_EUNSUPPORTED,
+                "rmsnorm_bwd_noalloc: this launch shape needs %lld bytes of partial sums, the "
+                "built-in scratch holds %lld (at most %lld partial rows of %lld floats)",
+                (long long)need, (long long)have, (long long)kNoAllocMaxBlocks,
+                (long long)kNoAllocMaxHidden);
+  float* scratch = nullptr;
+  if (int rc = noalloc_scratch_address(&scratch)) return rc;
+  return EVG_DISPATCH_DTYPE(dtype, [&] {
+    return launch_norm_bwd<T, false>(dy, x, weight, nullptr, rstd, dx, dweight, nullptr,
+                                     dweight_f32, scratch, have, rows, hidden,
                                      (cudaStream_t)stream);
   });
 }

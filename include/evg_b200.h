@@ -128,6 +128,38 @@ int evg_rmsnorm_bwd(const void* dy, const void* x, const void* weight,
                     float* dweight_f32, void* workspace, int64_t workspace_bytes,
                     int64_t rows, int64_t hidden, int dtype, void* stream);
 
+/*
+ * RMSNorm backward without any allocation: same arguments and results as
+ * evg_rmsnorm_bwd minus the workspace. It has no counterpart in the reference.
+ *
+ * Who needs it: code that cannot get device memory at the moment it must run
+ * the backward - for instance a plug-in inside a host process that has already
+ * given every byte of GPU memory to its own pool and offers no allocator to its
+ * guests, or a step of a latency-bound loop where a cudaMalloc (which may
+ * synchronise the whole device) is not acceptable. Such a caller has the
+ * tensors it was handed and nothing else, so the float32 partial sums of the
+ * two-stage dweight reduction are kept in an array that is compiled into the
+ * library (10 MiB, resident on every GPU that loads the library until the
+ * process exits) instead of a caller-provided workspace. The call performs no
+ * cudaMalloc / cudaFree and calls no allocating library routine.
+ *
+ * Limits: hidden <= 8192 and at most 320 partial rows (the built-in launch
+ * shapes use 2 per SM, 296 on a B200); anything larger returns
+ * EVG_EUNSUPPORTED with a message and enqueues nothing.
+ * First call on a device: looks up the array's device address (once per
+ * device, under a lock, with that device current). Make that first call before
+ * starting any stream capture.
+ * Sharing: every call on a device uses the same array. Nothing in it has to
+ * start at zero - each launch overwrites the rows it later reads - so stale
+ * contents from an earlier call are harmless, but two of these calls whose
+ * kernels overlap on the GPU (different streams, no ordering between them)
+ * race on it. Calls on one stream are safe.
+ */
+int evg_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* weight,
+                            const float* rstd, void* dx, void* dweight,
+                            float* dweight_f32, int64_t rows, int64_t hidden,
+                            int dtype, void* stream);
+
 /* ------------------------------------------------------------------- swiglu
  * c = round(silu(float(a))) * b  with the product taken in dtype, exactly the
  * rounding points of swiglu_forward_ref, ops/level1/swiglu/forward_ref.py:6-9.
