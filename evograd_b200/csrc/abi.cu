@@ -26,7 +26,8 @@ const char* const kTuneKeys[] = {
     "layernorm_fwd.threads",    "layernorm_bwd.group",    "layernorm_bwd.vpt",
     "layernorm_bwd.threads",    "rmsnorm_fwd.group",      "rmsnorm_fwd.vpt",
     "rmsnorm_fwd.threads",      "rmsnorm_bwd.group",      "rmsnorm_bwd.vpt",
-    "rmsnorm_bwd.threads",      "attention.variant",      "rope.generic",      "attention.wait_limit",
+    "rmsnorm_bwd.threads",      "attention.variant",      "rope.generic",           "norm_bwd.no_ring",
+    "norm_bwd.stages",      "attention.wait_limit",
 };
 }  // namespace
 
@@ -43,6 +44,15 @@ int check_launch(const char* what) {
   if (err != cudaSuccess)
     return fail(EVG_ELAUNCH, "%s: %s (%s)", what, cudaGetErrorName(err), cudaGetErrorString(err));
   return EVG_OK;
+}
+
+namespace {
+StatusReader g_status_readers[16];
+int g_status_reader_count = 0;
+}  // namespace
+
+void register_device_status(StatusReader reader) {
+  if (g_status_reader_count < 16) g_status_readers[g_status_reader_count++] = reader;
 }
 
 int tune(const char* key) {
@@ -132,4 +142,20 @@ extern "C" int evg_flush_l2(void* buffer, int64_t bytes, void* stream) {
   flush_kernel<<<device_info().sm_count * 4, 512, 0, (cudaStream_t)stream>>>((uint4*)buffer,
                                                                             bytes / 16, ++tag);
   return check_launch("flush_l2");
+}
+
+extern "C" int evg_device_status(int reset) {
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    const cudaError_t err = cudaGetLastError();
+    return fail(EVG_ELAUNCH, "device_status: %s", cudaGetErrorString(err));
+  }
+  int first = 0;
+  for (int i = 0; i < g_status_reader_count; ++i) {
+    const int code = g_status_readers[i](reset);
+    if (code != 0 && first == 0) first = code;
+  }
+  if (first < 0) return fail(EVG_ELAUNCH, "device_status: cannot read a status word");
+  if (first != 0)
+    return fail(EVG_ETIMEOUT, "a bounded device-side wait gave up (wait id %d)", first);
+  return EVG_OK;
 }

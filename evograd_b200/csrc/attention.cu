@@ -703,6 +703,20 @@ int launch_bwd(const void* dout, const void* q, const void* k, const void* v, co
   return EVG_OK;
 }
 
+int read_attention_status(int reset) {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, g_attn_device_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (reset && code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_attn_device_status, &zero, sizeof(int));
+  }
+  return code;
+}
+const bool g_attention_status_registered = (register_device_status(read_attention_status), true);
+
 }  // namespace
 }  // namespace evg
 
@@ -757,21 +771,3 @@ extern "C" int evg_causal_attention_bwd(const void* dout, const void* q, const v
              : launch_bwd<64, 0>(dout, q, k, v, o, lse, dq, dk, dv, delta, B, H, S, scale, st);
 }
 
-extern "C" int evg_device_status(int reset) {
-  if (cudaDeviceSynchronize() != cudaSuccess) {
-    const cudaError_t err = cudaGetLastError();
-    return fail(EVG_ELAUNCH, "device_status: %s", cudaGetErrorString(err));
-  }
-  int code = 0;
-  if (cudaMemcpyFromSymbol(&code, g_attn_device_status, sizeof(int)) != cudaSuccess) {
-    cudaGetLastError();
-    return fail(EVG_ELAUNCH, "device_status: cannot read the status word");
-  }
-  if (reset && code != 0) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_attn_device_status, &zero, sizeof(int));
-  }
-  if (code != 0)
-    return fail(EVG_ETIMEOUT, "a bounded device-side wait gave up (wait id %d)", code);
-  return EVG_OK;
-}

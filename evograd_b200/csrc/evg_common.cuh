@@ -17,6 +17,11 @@ int fail(int code, const char* fmt, ...);
 int check_launch(const char* what);
 // Tunable lookup (0 = not set).
 int tune(const char* key);
+// Kernels with bounded device-side waits keep a sticky status word per source
+// file; each file registers a reader (returns the word, optionally clearing
+// it) that evg_device_status() polls after synchronising.
+using StatusReader = int (*)(int reset);
+void register_device_status(StatusReader reader);
 // Cached properties of the current device.
 struct DeviceInfo {
   int device = -1;

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "rowcfg.cuh"
+#include "sm100_umma.cuh"
 
 namespace evg {
 namespace {
@@ -164,6 +165,175 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
   }
 }
 
+// Sticky status of the bounded waits in this file (0 = fine).
+__device__ int g_norm_device_status = 0;
+
+// Row-ring variant: the rows of x and dy are brought into a shared-memory ring
+// by bulk async copies (one thread issues them, an mbarrier per stage counts
+// the bytes), so the bytes in flight per SM are set by the ring depth and not
+// by registers or occupancy. One block = one group of THREADS threads walking
+// rows blockIdx.x, blockIdx.x + gridDim.x, ...; thread t owns vectors
+// t, t + THREADS, ... of every row, keeps its float32 column sums in registers
+// and writes the block's partial row straight from them at the end.
+// The block-wide reduction barrier of row i also tells the issuing thread that
+// stage i % STAGES has been read by everyone and can be refilled.
+template <typename T, int THREADS, int VPT, bool LN>
+__global__ void __launch_bounds__(THREADS)
+norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                     const float* __restrict__ mean, const float* __restrict__ rstd,
+                     T* __restrict__ dx, float* __restrict__ partial, int64_t rows, int cols,
+                     int stages, long long wait_limit) {
+  using namespace umma;
+  constexpr int N = Vec<T>::N;
+  constexpr int Q = N / 4;
+  constexpr int NV = LN ? 2 : 1;
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  const int tid = threadIdx.x;
+  const int nvec = cols / N;
+  const uint32_t row_bytes = (uint32_t)cols * sizeof(T);
+  // smem: [stages][2][row_bytes] ring | float32 weight [Q][nvec] float4 | mbarriers | scratch
+  uint8_t* ring = ring_raw;
+  float4* w4 = reinterpret_cast<float4*>(ring + (size_t)stages * 2 * row_bytes);
+  uint64_t* full = reinterpret_cast<uint64_t*>(w4 + (size_t)Q * nvec);
+  float* scratch = reinterpret_cast<float*>(full + 16);
+  int* abort_flag = reinterpret_cast<int*>(scratch + 2 * NV * 32);
+  int phase = 0;
+
+  const int64_t first = blockIdx.x;
+  const int64_t n_mine = first < rows ? (rows - first + gridDim.x - 1) / gridDim.x : 0;
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    fence_mbar_init();
+  }
+  for (int idx = tid; idx < nvec; idx += THREADS) {
+    float f[N];
+    unpack<T>(*reinterpret_cast<const uint4*>(w + (size_t)idx * N), f);
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+      w4[q * nvec + idx] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+  }
+  __syncthreads();
+  const WaitCtx ctx{abort_flag, &g_norm_device_status, wait_limit};
+  auto issue = [&](int64_t i) {
+    const int s = (int)(i % stages);
+    const int64_t row = first + i * gridDim.x;
+    uint8_t* dst = ring + (size_t)s * 2 * row_bytes;
+    mbar_expect_tx(&full[s], 2 * row_bytes);
+    bulk_load_1d(dst, x + row * cols, row_bytes, &full[s]);
+    bulk_load_1d(dst + row_bytes, dy + row * cols, row_bytes, &full[s]);
+  };
+  if (tid == 0)
+    for (int64_t i = 0; i < stages && i < n_mine; ++i) issue(i);
+
+  float acc_w[VPT][N];
+  float acc_b[LN ? VPT : 1][N];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k)
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      acc_w[k][j] = 0.f;
+      if constexpr (LN) acc_b[k][j] = 0.f;
+    }
+  const float inv_cols = 1.0f / (float)cols;
+  float rs_next = 0.f, mu_next = 0.f;
+  if (n_mine > 0) {
+    rs_next = rstd[first];
+    if constexpr (LN) mu_next = mean[first];
+  }
+
+  for (int64_t i = 0; i < n_mine; ++i) {
+    const int s = (int)(i % stages);
+    const uint32_t parity = (uint32_t)((i / stages) & 1);
+    const int64_t row = first + i * gridDim.x;
+    const float rs = rs_next;
+    const float nmr = LN ? -mu_next * rs : 0.f;
+    if (i + 1 < n_mine) {  // statistics of the next row, off the critical path
+      rs_next = rstd[row + gridDim.x];
+      if constexpr (LN) mu_next = mean[row + gridDim.x];
+    }
+    mbar_wait(&full[s], parity, ctx, 401);
+    const uint8_t* sx = ring + (size_t)s * 2 * row_bytes;
+    const uint8_t* sg = sx + row_bytes;
+
+    float xh[VPT][N], gy[VPT][N];
+    float c[NV];
+#pragma unroll
+    for (int q = 0; q < NV; ++q) c[q] = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = tid + k * THREADS;
+      const bool ok = idx < nvec;
+      const int sidx = ok ? idx : 0;
+      uint4 xv = make_uint4(0, 0, 0, 0), gv = make_uint4(0, 0, 0, 0);
+      if (ok) {
+        xv = *reinterpret_cast<const uint4*>(sx + (size_t)idx * 16);
+        gv = *reinterpret_cast<const uint4*>(sg + (size_t)idx * 16);
+      }
+      unpack<T>(xv, xh[k]);
+      unpack<T>(gv, gy[k]);
+#pragma unroll
+      for (int qq = 0; qq < Q; ++qq) {
+        const float4 wv = w4[qq * nvec + sidx];
+        const float wj[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int e = 4 * qq + j;
+          xh[k][e] = LN ? fmaf(xh[k][e], rs, nmr) : xh[k][e] * rs;
+          const float g = gy[k][e] * wj[j];  // padded vectors have dy = 0
+          c[0] = fmaf(g, xh[k][e], c[0]);
+          if constexpr (LN) c[1] += g;
+        }
+      }
+    }
+    block_allreduce<NV, SumOp>(c, scratch, phase);  // everyone is done with stage s
+    if (tid == 0 && i + stages < n_mine) issue(i + stages);
+    const float a_x = -rs * (c[0] * inv_cols);
+    const float a_0 = LN ? -rs * (c[1] * inv_cols) : 0.f;
+    T* dr = dx + row * cols;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = tid + k * THREADS;
+      if (idx < nvec) {
+        float o[N];
+#pragma unroll
+        for (int qq = 0; qq < Q; ++qq) {
+          const float4 wv = w4[qq * nvec + idx];
+          const float wj[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int e = 4 * qq + j;
+            const float g = gy[k][e] * wj[j];
+            o[e] = fmaf(xh[k][e], a_x, fmaf(g, rs, a_0));
+            acc_w[k][e] = fmaf(gy[k][e], xh[k][e], acc_w[k][e]);
+            if constexpr (LN) acc_b[k][e] += gy[k][e];
+          }
+        }
+        st_vec(dr + (size_t)idx * N, pack<T>(o));
+      }
+    }
+  }
+  // One group per block: the partial row goes out straight from registers.
+  float* pw = partial + (size_t)blockIdx.x * cols;
+  float* pb = partial + ((size_t)gridDim.x + blockIdx.x) * cols;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int idx = tid + k * THREADS;
+    if (idx < nvec) {
+#pragma unroll
+      for (int qq = 0; qq < Q; ++qq) {
+        *reinterpret_cast<float4*>(pw + (size_t)idx * N + 4 * qq) =
+            make_float4(acc_w[k][4 * qq], acc_w[k][4 * qq + 1], acc_w[k][4 * qq + 2],
+                        acc_w[k][4 * qq + 3]);
+        if constexpr (LN)
+          *reinterpret_cast<float4*>(pb + (size_t)idx * N + 4 * qq) =
+              make_float4(acc_b[k][4 * qq], acc_b[k][4 * qq + 1], acc_b[k][4 * qq + 2],
+                          acc_b[k][4 * qq + 3]);
+      }
+    }
+  }
+}
+
 // Any width / alignment. One block per row at a time; the block's partial row
 // in the workspace is private to it, so plain read-modify-write is race free.
 template <typename T, bool LN>
@@ -242,6 +412,20 @@ colreduce_kernel(const float* __restrict__ partial, int blocks, int64_t cols, T*
   }
 }
 
+int read_norm_status(int reset) {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, g_norm_device_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (reset && code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_norm_device_status, &zero, sizeof(int));
+  }
+  return code;
+}
+const bool g_norm_status_registered = (register_device_status(read_norm_status), true);
+
 struct BwdPlan {
   bool generic = false;
   RowCfg cfg;
@@ -282,7 +466,35 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
                       aligned16(w) && hidden < (int64_t)1 << 31;
   RowCfg cfg;
   bool launched = false;
-  if (vec_ok && !tune("rows.force_generic") && pick_rowcfg(op, hidden / N, cfg, 512, LN)) {
+  if (vec_ok && !tune("rows.force_generic") && !tune("norm_bwd.no_ring") && !tune(LN ? "layernorm_bwd.group" : "rmsnorm_bwd.group")) {
+    // Row ring: 256 threads, VPT = vectors per thread, as many stages as fit.
+    const int64_t nvec = hidden / N;
+    constexpr int kRingThreads = 256;
+    const size_t row_bytes = (size_t)hidden * sizeof(T);
+    const size_t fixed = (size_t)hidden * sizeof(float) + 16 * 8 + 2 * NV * 32 * sizeof(float) + 64;
+    const size_t budget = (size_t)device_info().max_smem_optin;
+    int stages = tune("norm_bwd.stages");
+    if (stages <= 0) stages = (int)((96 * 1024) / (2 * row_bytes));  // ~96 KB of rows in flight
+    if (stages > 12) stages = 12;
+    while (stages > 0 && fixed + (size_t)stages * 2 * row_bytes > budget) --stages;
+    long long wait_limit = 2000000000ll;
+    if (stages >= 2 && nvec <= 8 * kRingThreads) {
+      const size_t smem = fixed + (size_t)stages * 2 * row_bytes;
+#define EVG_RING(v)                                                                              \
+  if (!launched && nvec <= (int64_t)v * kRingThreads) {                                          \
+    auto kern = norm_bwd_ring_kernel<T, kRingThreads, v, LN>;                                    \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+    blocks = persistent_grid(kern, kRingThreads, smem, rows, 1, cap);                            \
+    kern<<<blocks, kRingThreads, smem, stream>>>((const T*)dy, (const T*)x, (const T*)w, mean,   \
+                                                 rstd, (T*)dx, partial, rows, (int)hidden,       \
+                                                 stages, wait_limit);                            \
+    launched = true;                                                                             \
+  }
+      EVG_RING(1) EVG_RING(2) EVG_RING(4) EVG_RING(8)
+#undef EVG_RING
+    }
+  }
+  if (!launched && vec_ok && !tune("rows.force_generic") && pick_rowcfg(op, hidden / N, cfg, 512, LN)) {
     const int groups = cfg.threads / cfg.G;
     const size_t smem =
         ((size_t)groups * 2 * NV * (cfg.G / 32) + (size_t)(NV + 1) * hidden) * sizeof(float);

@@ -104,7 +104,7 @@ def test_parameter_gradients_are_bit_reproducible(op):
 
 @pytest.mark.parametrize("op", ["layernorm", "rmsnorm", "softmax"])
 @pytest.mark.parametrize("knobs", [
-    {"rows.force_generic": 1},
+    {"rows.force_generic": 1}, {"norm_bwd.no_ring": 1}, {"norm_bwd.stages": 2},
     {"group": 64, "vpt": 8}, {"group": 256, "vpt": 2}, {"group": 512, "vpt": 1},
     {"group": 128, "vpt": 4, "threads": 512}, {"group": 32, "vpt": 4, "threads": 128},
 ])
