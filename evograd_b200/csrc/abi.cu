@@ -27,7 +27,7 @@ const char* const kTuneKeys[] = {
     "layernorm_bwd.threads",    "rmsnorm_fwd.group",      "rmsnorm_fwd.vpt",
     "rmsnorm_fwd.threads",      "rmsnorm_bwd.group",      "rmsnorm_bwd.vpt",
     "rmsnorm_bwd.threads",      "attention.variant",      "rope.generic",           "norm_bwd.no_ring",
-    "norm_bwd.stages",      "attention.wait_limit",
+    "norm_bwd.stages",         "norm_bwd.ring_threads",      "attention.wait_limit",
 };
 }  // namespace
 

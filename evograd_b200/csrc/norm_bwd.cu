@@ -178,7 +178,7 @@ __device__ int g_norm_device_status = 0;
 // The block-wide reduction barrier of row i also tells the issuing thread that
 // stage i % STAGES has been read by everyone and can be refilled.
 template <typename T, int THREADS, int VPT, bool LN>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, (THREADS == 256 && VPT <= 2) ? (LN ? 2 : 3) : 1)
 norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                      const float* __restrict__ mean, const float* __restrict__ rstd,
                      T* __restrict__ dx, float* __restrict__ partial, int64_t rows, int cols,
@@ -386,26 +386,35 @@ norm_bwd_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   }
 }
 
-// Stage 2: out[c] = sum_p partial[p][c], p ascending inside each of 16 strided
-// slices, slices then added in order. gridDim.y selects dweight / dbias.
+// Stage 2: out[c] = sum_p partial[p][c]. Block = 32 columns x 32 row slices;
+// a slice adds its rows p = y, y+32, ... with four independent accumulators
+// (so four loads are in flight per thread), the slices are then added in
+// order. Fixed order throughout: bit-reproducible. gridDim.y = dweight / dbias.
 template <typename T>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(1024)
 colreduce_kernel(const float* __restrict__ partial, int blocks, int64_t cols, T* out_w, T* out_b,
                  float* out_f32) {
-  __shared__ float tile[16][33];
+  __shared__ float tile[32][33];
   const int which = blockIdx.y;
   const float* src = partial + (size_t)which * blocks * cols;
   const int64_t col = (int64_t)blockIdx.x * 32 + threadIdx.x;
-  float s = 0.f;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
   if (col < cols) {
-    for (int p = threadIdx.y; p < blocks; p += 16) s += src[(size_t)p * cols + col];
+    int p = threadIdx.y;
+    for (; p + 96 < blocks; p += 128) {
+      s0 += src[(size_t)p * cols + col];
+      s1 += src[(size_t)(p + 32) * cols + col];
+      s2 += src[(size_t)(p + 64) * cols + col];
+      s3 += src[(size_t)(p + 96) * cols + col];
+    }
+    for (; p < blocks; p += 32) s0 += src[(size_t)p * cols + col];
   }
-  tile[threadIdx.y][threadIdx.x] = s;
+  tile[threadIdx.y][threadIdx.x] = (s0 + s1) + (s2 + s3);
   __syncthreads();
   if (threadIdx.y == 0 && col < cols) {
     float t = tile[0][threadIdx.x];
 #pragma unroll
-    for (int i = 1; i < 16; ++i) t += tile[i][threadIdx.x];
+    for (int i = 1; i < 32; ++i) t += tile[i][threadIdx.x];
     T* out = which == 0 ? out_w : out_b;
     if (out) out[col] = from_f32<T>(t);
     if (out_f32) out_f32[(size_t)which * cols + col] = t;
@@ -435,13 +444,15 @@ struct BwdPlan {
 
 int max_partial_blocks() {
   int per_sm = tune("norm_bwd.blocks_per_sm");
-  if (per_sm <= 0) per_sm = 2;
+  if (per_sm <= 0) per_sm = 3;
   return device_info().sm_count * per_sm;
 }
 
+// `block_limit` > 0 bounds the number of partial rows (callers with a fixed scratch).
 template <typename T, bool LN>
-int64_t norm_bwd_workspace(int64_t rows, int64_t hidden) {
+int64_t norm_bwd_workspace(int64_t rows, int64_t hidden, int64_t block_limit = 0) {
   int64_t blocks = max_partial_blocks();
+  if (block_limit > 0 && blocks > block_limit) blocks = block_limit;
   if (blocks > rows) blocks = rows > 0 ? rows : 1;
   return blocks * hidden * (LN ? 2 : 1) * (int64_t)sizeof(float);
 }
@@ -450,47 +461,52 @@ template <typename T, bool LN>
 int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* mean,
                     const float* rstd, void* dx, void* dweight, void* dbias, float* out_f32,
                     void* workspace, int64_t workspace_bytes, int64_t rows, int64_t hidden,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, int64_t block_limit = 0) {
   constexpr int N = Vec<T>::N;
   constexpr int NV = LN ? 2 : 1;
   const char* op = LN ? "layernorm_bwd" : "rmsnorm_bwd";
-  const int64_t need = norm_bwd_workspace<T, LN>(rows, hidden);
+  const int64_t need = norm_bwd_workspace<T, LN>(rows, hidden, block_limit);
   if (!workspace || workspace_bytes < need)
     return fail(EVG_EWORKSPACE, "%s: workspace %lld bytes, need %lld", op,
                 (long long)workspace_bytes, (long long)need);
   if (!aligned16(workspace)) return fail(EVG_EALIGN, "%s: workspace not 16-byte aligned", op);
   float* partial = (float*)workspace;
-  const int cap = max_partial_blocks();
+  int cap = max_partial_blocks();
+  if (block_limit > 0 && cap > block_limit) cap = (int)block_limit;
   int blocks = 0;
   const bool vec_ok = hidden % N == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) &&
                       aligned16(w) && hidden < (int64_t)1 << 31;
   RowCfg cfg;
   bool launched = false;
   if (vec_ok && !tune("rows.force_generic") && !tune("norm_bwd.no_ring") && !tune(LN ? "layernorm_bwd.group" : "rmsnorm_bwd.group")) {
-    // Row ring: 256 threads, VPT = vectors per thread, as many stages as fit.
+    // Row ring: one group of 256 or 512 threads per block, VPT vectors per
+    // thread, as many stages as fit (about 48 KB of rows in flight per block).
     const int64_t nvec = hidden / N;
-    constexpr int kRingThreads = 256;
+    int ring_threads = tune("norm_bwd.ring_threads");
+    if (ring_threads != 256 && ring_threads != 512) ring_threads = 256;
     const size_t row_bytes = (size_t)hidden * sizeof(T);
     const size_t fixed = (size_t)hidden * sizeof(float) + 16 * 8 + 2 * NV * 32 * sizeof(float) + 64;
     const size_t budget = (size_t)device_info().max_smem_optin;
     int stages = tune("norm_bwd.stages");
-    if (stages <= 0) stages = (int)((96 * 1024) / (2 * row_bytes));  // ~96 KB of rows in flight
+    if (stages <= 0) stages = (int)((48 * 1024) / (2 * row_bytes));  // 3 for 8 KB rows
+    if (stages < 2) stages = 2;
     if (stages > 12) stages = 12;
     while (stages > 0 && fixed + (size_t)stages * 2 * row_bytes > budget) --stages;
     long long wait_limit = 2000000000ll;
-    if (stages >= 2 && nvec <= 8 * kRingThreads) {
+    const int ring_cap = cap;
+    if (stages >= 2 && nvec <= 8 * ring_threads) {
       const size_t smem = fixed + (size_t)stages * 2 * row_bytes;
-#define EVG_RING(v)                                                                              \
-  if (!launched && nvec <= (int64_t)v * kRingThreads) {                                          \
-    auto kern = norm_bwd_ring_kernel<T, kRingThreads, v, LN>;                                    \
+#define EVG_RING(t, v)                                                                           \
+  if (!launched && ring_threads == t && nvec <= (int64_t)v * t) {                                \
+    auto kern = norm_bwd_ring_kernel<T, t, v, LN>;                                               \
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
-    blocks = persistent_grid(kern, kRingThreads, smem, rows, 1, cap);                            \
-    kern<<<blocks, kRingThreads, smem, stream>>>((const T*)dy, (const T*)x, (const T*)w, mean,   \
-                                                 rstd, (T*)dx, partial, rows, (int)hidden,       \
-                                                 stages, wait_limit);                            \
+    blocks = persistent_grid(kern, t, smem, rows, 1, ring_cap);                                  \
+    kern<<<blocks, t, smem, stream>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd,        \
+                                      (T*)dx, partial, rows, (int)hidden, stages, wait_limit);   \
     launched = true;                                                                             \
   }
-      EVG_RING(1) EVG_RING(2) EVG_RING(4) EVG_RING(8)
+      EVG_RING(256, 1) EVG_RING(256, 2) EVG_RING(256, 4) EVG_RING(256, 8)
+      EVG_RING(512, 1) EVG_RING(512, 2) EVG_RING(512, 4) EVG_RING(512, 8)
 #undef EVG_RING
     }
   }
@@ -526,7 +542,7 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
     return fail(EVG_EWORKSPACE, "%s: internal: partial rows exceed workspace", op);
   if (dweight || dbias || out_f32) {
     dim3 grid((unsigned)((hidden + 31) / 32), NV);
-    colreduce_kernel<T><<<grid, dim3(32, 16), 0, stream>>>(partial, blocks, hidden, (T*)dweight,
+    colreduce_kernel<T><<<grid, dim3(32, 32), 0, stream>>>(partial, blocks, hidden, (T*)dweight,
                                                            (T*)dbias, out_f32);
     rc = check_launch("norm_bwd colreduce");
   }
@@ -639,7 +655,8 @@ extern "C" int evg_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
                 "rmsnorm_bwd_noalloc: hidden=%lld exceeds the built-in scratch (max hidden %lld); "
                 "use evg_rmsnorm_bwd with a caller-provided workspace",
                 (long long)hidden, (long long)kNoAllocMaxHidden);
-  const int64_t need = norm_bwd_workspace<float, false>(rows, hidden);
+  const int64_t block_limit = kNoAllocFloats / hidden;  // >= kNoAllocMaxBlocks
+  const int64_t need = norm_bwd_workspace<float, false>(rows, hidden, block_limit);
   const int64_t have = kNoAllocFloats * (int64_t)sizeof(float);
   if (need > have)
     return fail(EVG_EUNSUPPORTED,
@@ -652,6 +669,6 @@ extern "C" int evg_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   return EVG_DISPATCH_DTYPE(dtype, [&] {
     return launch_norm_bwd<T, false>(dy, x, weight, nullptr, rstd, dx, dweight, nullptr,
                                      dweight_f32, scratch, have, rows, hidden,
-                                     (cudaStream_t)stream);
+                                     (cudaStream_t)stream, block_limit);
   });
 }

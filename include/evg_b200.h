@@ -143,9 +143,10 @@ int evg_rmsnorm_bwd(const void* dy, const void* x, const void* weight,
  * process exits) instead of a caller-provided workspace. The call performs no
  * cudaMalloc / cudaFree and calls no allocating library routine.
  *
- * Limits: hidden <= 8192 and at most 320 partial rows (the built-in launch
- * shapes use 2 per SM, 296 on a B200); anything larger returns
- * EVG_EUNSUPPORTED with a message and enqueues nothing.
+ * Limits: hidden <= 8192. The launch is shaped so that its partial rows fit the
+ * array (at least 320 rows of 8192 floats, more for narrower rows); a request
+ * that cannot be made to fit returns EVG_EUNSUPPORTED with a message and
+ * enqueues nothing.
  * First call on a device: looks up the array's device address (once per
  * device, under a lock, with that device current). Make that first call before
  * starting any stream capture.
