@@ -663,9 +663,15 @@ def main():
     ap.add_argument("--no-per-op", action="store_true", help="skip the per-operator table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--attention-shape", default=None, metavar="B,H,S",
+                    help="smaller causal-attention case (profiling captures only; head_dim stays 128)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
+    if args.attention_shape:
+        b, h, sq = (int(t) for t in args.attention_shape.split(","))
+        AttentionWL.B, AttentionWL.H, AttentionWL.S = b, h, sq
+        AttentionWL.name = f"causal_attention_bf16_{b}x{h}x{sq}x128"
     if args.impl == "reference":
         run_reference(args)
     else:

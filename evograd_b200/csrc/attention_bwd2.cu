@@ -1,0 +1,543 @@
+// Causal attention backward, warp-specialised and pipelined (sm_100a).
+//
+// Roles inside a block of 320 threads:
+//   warp 0, lane 0   TMA producer: tiles of Q/K/V/dO (+ row statistics) into a
+//                    shared-memory ring, completion on "full" mbarriers, refills
+//                    gated by "empty" mbarriers that the MMA thread commits;
+//   warp 1, lane 0   tcgen05.mma issuer: every product of the kernel, in an
+//                    order that keeps the tensor pipe fed while the compute
+//                    warps work on the previous tile;
+//   warps 2..9       256 compute threads: thread = one TMEM lane (score row)
+//                    and one half of the tile's columns.
+// The score buffers are double-buffered in TMEM, so the scores of tile j+1 are
+// formed while tile j is being turned into dS. A compute warp writes its 16-bit
+// results only into TMEM columns it read itself, so no block-wide barrier is
+// needed between reading scores and writing dS: the A operand of the following
+// product is addressed k-step by k-step and need not be contiguous.
+//
+// As in the first version, dK/dV belong to the block that owns a key tile and dQ
+// to the block that owns a query tile: deterministic, no atomics.
+#include "attention_common.cuh"
+
+namespace evg {
+
+__device__ int g_attn2_device_status = 0;
+
+namespace {
+
+using namespace umma;
+using namespace attn;
+
+constexpr int kThreads2 = 320;
+
+struct Roles {
+  int warp, lane;
+  bool is_tma, is_mma, is_compute;
+  int quarter;  // TMEM lane quarter this warp may access (warp % 4)
+  int half;     // which half of the tile's columns a compute warp handles
+  int row;      // row inside the tile owned by a compute thread
+};
+__device__ __forceinline__ Roles roles() {
+  Roles r;
+  r.warp = threadIdx.x >> 5;
+  r.lane = threadIdx.x & 31;
+  r.is_tma = r.warp == 0;
+  r.is_mma = r.warp == 1;
+  r.is_compute = r.warp >= 2;
+  r.quarter = r.warp & 3;
+  r.half = r.is_compute ? (r.warp - 2) >> 2 : 0;
+  r.row = r.quarter * 32 + r.lane;
+  return r;
+}
+
+// A warp has finished its TMEM accesses: order them, then one arrival.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
+// Rows of a [128 x HD] float32 TMEM accumulator -> 16-bit rows of [B*H, S, HD].
+template <int HD, int FMT>
+__device__ __forceinline__ void store_rows(uint32_t t_acc, void* out, int bh, int row0, int S,
+                                           float scale, const Roles& r) {
+  const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
+  const int row = row0 + r.row;
+  const bool ok = row < S;
+  uint8_t* dst = reinterpret_cast<uint8_t*>(out) + ((size_t)bh * S + (ok ? row : 0)) * HD * 2;
+#pragma unroll
+  for (int c = 0; c < HD / 64; ++c) {
+    const int col = r.half * (HD / 2) + c * 32;
+    uint32_t acc[32];
+    tmem_ld32(t_acc + lane_base + col, acc);
+    tmem_wait_ld();
+    if (ok) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint4 pk;
+        pk.x = pack2<FMT>(__uint_as_float(acc[8 * v + 0]) * scale, __uint_as_float(acc[8 * v + 1]) * scale);
+        pk.y = pack2<FMT>(__uint_as_float(acc[8 * v + 2]) * scale, __uint_as_float(acc[8 * v + 3]) * scale);
+        pk.z = pack2<FMT>(__uint_as_float(acc[8 * v + 4]) * scale, __uint_as_float(acc[8 * v + 5]) * scale);
+        pk.w = pack2<FMT>(__uint_as_float(acc[8 * v + 6]) * scale, __uint_as_float(acc[8 * v + 7]) * scale);
+        *reinterpret_cast<uint4*>(dst + (col + v * 8) * 2) = pk;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ prepare
+// delta = rowsum(dO * O) and the log-sum-exp in log2 units, both written to
+// arrays padded to whole 128-row tiles per (batch, head): rows >= S get
+// lse2 = +inf (probability 0) and delta = 0. HD/8 threads per row.
+template <int HD, int FMT>
+__global__ void __launch_bounds__(256)
+attn_prepare_kernel(const void* __restrict__ do_ptr, const void* __restrict__ o_ptr,
+                    const float* __restrict__ lse, float* __restrict__ lse2_pad,
+                    float* __restrict__ delta_pad, int S, int S_pad, int64_t padded_rows) {
+  constexpr int TPR = HD / 8;
+  const int64_t prow = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / TPR;
+  const int part = threadIdx.x % TPR;
+  if (prow >= padded_rows) return;
+  const int64_t bh = prow / S_pad;
+  const int q = (int)(prow % S_pad);
+  const bool ok = q < S;
+  float s = 0.f;
+  if (ok) {
+    const int64_t row = bh * S + q;
+    const uint4 a = ld_vec(reinterpret_cast<const uint8_t*>(do_ptr) + (row * HD + part * 8) * 2);
+    const uint4 b = ld_vec(reinterpret_cast<const uint8_t*>(o_ptr) + (row * HD + part * 8) * 2);
+    float af[8], bf[8];
+    if constexpr (FMT == 1) { unpack<__nv_bfloat16>(a, af); unpack<__nv_bfloat16>(b, bf); }
+    else { unpack<__half>(a, af); unpack<__half>(b, bf); }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += af[i] * bf[i];
+  }
+#pragma unroll
+  for (int off = TPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (part == 0) {
+    delta_pad[prow] = ok ? s : 0.f;
+    lse2_pad[prow] = ok ? lse[bh * S + q] * kLog2e : INFINITY;
+  }
+}
+
+// ------------------------------------------------------------------------ dQ
+// grid = (query tiles, B*H). The block owns query tile `qtile` and walks key
+// tiles j = 0..qtile:  S = Q K_j^T, dP = dO V_j^T, dS = exp2(S*c - lse2)*(dP - delta),
+// dQ += dS K_j.
+// TMEM (512 columns): [0,128) and [128,256) two score buffers (tile j uses
+// buffer j%2; its dS goes back into the same buffer), [256,384) dP,
+// [384,384+HD) dQ.
+// Issue order of the MMA thread for tile j:  S(j+1), dP(j+1) [after the compute
+// warps have pulled dP(j) into registers], dQ(j) [after dS(j) is in TMEM].
+template <int HD, int FMT>
+__global__ void __launch_bounds__(kThreads2, 1)
+attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                    const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
+                    void* __restrict__ dq_ptr, int S, int S_pad, float scale, long long wait_limit) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr uint32_t TB = tile_bytes<HD>();
+  BlockSetup bs = carve(smem_raw, 6 * TB);
+  uint8_t* sQ = bs.smem;
+  uint8_t* sDO = sQ + TB;
+  uint8_t* sK[2] = {sDO + TB, sDO + 2 * TB};
+  uint8_t* sV[2] = {sDO + 3 * TB, sDO + 4 * TB};
+  uint64_t* qdo_full = bs.bars + 0;
+  uint64_t* kv_full = bs.bars + 1;   // [2]
+  uint64_t* kv_empty = bs.bars + 3;  // [2]
+  uint64_t* s_full = bs.bars + 5;    // [2]
+  uint64_t* dp_full = bs.bars + 7;
+  uint64_t* dp_free = bs.bars + 8;
+  uint64_t* ds_full = bs.bars + 9;   // [2]
+  uint64_t* done = bs.bars + 11;
+  const Roles r = roles();
+  const int qtile = gridDim.x - 1 - blockIdx.x;  // heaviest tiles first
+  const int bh = blockIdx.y;
+  const int q0 = qtile * kTile;
+  const int n_it = qtile + 1;
+  const float scale_log2 = scale * kLog2e;
+
+  if (threadIdx.x == 0) {
+    *bs.abort_flag = 0;
+    mbar_init(qdo_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1);
+      mbar_init(s_full + i, 1); mbar_init(ds_full + i, 8);
+    }
+    mbar_init(dp_full, 1); mbar_init(dp_free, 8); mbar_init(done, 1);
+    fence_mbar_init();
+    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
+  }
+  __syncthreads();
+  if (r.warp == 1) { tmem_alloc(bs.tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *bs.tmem_slot;
+  const WaitCtx ctx{bs.abort_flag, &g_attn2_device_status, wait_limit};
+  constexpr uint32_t idesc_s = instr_desc_f16(FMT, 128, 128, 0, 0);
+  constexpr uint32_t idesc_d = instr_desc_f16(FMT, 128, HD, 0, 1);
+  const uint32_t tSb[2] = {tmem, tmem + 128};
+  const uint32_t tDP = tmem + 256, tDQ = tmem + 384;
+
+  if (r.is_tma && r.lane == 0) {
+    mbar_expect_tx(qdo_full, 2 * TB);
+    load_tile<HD>(sQ, &map_q, q0, bh, qdo_full);
+    load_tile<HD>(sDO, &map_do, q0, bh, qdo_full);
+    for (int j = 0; j < n_it; ++j) {
+      const int st = j & 1;
+      if (j >= 2) mbar_wait(kv_empty + st, ((j - 2) >> 1) & 1, ctx, 501);
+      mbar_expect_tx(kv_full + st, 2 * TB);
+      load_tile<HD>(sK[st], &map_k, j * kTile, bh, kv_full + st);
+      load_tile<HD>(sV[st], &map_v, j * kTile, bh, kv_full + st);
+    }
+  } else if (r.is_mma && r.lane == 0) {
+    mbar_wait(qdo_full, 0, ctx, 502);
+    mbar_wait(kv_full + 0, 0, ctx, 503);
+    tc_fence_after_sync();
+    issue_scores<HD>(tSb[0], smem_u32(sQ), smem_u32(sK[0]), idesc_s);
+    mma_commit(s_full + 0);
+    issue_scores<HD>(tDP, smem_u32(sDO), smem_u32(sV[0]), idesc_s);
+    mma_commit(dp_full);
+    for (int j = 0; j < n_it; ++j) {
+      const int b = j & 1;
+      if (j + 1 < n_it) {
+        const int b1 = (j + 1) & 1;
+        mbar_wait(kv_full + b1, ((j + 1) >> 1) & 1, ctx, 504);
+        tc_fence_after_sync();
+        issue_scores<HD>(tSb[b1], smem_u32(sQ), smem_u32(sK[b1]), idesc_s);
+        mma_commit(s_full + b1);
+        mbar_wait(dp_free, j & 1, ctx, 505);
+        tc_fence_after_sync();
+        issue_scores<HD>(tDP, smem_u32(sDO), smem_u32(sV[b1]), idesc_s);
+        mma_commit(dp_full);
+      }
+      mbar_wait(ds_full + b, (j >> 1) & 1, ctx, 506);
+      tc_fence_after_sync();
+      // dS is stored as two 32-column halves at buffer columns 0 and 64.
+#pragma unroll
+      for (int ks = 0; ks < kTile / 16; ++ks)
+        mma_ts(tDQ, tSb[b] + (ks >> 2) * 64 + (ks & 3) * 8, desc_mnmajor(smem_u32(sK[b]), kTile, ks),
+               idesc_d, (j > 0 || ks > 0) ? 1u : 0u);
+      mma_commit(kv_empty + b);
+    }
+    mma_commit(done);
+  } else if (r.is_compute) {
+    const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
+    const int q_glob = q0 + r.row;
+    const float lse2 = lse2_pad[(size_t)bh * S_pad + q_glob];
+    const float delta = delta_pad[(size_t)bh * S_pad + q_glob];
+    for (int j = 0; j < n_it; ++j) {
+      const int b = j & 1;
+      mbar_wait(s_full + b, (j >> 1) & 1, ctx, 507);
+      mbar_wait(dp_full, j & 1, ctx, 508);
+      __syncwarp();
+      tc_fence_after_sync();
+      uint32_t sr[64], dr[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tmem_ld32(tSb[b] + lane_base + r.half * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
+        tmem_ld32(tDP + lane_base + r.half * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&dr[c * 32]));
+      }
+      tmem_wait_ld();
+      warp_arrive(dp_free, r.lane);
+      const bool diag = (j == qtile);
+      const int kv0 = j * kTile + r.half * 64;
+      uint32_t dd[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float d[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float pe = exp2f(__uint_as_float(sr[2 * i + e]) * scale_log2 - lse2);
+          if (diag && kv0 + 2 * i + e > q_glob) pe = 0.f;
+          d[e] = pe * (__uint_as_float(dr[2 * i + e]) - delta);
+        }
+        dd[i] = pack2<FMT>(d[0], d[1]);
+      }
+      tmem_st32(tSb[b] + lane_base + r.half * 64, dd);
+      tmem_wait_st();
+      warp_arrive(ds_full + b, r.lane);
+    }
+    mbar_wait(done, 0, ctx, 509);
+    __syncwarp();
+    tc_fence_after_sync();
+    store_rows<HD, FMT>(tDQ, dq_ptr, bh, q0, S, scale, r);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (r.warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// -------------------------------------------------------------------- dK, dV
+// grid = (key tiles, B*H). The block owns key tile `kvt` and walks the query
+// tiles i >= kvt in CHUNKS of 64 query rows (two chunks per 128-row tile), so
+// that the float32 score/dP buffers take 64 TMEM columns each and can be
+// double-buffered next to the two 128-column accumulators:
+//   S^T = K Q_c^T, dP^T = V dO_c^T           [128 keys x 64 queries]
+//   P^T = exp2(S^T*c - lse2_q), dS^T = P^T*(dP^T - delta_q)
+//   dV += P^T dO_c, dK += dS^T Q_c           (A from TMEM, 4 k-steps of 16 queries)
+// TMEM: [0,64) [64,128) score buffers, [128,192) [192,256) dP buffers,
+//       [256,256+HD) dV, [384,384+HD) dK.
+// A compute warp handles 32 of a chunk's 64 query columns; its packed P^T / dS^T
+// (16 columns) go to the start of the 32 columns it read.
+template <int HD, int FMT>
+__global__ void __launch_bounds__(kThreads2, 1)
+attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                      const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
+                      void* __restrict__ dk_ptr, void* __restrict__ dv_ptr, int S, int S_pad,
+                      float scale, long long wait_limit) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr uint32_t TB = tile_bytes<HD>();
+  BlockSetup bs = carve(smem_raw, 6 * TB + 2048);
+  uint8_t* sK = bs.smem;
+  uint8_t* sV = sK + TB;
+  uint8_t* sQ[2] = {sV + TB, sV + 2 * TB};
+  uint8_t* sDO[2] = {sV + 3 * TB, sV + 4 * TB};
+  float* s_stat = reinterpret_cast<float*>(sV + 5 * TB);  // [stage][lse2 | delta][128]
+  uint64_t* kv_full = bs.bars + 0;
+  uint64_t* q_full = bs.bars + 1;     // [2]
+  uint64_t* q_empty = bs.bars + 3;    // [2]
+  uint64_t* sdp_full = bs.bars + 5;   // [2]
+  uint64_t* pds_full = bs.bars + 7;   // [2]
+  uint64_t* done = bs.bars + 9;
+  const Roles r = roles();
+  const int kvt = blockIdx.x;  // key tile 0 meets the most query tiles: heaviest first
+  const int bh = blockIdx.y;
+  const int kv0 = kvt * kTile;
+  const int n_q = S_pad / kTile;
+  const int n_it = n_q - kvt;
+  const int n_chunks = 2 * n_it;
+  const float scale_log2 = scale * kLog2e;
+
+  if (threadIdx.x == 0) {
+    *bs.abort_flag = 0;
+    mbar_init(kv_full, 1); mbar_init(done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(q_full + i, 1); mbar_init(q_empty + i, 1);
+      mbar_init(sdp_full + i, 1); mbar_init(pds_full + i, 8);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
+  }
+  __syncthreads();
+  if (r.warp == 1) { tmem_alloc(bs.tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *bs.tmem_slot;
+  const WaitCtx ctx{bs.abort_flag, &g_attn2_device_status, wait_limit};
+  constexpr uint32_t idesc_s = instr_desc_f16(FMT, 128, 64, 0, 0);
+  constexpr uint32_t idesc_d = instr_desc_f16(FMT, 128, HD, 0, 1);
+  const uint32_t tSb[2] = {tmem, tmem + 64};
+  const uint32_t tPb[2] = {tmem + 128, tmem + 192};
+  const uint32_t tDV = tmem + 256, tDK = tmem + 384;
+
+  if (r.is_tma && r.lane == 0) {
+    mbar_expect_tx(kv_full, 2 * TB);
+    load_tile<HD>(sK, &map_k, kv0, bh, kv_full);
+    load_tile<HD>(sV, &map_v, kv0, bh, kv_full);
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it & 1;
+      const int q0 = (kvt + it) * kTile;
+      if (it >= 2) mbar_wait(q_empty + st, ((it - 2) >> 1) & 1, ctx, 601);
+      mbar_expect_tx(q_full + st, 2 * TB + 1024);
+      load_tile<HD>(sQ[st], &map_q, q0, bh, q_full + st);
+      load_tile<HD>(sDO[st], &map_do, q0, bh, q_full + st);
+      bulk_load_1d(s_stat + st * 256, lse2_pad + (size_t)bh * S_pad + q0, 512, q_full + st);
+      bulk_load_1d(s_stat + st * 256 + 128, delta_pad + (size_t)bh * S_pad + q0, 512, q_full + st);
+    }
+  } else if (r.is_mma && r.lane == 0) {
+    // Scores of chunk c: B operand = 64 rows of the Q / dO tile starting at row 64*(c&1).
+    auto issue_chunk_scores = [&](int c) {
+      const int st = (c >> 1) & 1, hq = c & 1, b = c & 1;
+      const uint32_t qa = smem_u32(sQ[st]) + hq * 64 * 128, da = smem_u32(sDO[st]) + hq * 64 * 128;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        mma_ss(tSb[b], desc_kmajor(smem_u32(sK), kTile, ks), desc_kmajor(qa, kTile, ks), idesc_s,
+               ks > 0 ? 1u : 0u);
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        mma_ss(tPb[b], desc_kmajor(smem_u32(sV), kTile, ks), desc_kmajor(da, kTile, ks), idesc_s,
+               ks > 0 ? 1u : 0u);
+      mma_commit(sdp_full + b);
+    };
+    mbar_wait(kv_full, 0, ctx, 602);
+    mbar_wait(q_full + 0, 0, ctx, 603);
+    tc_fence_after_sync();
+    issue_chunk_scores(0);
+    for (int c = 0; c < n_chunks; ++c) {
+      const int b = c & 1, it = c >> 1, st = it & 1, hq = c & 1;
+      if (c + 1 < n_chunks) {
+        const int it1 = (c + 1) >> 1;
+        if (((c + 1) & 1) == 0) {
+          mbar_wait(q_full + (it1 & 1), (it1 >> 1) & 1, ctx, 604);
+          tc_fence_after_sync();
+        }
+        issue_chunk_scores(c + 1);
+      }
+      mbar_wait(pds_full + b, (c >> 1) & 1, ctx, 605);
+      tc_fence_after_sync();
+      // 4 k-steps of 16 queries; packed halves sit at buffer columns 0 and 32.
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        mma_ts(tDV, tSb[b] + (ks >> 1) * 32 + (ks & 1) * 8,
+               desc_mnmajor(smem_u32(sDO[st]), kTile, hq * 4 + ks), idesc_d, (c > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        mma_ts(tDK, tPb[b] + (ks >> 1) * 32 + (ks & 1) * 8,
+               desc_mnmajor(smem_u32(sQ[st]), kTile, hq * 4 + ks), idesc_d, (c > 0 || ks > 0) ? 1u : 0u);
+      if (hq == 1) mma_commit(q_empty + st);
+    }
+    mma_commit(done);
+  } else if (r.is_compute) {
+    const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
+    const int kv_glob = kv0 + r.row;
+    for (int c = 0; c < n_chunks; ++c) {
+      const int b = c & 1, it = c >> 1, st = it & 1, hq = c & 1;
+      if (hq == 0) mbar_wait(q_full + st, (it >> 1) & 1, ctx, 606);  // row statistics landed
+      mbar_wait(sdp_full + b, (c >> 1) & 1, ctx, 607);
+      __syncwarp();
+      tc_fence_after_sync();
+      uint32_t sr[32], dr[32];
+      tmem_ld32(tSb[b] + lane_base + r.half * 32, sr);
+      tmem_ld32(tPb[b] + lane_base + r.half * 32, dr);
+      tmem_wait_ld();
+      const int col0 = hq * 64 + r.half * 32;  // first query column (inside the tile) of this warp
+      const float4* lse4 = reinterpret_cast<const float4*>(s_stat + st * 256 + col0);
+      const float4* del4 = reinterpret_cast<const float4*>(s_stat + st * 256 + 128 + col0);
+      const bool diag = (it == 0);
+      const int q_first = (kvt + it) * kTile + col0;
+      uint32_t pp[16], dd[16];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const float4 l4 = lse4[g], d4 = del4[g];
+        const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+        float p[4], d[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float pe = exp2f(__uint_as_float(sr[4 * g + e]) * scale_log2 - lv[e]);
+          if (diag && q_first + 4 * g + e < kv_glob) pe = 0.f;
+          p[e] = pe;
+          d[e] = pe * (__uint_as_float(dr[4 * g + e]) - dv[e]);
+        }
+        pp[2 * g] = pack2<FMT>(p[0], p[1]); pp[2 * g + 1] = pack2<FMT>(p[2], p[3]);
+        dd[2 * g] = pack2<FMT>(d[0], d[1]); dd[2 * g + 1] = pack2<FMT>(d[2], d[3]);
+      }
+      tmem_st16(tSb[b] + lane_base + r.half * 32, pp);
+      tmem_st16(tPb[b] + lane_base + r.half * 32, dd);
+      tmem_wait_st();
+      warp_arrive(pds_full + b, r.lane);
+    }
+    mbar_wait(done, 0, ctx, 608);
+    __syncwarp();
+    tc_fence_after_sync();
+    store_rows<HD, FMT>(tDV, dv_ptr, bh, kv0, S, 1.0f, r);
+    store_rows<HD, FMT>(tDK, dk_ptr, bh, kv0, S, scale, r);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (r.warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------- host side
+long long wait_limit_cycles2() {
+  const int t = tune("attention.wait_limit");  // in millions of cycles
+  return t > 0 ? (long long)t * 1000000ll : 2000000000ll;
+}
+
+template <typename Kernel>
+int reserve_smem(Kernel kernel, size_t bytes) {
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return fail(EVG_ELAUNCH, "attention backward: cannot reserve %zu bytes of shared memory", bytes);
+  }
+  return EVG_OK;
+}
+
+template <int HD, int FMT>
+int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                const float* lse, void* dq, void* dk, void* dv, float* workspace, int64_t B,
+                int64_t H, int64_t S, float scale, cudaStream_t stream) {
+  CUtensorMap mq, mk, mv, mdo;
+  if (!encode_tile_map_16bit(&mq, q, FMT, HD, S, B * H, kTile) ||
+      !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * H, kTile) ||
+      !encode_tile_map_16bit(&mv, v, FMT, HD, S, B * H, kTile) ||
+      !encode_tile_map_16bit(&mdo, dout, FMT, HD, S, B * H, kTile))
+    return fail(EVG_ELAUNCH, "causal_attention_bwd: cuTensorMapEncodeTiled failed");
+  const int64_t n_q = (S + kTile - 1) / kTile;
+  const int64_t S_pad = n_q * kTile;
+  const int64_t padded_rows = B * H * S_pad;
+  float* lse2_pad = workspace;
+  float* delta_pad = workspace + padded_rows;
+  {
+    constexpr int TPR = HD / 8;
+    const int64_t threads = padded_rows * TPR;  // a multiple of 256
+    attn_prepare_kernel<HD, FMT><<<(unsigned)(threads / 256), 256, 0, stream>>>(
+        dout, o, lse, lse2_pad, delta_pad, (int)S, (int)S_pad, padded_rows);
+    if (int rc = check_launch("causal_attention_bwd prepare")) return rc;
+  }
+  dim3 grid((unsigned)n_q, (unsigned)(B * H));
+  const long long limit = wait_limit_cycles2();
+  {
+    const size_t smem = 6 * tile_bytes<HD>() + 2048 + kControlBytes + 1024;
+    auto kern = attn_bwd2_dkdv_kernel<HD, FMT>;
+    if (int rc = reserve_smem(kern, smem)) return rc;
+    kern<<<grid, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv, (int)S,
+                                            (int)S_pad, scale, limit);
+    if (int rc = check_launch("causal_attention_bwd dkdv")) return rc;
+  }
+  {
+    const size_t smem = 6 * tile_bytes<HD>() + kControlBytes + 1024;
+    auto kern = attn_bwd2_dq_kernel<HD, FMT>;
+    if (int rc = reserve_smem(kern, smem)) return rc;
+    kern<<<grid, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq, (int)S,
+                                            (int)S_pad, scale, limit);
+    if (int rc = check_launch("causal_attention_bwd dq")) return rc;
+  }
+  return EVG_OK;
+}
+
+int read_attention2_status(int reset) {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, g_attn2_device_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (reset && code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_attn2_device_status, &zero, sizeof(int));
+  }
+  return code;
+}
+const bool g_attention2_status_registered =
+    (register_device_status(read_attention2_status), true);
+
+}  // namespace
+
+namespace attn {
+
+int64_t bwd2_workspace_bytes(int64_t B, int64_t H, int64_t S) {
+  const int64_t S_pad = (S + kTile - 1) / kTile * kTile;
+  return 2 * B * H * S_pad * (int64_t)sizeof(float);
+}
+
+int launch_bwd2_any(int head_dim, int fmt, const void* dout, const void* q, const void* k,
+                    const void* v, const void* o, const float* lse, void* dq, void* dk, void* dv,
+                    float* workspace, int64_t B, int64_t H, int64_t S, float scale,
+                    cudaStream_t stream) {
+  if (head_dim == 128)
+    return fmt == 1
+               ? launch_bwd2<128, 1>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, S, scale, stream)
+               : launch_bwd2<128, 0>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, S, scale, stream);
+  return fmt == 1
+             ? launch_bwd2<64, 1>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, S, scale, stream)
+             : launch_bwd2<64, 0>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, S, scale, stream);
+}
+
+}  // namespace attn
+}  // namespace evg

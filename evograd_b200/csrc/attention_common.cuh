@@ -1,0 +1,88 @@
+// Building blocks shared by the attention kernels: tile geometry, TMA tile
+// loads, tcgen05 issue helpers for the two product shapes, 16-bit packing and
+// the shared-memory carve-up.
+#pragma once
+
+#include "evg_common.cuh"
+#include "sm100_umma.cuh"
+
+namespace evg {
+namespace attn {
+
+using namespace umma;
+
+constexpr int kTile = 128;  // rows of every tile (queries and keys alike)
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+// The running maximum of a query row is only moved when it would grow by more
+// than this many powers of two; until then probabilities may exceed 1 (by at
+// most 2^8), which float32 sums and 16-bit P absorb, and O needs no rescaling.
+constexpr float kRescaleThreshold = 8.0f;
+
+template <int HD> __host__ __device__ constexpr uint32_t tile_bytes() { return kTile * HD * 2; }
+
+// One 128-row tile = HD/64 TMA boxes of [128 x 64].
+template <int HD>
+__device__ __forceinline__ void load_tile(uint8_t* smem_tile, const CUtensorMap* map, int row0,
+                                          int outer, uint64_t* bar) {
+#pragma unroll
+  for (int a = 0; a < HD / 64; ++a)
+    tma_load_3d(smem_tile + a * (kTile * 128), map, a * 64, row0, outer, bar);
+}
+
+// S[128x128] = A[128xHD] * B[128xHD]^T, both tiles K-major.
+template <int HD>
+__device__ __forceinline__ void issue_scores(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr,
+                                             uint32_t idesc) {
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks)
+    mma_ss(d_tmem, desc_kmajor(a_saddr, kTile, ks), desc_kmajor(b_saddr, kTile, ks), idesc,
+           ks > 0 ? 1u : 0u);
+}
+// D[128xHD] (+)= A_tmem[128x128 (16-bit)] * B[128 rows x HD], B read MN-major.
+__device__ __forceinline__ void issue_accumulate(uint32_t d_tmem, uint32_t a_tmem,
+                                                 uint32_t b_saddr, uint32_t idesc,
+                                                 bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < kTile / 16; ++ks)
+    mma_ts(d_tmem, a_tmem + ks * 8, desc_mnmajor(b_saddr, kTile, ks), idesc,
+           (accumulate || ks > 0) ? 1u : 0u);
+}
+
+template <int FMT> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (FMT == 1) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+struct BlockSetup {
+  uint8_t* smem;        // 1024-byte aligned dynamic shared memory
+  uint64_t* bars;       // mbarriers
+  uint32_t* tmem_slot;  // where tcgen05.alloc writes the base address
+  int* abort_flag;
+};
+
+__device__ __forceinline__ BlockSetup carve(uint8_t* raw, size_t tile_region_bytes) {
+  BlockSetup b;
+  b.smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  b.bars = reinterpret_cast<uint64_t*>(b.smem + tile_region_bytes);
+  b.tmem_slot = reinterpret_cast<uint32_t*>(b.bars + 16);
+  b.abort_flag = reinterpret_cast<int*>(b.tmem_slot + 1);
+  return b;
+}
+constexpr size_t kControlBytes = 16 * 8 + 64;
+
+// Pipelined backward (attention_bwd2.cu): scratch = two float32 arrays padded
+// to whole tiles per (batch, head). fmt: 0 float16, 1 bfloat16.
+int64_t bwd2_workspace_bytes(int64_t B, int64_t H, int64_t S);
+int launch_bwd2_any(int head_dim, int fmt, const void* dout, const void* q, const void* k,
+                    const void* v, const void* o, const float* lse, void* dq, void* dk, void* dv,
+                    float* workspace, int64_t B, int64_t H, int64_t S, float scale,
+                    cudaStream_t stream);
+
+}  // namespace attn
+}  // namespace evg
