@@ -137,19 +137,23 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     void* __restrict__ dq_ptr, int S, int S_pad, float scale, long long wait_limit) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
-  BlockSetup bs = carve(smem_raw, 6 * TB);
+  BlockSetup bs = carve(smem_raw, 7 * TB);
   uint8_t* sQ = bs.smem;
   uint8_t* sDO = sQ + TB;
-  uint8_t* sK[2] = {sDO + TB, sDO + 2 * TB};
-  uint8_t* sV[2] = {sDO + 3 * TB, sDO + 4 * TB};
+  // K is needed twice per tile (scores at the start, dQ at the end), V once:
+  // three K stages and two V stages keep the TMA latency off the MMA thread.
+  uint8_t* sK[3] = {sDO + TB, sDO + 2 * TB, sDO + 3 * TB};
+  uint8_t* sV[2] = {sDO + 4 * TB, sDO + 5 * TB};
   uint64_t* qdo_full = bs.bars + 0;
-  uint64_t* kv_full = bs.bars + 1;   // [2]
-  uint64_t* kv_empty = bs.bars + 3;  // [2]
-  uint64_t* s_full = bs.bars + 5;    // [2]
-  uint64_t* dp_full = bs.bars + 7;
-  uint64_t* dp_free = bs.bars + 8;
-  uint64_t* ds_full = bs.bars + 9;   // [2]
-  uint64_t* done = bs.bars + 11;
+  uint64_t* k_full = bs.bars + 1;    // [3]
+  uint64_t* k_empty = bs.bars + 4;   // [3]
+  uint64_t* v_full = bs.bars + 7;    // [2]
+  uint64_t* v_empty = bs.bars + 9;   // [2]
+  uint64_t* s_full = bs.bars + 11;   // [2]
+  uint64_t* dp_full = bs.bars + 13;
+  uint64_t* dp_free = bs.bars + 14;
+  uint64_t* ds_full = bs.bars + 15;  // [2]
+  uint64_t* done = bs.bars + 17;
   const Roles r = roles();
   const int qtile = gridDim.x - 1 - blockIdx.x;  // heaviest tiles first
   const int bh = blockIdx.y;
@@ -160,8 +164,9 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (threadIdx.x == 0) {
     *bs.abort_flag = 0;
     mbar_init(qdo_full, 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(k_full + i, 1); mbar_init(k_empty + i, 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1);
+      mbar_init(v_full + i, 1); mbar_init(v_empty + i, 1);
       mbar_init(s_full + i, 1); mbar_init(ds_full + i, 8);
     }
     mbar_init(dp_full, 1); mbar_init(dp_free, 8); mbar_init(done, 1);
@@ -186,41 +191,48 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     load_tile<HD>(sQ, &map_q, q0, bh, qdo_full);
     load_tile<HD>(sDO, &map_do, q0, bh, qdo_full);
     for (int j = 0; j < n_it; ++j) {
-      const int st = j & 1;
-      if (j >= 2) mbar_wait(kv_empty + st, ((j - 2) >> 1) & 1, ctx, 501);
-      mbar_expect_tx(kv_full + st, 2 * TB);
-      load_tile<HD>(sK[st], &map_k, j * kTile, bh, kv_full + st);
-      load_tile<HD>(sV[st], &map_v, j * kTile, bh, kv_full + st);
+      const int ks = j % 3, vs = j & 1;
+      if (j >= 3) mbar_wait(k_empty + ks, ((j / 3) - 1) & 1, ctx, 501);
+      mbar_expect_tx(k_full + ks, TB);
+      load_tile<HD>(sK[ks], &map_k, j * kTile, bh, k_full + ks);
+      if (j >= 2) mbar_wait(v_empty + vs, ((j >> 1) - 1) & 1, ctx, 510);
+      mbar_expect_tx(v_full + vs, TB);
+      load_tile<HD>(sV[vs], &map_v, j * kTile, bh, v_full + vs);
     }
   } else if (r.is_mma && r.lane == 0) {
     mbar_wait(qdo_full, 0, ctx, 502);
-    mbar_wait(kv_full + 0, 0, ctx, 503);
+    mbar_wait(k_full + 0, 0, ctx, 503);
     tc_fence_after_sync();
     issue_scores<HD>(tSb[0], smem_u32(sQ), smem_u32(sK[0]), idesc_s);
     mma_commit(s_full + 0);
+    mbar_wait(v_full + 0, 0, ctx, 511);
+    tc_fence_after_sync();
     issue_scores<HD>(tDP, smem_u32(sDO), smem_u32(sV[0]), idesc_s);
     mma_commit(dp_full);
+    mma_commit(v_empty + 0);
     for (int j = 0; j < n_it; ++j) {
       const int b = j & 1;
       if (j + 1 < n_it) {
-        const int b1 = (j + 1) & 1;
-        mbar_wait(kv_full + b1, ((j + 1) >> 1) & 1, ctx, 504);
+        const int b1 = (j + 1) & 1, k1 = (j + 1) % 3;
+        mbar_wait(k_full + k1, ((j + 1) / 3) & 1, ctx, 504);
         tc_fence_after_sync();
-        issue_scores<HD>(tSb[b1], smem_u32(sQ), smem_u32(sK[b1]), idesc_s);
+        issue_scores<HD>(tSb[b1], smem_u32(sQ), smem_u32(sK[k1]), idesc_s);
         mma_commit(s_full + b1);
+        mbar_wait(v_full + b1, ((j + 1) >> 1) & 1, ctx, 512);
         mbar_wait(dp_free, j & 1, ctx, 505);
         tc_fence_after_sync();
         issue_scores<HD>(tDP, smem_u32(sDO), smem_u32(sV[b1]), idesc_s);
         mma_commit(dp_full);
+        mma_commit(v_empty + b1);
       }
       mbar_wait(ds_full + b, (j >> 1) & 1, ctx, 506);
       tc_fence_after_sync();
       // dS is stored as two 32-column halves at buffer columns 0 and 64.
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks)
-        mma_ts(tDQ, tSb[b] + (ks >> 2) * 64 + (ks & 3) * 8, desc_mnmajor(smem_u32(sK[b]), kTile, ks),
-               idesc_d, (j > 0 || ks > 0) ? 1u : 0u);
-      mma_commit(kv_empty + b);
+        mma_ts(tDQ, tSb[b] + (ks >> 2) * 64 + (ks & 3) * 8,
+               desc_mnmajor(smem_u32(sK[j % 3]), kTile, ks), idesc_d, (j > 0 || ks > 0) ? 1u : 0u);
+      mma_commit(k_empty + (j % 3));
     }
     mma_commit(done);
   } else if (r.is_compute) {
@@ -492,7 +504,7 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
     if (int rc = check_launch("causal_attention_bwd dkdv")) return rc;
   }
   {
-    const size_t smem = 6 * tile_bytes<HD>() + kControlBytes + 1024;
+    const size_t smem = 7 * tile_bytes<HD>() + kControlBytes + 1024;
     auto kern = attn_bwd2_dq_kernel<HD, FMT>;
     if (int rc = reserve_smem(kern, smem)) return rc;
     kern<<<grid, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq, (int)S,

@@ -70,11 +70,11 @@ __device__ __forceinline__ BlockSetup carve(uint8_t* raw, size_t tile_region_byt
   BlockSetup b;
   b.smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   b.bars = reinterpret_cast<uint64_t*>(b.smem + tile_region_bytes);
-  b.tmem_slot = reinterpret_cast<uint32_t*>(b.bars + 16);
+  b.tmem_slot = reinterpret_cast<uint32_t*>(b.bars + 24);
   b.abort_flag = reinterpret_cast<int*>(b.tmem_slot + 1);
   return b;
 }
-constexpr size_t kControlBytes = 16 * 8 + 64;
+constexpr size_t kControlBytes = 24 * 8 + 64;
 
 // Pipelined backward (attention_bwd2.cu): scratch = two float32 arrays padded
 // to whole tiles per (batch, head). fmt: 0 float16, 1 bfloat16.
