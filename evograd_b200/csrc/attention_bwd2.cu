@@ -228,10 +228,11 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       mbar_wait(ds_full + b, (j >> 1) & 1, ctx, 506);
       tc_fence_after_sync();
       // dS is stored as two 32-column halves at buffer columns 0 and 64.
+      const DescBase kb = desc_base_mnmajor(smem_u32(sK[j % 3]), kTile);
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks)
-        mma_ts(tDQ, tSb[b] + (ks >> 2) * 64 + (ks & 3) * 8,
-               desc_mnmajor(smem_u32(sK[j % 3]), kTile, ks), idesc_d, (j > 0 || ks > 0) ? 1u : 0u);
+        mma_ts(tDQ, tSb[b] + (ks >> 2) * 64 + (ks & 3) * 8, desc_at(kb, kstep_mnmajor(ks)), idesc_d,
+               (j > 0 || ks > 0) ? 1u : 0u);
       mma_commit(k_empty + (j % 3));
     }
     mma_commit(done);
@@ -363,18 +364,20 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       bulk_load_1d(s_stat + st * 256 + 128, delta_pad + (size_t)bh * S_pad + q0, 512, q_full + st);
     }
   } else if (r.is_mma && r.lane == 0) {
+    const DescBase k_base = desc_base_kmajor(smem_u32(sK)), v_base = desc_base_kmajor(smem_u32(sV));
     // Scores of chunk c: B operand = 64 rows of the Q / dO tile starting at row 64*(c&1).
     auto issue_chunk_scores = [&](int c) {
       const int st = (c >> 1) & 1, hq = c & 1, b = c & 1;
-      const uint32_t qa = smem_u32(sQ[st]) + hq * 64 * 128, da = smem_u32(sDO[st]) + hq * 64 * 128;
+      const DescBase qa = desc_base_kmajor(smem_u32(sQ[st]) + hq * 64 * 128);
+      const DescBase da = desc_base_kmajor(smem_u32(sDO[st]) + hq * 64 * 128);
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks)
-        mma_ss(tSb[b], desc_kmajor(smem_u32(sK), kTile, ks), desc_kmajor(qa, kTile, ks), idesc_s,
-               ks > 0 ? 1u : 0u);
+        mma_ss(tSb[b], desc_at(k_base, kstep_kmajor(kTile, ks)), desc_at(qa, kstep_kmajor(kTile, ks)),
+               idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks)
-        mma_ss(tPb[b], desc_kmajor(smem_u32(sV), kTile, ks), desc_kmajor(da, kTile, ks), idesc_s,
-               ks > 0 ? 1u : 0u);
+        mma_ss(tPb[b], desc_at(v_base, kstep_kmajor(kTile, ks)), desc_at(da, kstep_kmajor(kTile, ks)),
+               idesc_s, ks > 0 ? 1u : 0u);
       mma_commit(sdp_full + b);
     };
     mbar_wait(kv_full, 0, ctx, 602);
@@ -394,14 +397,16 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       mbar_wait(pds_full + b, (c >> 1) & 1, ctx, 605);
       tc_fence_after_sync();
       // 4 k-steps of 16 queries; packed halves sit at buffer columns 0 and 32.
+      const DescBase dob = desc_base_mnmajor(smem_u32(sDO[st]) + hq * 64 * 128, kTile);
+      const DescBase qb = desc_base_mnmajor(smem_u32(sQ[st]) + hq * 64 * 128, kTile);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        mma_ts(tDV, tSb[b] + (ks >> 1) * 32 + (ks & 1) * 8,
-               desc_mnmajor(smem_u32(sDO[st]), kTile, hq * 4 + ks), idesc_d, (c > 0 || ks > 0) ? 1u : 0u);
+        mma_ts(tDV, tSb[b] + (ks >> 1) * 32 + (ks & 1) * 8, desc_at(dob, kstep_mnmajor(ks)), idesc_d,
+               (c > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        mma_ts(tDK, tPb[b] + (ks >> 1) * 32 + (ks & 1) * 8,
-               desc_mnmajor(smem_u32(sQ[st]), kTile, hq * 4 + ks), idesc_d, (c > 0 || ks > 0) ? 1u : 0u);
+        mma_ts(tDK, tPb[b] + (ks >> 1) * 32 + (ks & 1) * 8, desc_at(qb, kstep_mnmajor(ks)), idesc_d,
+               (c > 0 || ks > 0) ? 1u : 0u);
       if (hq == 1) mma_commit(q_empty + st);
     }
     mma_commit(done);

@@ -30,22 +30,24 @@ __device__ __forceinline__ void load_tile(uint8_t* smem_tile, const CUtensorMap*
     tma_load_3d(smem_tile + a * (kTile * 128), map, a * 64, row0, outer, bar);
 }
 
-// S[128x128] = A[128xHD] * B[128xHD]^T, both tiles K-major.
+// S[128xN] = A[128xHD] * B[NxHD]^T, both tiles K-major (N from the descriptor).
 template <int HD>
 __device__ __forceinline__ void issue_scores(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr,
                                              uint32_t idesc) {
+  const DescBase a = desc_base_kmajor(a_saddr), b = desc_base_kmajor(b_saddr);
 #pragma unroll
   for (int ks = 0; ks < HD / 16; ++ks)
-    mma_ss(d_tmem, desc_kmajor(a_saddr, kTile, ks), desc_kmajor(b_saddr, kTile, ks), idesc,
+    mma_ss(d_tmem, desc_at(a, kstep_kmajor(kTile, ks)), desc_at(b, kstep_kmajor(kTile, ks)), idesc,
            ks > 0 ? 1u : 0u);
 }
 // D[128xHD] (+)= A_tmem[128x128 (16-bit)] * B[128 rows x HD], B read MN-major.
 __device__ __forceinline__ void issue_accumulate(uint32_t d_tmem, uint32_t a_tmem,
                                                  uint32_t b_saddr, uint32_t idesc,
                                                  bool accumulate) {
+  const DescBase b = desc_base_mnmajor(b_saddr, kTile);
 #pragma unroll
   for (int ks = 0; ks < kTile / 16; ++ks)
-    mma_ts(d_tmem, a_tmem + ks * 8, desc_mnmajor(b_saddr, kTile, ks), idesc,
+    mma_ts(d_tmem, a_tmem + ks * 8, desc_at(b, kstep_mnmajor(ks)), idesc,
            (accumulate || ks > 0) ? 1u : 0u);
 }
 

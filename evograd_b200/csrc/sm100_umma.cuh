@@ -203,6 +203,34 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_saddr, uint32_t r
   return smem_desc_sw128(addr, rows * kAtomBytesPerRow, kAtomGroupBytes);
 }
 
+// The same descriptors split into a per-tile base and a per-k-step increment, so
+// that the single issuing thread spends one integer add per operand per MMA
+// (building a descriptor from scratch costs more issue cycles than the MMA takes
+// to execute). The start-address field holds (address >> 4) in 14 bits; shared
+// memory is < 256 KB, so adding a k-step offset never carries out of the field.
+struct DescBase {
+  uint32_t lo;  // start address | leading byte offset
+  uint32_t hi;  // stride byte offset | version | swizzle mode
+};
+__device__ __forceinline__ DescBase desc_base_kmajor(uint32_t tile_saddr) {
+  return DescBase{((tile_saddr & 0x3FFFFu) >> 4) | (1u << 16),
+                  (kAtomGroupBytes >> 4) | (1u << 14) | (2u << 29)};
+}
+__device__ __forceinline__ DescBase desc_base_mnmajor(uint32_t tile_saddr, uint32_t rows) {
+  return DescBase{((tile_saddr & 0x3FFFFu) >> 4) | (((rows * kAtomBytesPerRow) >> 4) << 16),
+                  (kAtomGroupBytes >> 4) | (1u << 14) | (2u << 29)};
+}
+// k-step increments of the start-address field (units of 16 bytes).
+__host__ __device__ constexpr uint32_t kstep_kmajor(uint32_t rows, int ks) {
+  return ((uint32_t)(ks >> 2) * rows * kAtomBytesPerRow + (uint32_t)(ks & 3) * 32u) >> 4;
+}
+__host__ __device__ constexpr uint32_t kstep_mnmajor(int ks) {
+  return ((uint32_t)ks * 16u * kAtomBytesPerRow) >> 4;
+}
+__device__ __forceinline__ uint64_t desc_at(const DescBase& b, uint32_t step) {
+  return ((uint64_t)b.hi << 32) | (uint64_t)(b.lo + step);
+}
+
 // Instruction descriptor for kind::f16 with float32 accumulation.
 // fmt: 0 = f16, 1 = bf16. *_mn: 1 when that operand is MN-major.
 __host__ __device__ constexpr uint32_t instr_desc_f16(int fmt, int m, int n, int a_mn, int b_mn) {
