@@ -199,31 +199,31 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       mbar_expect_tx(v_full + vs, TB);
       load_tile<HD>(sV[vs], &map_v, j * kTile, bh, v_full + vs);
     }
-  } else if (r.is_mma && r.lane == 0) {
+  } else if (r.is_mma) {
+    // All 32 lanes run this program; `lead` predicates the tcgen05 instructions.
+    const bool lead = elect_one();
     mbar_wait(qdo_full, 0, ctx, 502);
     mbar_wait(k_full + 0, 0, ctx, 503);
     tc_fence_after_sync();
-    issue_scores<HD>(tSb[0], smem_u32(sQ), smem_u32(sK[0]), idesc_s);
-    mma_commit(s_full + 0);
+    issue_scores<HD>(lead, tSb[0], smem_u32(sQ), smem_u32(sK[0]), idesc_s);
+    if (lead) mma_commit(s_full + 0);
     mbar_wait(v_full + 0, 0, ctx, 511);
     tc_fence_after_sync();
-    issue_scores<HD>(tDP, smem_u32(sDO), smem_u32(sV[0]), idesc_s);
-    mma_commit(dp_full);
-    mma_commit(v_empty + 0);
+    issue_scores<HD>(lead, tDP, smem_u32(sDO), smem_u32(sV[0]), idesc_s);
+    if (lead) { mma_commit(dp_full); mma_commit(v_empty + 0); }
     for (int j = 0; j < n_it; ++j) {
       const int b = j & 1;
       if (j + 1 < n_it) {
         const int b1 = (j + 1) & 1, k1 = (j + 1) % 3;
         mbar_wait(k_full + k1, ((j + 1) / 3) & 1, ctx, 504);
         tc_fence_after_sync();
-        issue_scores<HD>(tSb[b1], smem_u32(sQ), smem_u32(sK[k1]), idesc_s);
-        mma_commit(s_full + b1);
+        issue_scores<HD>(lead, tSb[b1], smem_u32(sQ), smem_u32(sK[k1]), idesc_s);
+        if (lead) mma_commit(s_full + b1);
         mbar_wait(v_full + b1, ((j + 1) >> 1) & 1, ctx, 512);
         mbar_wait(dp_free, j & 1, ctx, 505);
         tc_fence_after_sync();
-        issue_scores<HD>(tDP, smem_u32(sDO), smem_u32(sV[b1]), idesc_s);
-        mma_commit(dp_full);
-        mma_commit(v_empty + b1);
+        issue_scores<HD>(lead, tDP, smem_u32(sDO), smem_u32(sV[b1]), idesc_s);
+        if (lead) { mma_commit(dp_full); mma_commit(v_empty + b1); }
       }
       mbar_wait(ds_full + b, (j >> 1) & 1, ctx, 506);
       tc_fence_after_sync();
@@ -231,11 +231,13 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const DescBase kb = desc_base_mnmajor(smem_u32(sK[j % 3]), kTile);
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks)
-        mma_ts(tDQ, tSb[b] + (ks >> 2) * 64 + (ks & 3) * 8, desc_at(kb, kstep_mnmajor(ks)), idesc_d,
-               (j > 0 || ks > 0) ? 1u : 0u);
-      mma_commit(k_empty + (j % 3));
+        if (lead)
+          mma_ts(tDQ, tSb[b] + (ks >> 2) * 64 + (ks & 3) * 8, desc_at(kb, kstep_mnmajor(ks)),
+                 idesc_d, (j > 0 || ks > 0) ? 1u : 0u);
+      if (lead) mma_commit(k_empty + (j % 3));
+      __syncwarp();
     }
-    mma_commit(done);
+    if (lead) mma_commit(done);
   } else if (r.is_compute) {
     const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
     const int q_glob = q0 + r.row;
@@ -363,7 +365,8 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       bulk_load_1d(s_stat + st * 256, lse2_pad + (size_t)bh * S_pad + q0, 512, q_full + st);
       bulk_load_1d(s_stat + st * 256 + 128, delta_pad + (size_t)bh * S_pad + q0, 512, q_full + st);
     }
-  } else if (r.is_mma && r.lane == 0) {
+  } else if (r.is_mma) {
+    const bool lead = elect_one();
     const DescBase k_base = desc_base_kmajor(smem_u32(sK)), v_base = desc_base_kmajor(smem_u32(sV));
     // Scores of chunk c: B operand = 64 rows of the Q / dO tile starting at row 64*(c&1).
     auto issue_chunk_scores = [&](int c) {
@@ -372,13 +375,15 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const DescBase da = desc_base_kmajor(smem_u32(sDO[st]) + hq * 64 * 128);
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks)
-        mma_ss(tSb[b], desc_at(k_base, kstep_kmajor(kTile, ks)), desc_at(qa, kstep_kmajor(kTile, ks)),
-               idesc_s, ks > 0 ? 1u : 0u);
+        if (lead)
+          mma_ss(tSb[b], desc_at(k_base, kstep_kmajor(kTile, ks)),
+                 desc_at(qa, kstep_kmajor(kTile, ks)), idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks)
-        mma_ss(tPb[b], desc_at(v_base, kstep_kmajor(kTile, ks)), desc_at(da, kstep_kmajor(kTile, ks)),
-               idesc_s, ks > 0 ? 1u : 0u);
-      mma_commit(sdp_full + b);
+        if (lead)
+          mma_ss(tPb[b], desc_at(v_base, kstep_kmajor(kTile, ks)),
+                 desc_at(da, kstep_kmajor(kTile, ks)), idesc_s, ks > 0 ? 1u : 0u);
+      if (lead) mma_commit(sdp_full + b);
     };
     mbar_wait(kv_full, 0, ctx, 602);
     mbar_wait(q_full + 0, 0, ctx, 603);
@@ -401,15 +406,18 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const DescBase qb = desc_base_mnmajor(smem_u32(sQ[st]) + hq * 64 * 128, kTile);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        mma_ts(tDV, tSb[b] + (ks >> 1) * 32 + (ks & 1) * 8, desc_at(dob, kstep_mnmajor(ks)), idesc_d,
-               (c > 0 || ks > 0) ? 1u : 0u);
+        if (lead)
+          mma_ts(tDV, tSb[b] + (ks >> 1) * 32 + (ks & 1) * 8, desc_at(dob, kstep_mnmajor(ks)),
+                 idesc_d, (c > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        mma_ts(tDK, tPb[b] + (ks >> 1) * 32 + (ks & 1) * 8, desc_at(qb, kstep_mnmajor(ks)), idesc_d,
-               (c > 0 || ks > 0) ? 1u : 0u);
-      if (hq == 1) mma_commit(q_empty + st);
+        if (lead)
+          mma_ts(tDK, tPb[b] + (ks >> 1) * 32 + (ks & 1) * 8, desc_at(qb, kstep_mnmajor(ks)),
+                 idesc_d, (c > 0 || ks > 0) ? 1u : 0u);
+      if (lead && hq == 1) mma_commit(q_empty + st);
+      __syncwarp();
     }
-    mma_commit(done);
+    if (lead) mma_commit(done);
   } else if (r.is_compute) {
     const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
     const int kv_glob = kv0 + r.row;

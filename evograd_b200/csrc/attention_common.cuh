@@ -32,13 +32,19 @@ __device__ __forceinline__ void load_tile(uint8_t* smem_tile, const CUtensorMap*
 
 // S[128xN] = A[128xHD] * B[NxHD]^T, both tiles K-major (N from the descriptor).
 template <int HD>
-__device__ __forceinline__ void issue_scores(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr,
-                                             uint32_t idesc) {
+__device__ __forceinline__ void issue_scores(bool lead, uint32_t d_tmem, uint32_t a_saddr,
+                                             uint32_t b_saddr, uint32_t idesc) {
   const DescBase a = desc_base_kmajor(a_saddr), b = desc_base_kmajor(b_saddr);
 #pragma unroll
   for (int ks = 0; ks < HD / 16; ++ks)
-    mma_ss(d_tmem, desc_at(a, kstep_kmajor(kTile, ks)), desc_at(b, kstep_kmajor(kTile, ks)), idesc,
-           ks > 0 ? 1u : 0u);
+    if (lead)
+      mma_ss(d_tmem, desc_at(a, kstep_kmajor(kTile, ks)), desc_at(b, kstep_kmajor(kTile, ks)),
+             idesc, ks > 0 ? 1u : 0u);
+}
+template <int HD>
+__device__ __forceinline__ void issue_scores(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr,
+                                             uint32_t idesc) {
+  issue_scores<HD>(true, d_tmem, a_saddr, b_saddr, idesc);
 }
 // D[128xHD] (+)= A_tmem[128x128 (16-bit)] * B[128 rows x HD], B read MN-major.
 __device__ __forceinline__ void issue_accumulate(uint32_t d_tmem, uint32_t a_tmem,

@@ -238,6 +238,20 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(int fmt, int m, int n, int
          ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// One lane of a converged warp (warp-collective). The issuing warp runs its
+// whole program on all 32 lanes and predicates only the tcgen05 instruction
+// with this, so that descriptors and addresses stay warp-uniform values (the
+// instruction takes them from uniform registers; computing them inside a
+// divergent single-lane branch forces per-operand transfers that cost more
+// issue time than the MMA takes to execute).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                        uint32_t idesc, uint32_t accumulate) {
