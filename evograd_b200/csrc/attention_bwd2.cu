@@ -257,19 +257,29 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       tmem_wait_ld();
       warp_arrive(dp_free, r.lane);
-      const bool diag = (j == qtile);
       const int kv0 = j * kTile + r.half * 64;
+      const float nlse = -lse2;
       uint32_t dd[32];
+      if (j == qtile) {  // diagonal tile: keys after the query are masked
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float d[2];
+        for (int i = 0; i < 32; ++i) {
+          float d[2];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          float pe = exp2f(__uint_as_float(sr[2 * i + e]) * scale_log2 - lse2);
-          if (diag && kv0 + 2 * i + e > q_glob) pe = 0.f;
-          d[e] = pe * (__uint_as_float(dr[2 * i + e]) - delta);
+          for (int e = 0; e < 2; ++e) {
+            float pe = fast_exp2(fmaf(__uint_as_float(sr[2 * i + e]), scale_log2, nlse));
+            if (kv0 + 2 * i + e > q_glob) pe = 0.f;
+            d[e] = pe * (__uint_as_float(dr[2 * i + e]) - delta);
+          }
+          dd[i] = pack2<FMT>(d[0], d[1]);
         }
-        dd[i] = pack2<FMT>(d[0], d[1]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * i]), scale_log2, nlse));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * i + 1]), scale_log2, nlse));
+          dd[i] = pack2<FMT>(p0 * (__uint_as_float(dr[2 * i]) - delta),
+                             p1 * (__uint_as_float(dr[2 * i + 1]) - delta));
+        }
       }
       tmem_st32(tSb[b] + lane_base + r.half * 64, dd);
       tmem_wait_st();
@@ -434,23 +444,38 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const int col0 = hq * 64 + r.half * 32;  // first query column (inside the tile) of this warp
       const float4* lse4 = reinterpret_cast<const float4*>(s_stat + st * 256 + col0);
       const float4* del4 = reinterpret_cast<const float4*>(s_stat + st * 256 + 128 + col0);
-      const bool diag = (it == 0);
       const int q_first = (kvt + it) * kTile + col0;
       uint32_t pp[16], dd[16];
+      if (it == 0) {  // diagonal tile: queries before the key are masked
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        const float4 l4 = lse4[g], d4 = del4[g];
-        const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-        float p[4], d[4];
+        for (int g = 0; g < 8; ++g) {
+          const float4 l4 = lse4[g], d4 = del4[g];
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          float p[4], d[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float pe = exp2f(__uint_as_float(sr[4 * g + e]) * scale_log2 - lv[e]);
-          if (diag && q_first + 4 * g + e < kv_glob) pe = 0.f;
-          p[e] = pe;
-          d[e] = pe * (__uint_as_float(dr[4 * g + e]) - dv[e]);
+          for (int e = 0; e < 4; ++e) {
+            float pe = fast_exp2(fmaf(__uint_as_float(sr[4 * g + e]), scale_log2, -lv[e]));
+            if (q_first + 4 * g + e < kv_glob) pe = 0.f;
+            p[e] = pe;
+            d[e] = pe * (__uint_as_float(dr[4 * g + e]) - dv[e]);
+          }
+          pp[2 * g] = pack2<FMT>(p[0], p[1]); pp[2 * g + 1] = pack2<FMT>(p[2], p[3]);
+          dd[2 * g] = pack2<FMT>(d[0], d[1]); dd[2 * g + 1] = pack2<FMT>(d[2], d[3]);
         }
-        pp[2 * g] = pack2<FMT>(p[0], p[1]); pp[2 * g + 1] = pack2<FMT>(p[2], p[3]);
-        dd[2 * g] = pack2<FMT>(d[0], d[1]); dd[2 * g + 1] = pack2<FMT>(d[2], d[3]);
+      } else {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 l4 = lse4[g], d4 = del4[g];
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          float p[4], d[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            p[e] = fast_exp2(fmaf(__uint_as_float(sr[4 * g + e]), scale_log2, -lv[e]));
+            d[e] = p[e] * (__uint_as_float(dr[4 * g + e]) - dv[e]);
+          }
+          pp[2 * g] = pack2<FMT>(p[0], p[1]); pp[2 * g + 1] = pack2<FMT>(p[2], p[3]);
+          dd[2 * g] = pack2<FMT>(d[0], d[1]); dd[2 * g + 1] = pack2<FMT>(d[2], d[3]);
+        }
       }
       tmem_st16(tSb[b] + lane_base + r.half * 32, pp);
       tmem_st16(tPb[b] + lane_base + r.half * 32, dd);

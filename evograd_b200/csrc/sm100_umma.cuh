@@ -238,6 +238,14 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(int fmt, int m, int n, int
          ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// 2^x on the special-function unit, denormals flushed (inputs here are scores
+// minus a log-sum-exp: anything that small is zero after rounding to 16 bits).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // One lane of a converged warp (warp-collective). The issuing warp runs its
 // whole program on all 32 lanes and predicates only the tcgen05 instruction
 // with this, so that descriptors and addresses stay warp-uniform values (the
