@@ -47,14 +47,20 @@ __device__ __forceinline__ void issue_scores(uint32_t d_tmem, uint32_t a_saddr, 
   issue_scores<HD>(true, d_tmem, a_saddr, b_saddr, idesc);
 }
 // D[128xHD] (+)= A_tmem[128x128 (16-bit)] * B[128 rows x HD], B read MN-major.
-__device__ __forceinline__ void issue_accumulate(uint32_t d_tmem, uint32_t a_tmem,
+__device__ __forceinline__ void issue_accumulate(bool lead, uint32_t d_tmem, uint32_t a_tmem,
                                                  uint32_t b_saddr, uint32_t idesc,
                                                  bool accumulate) {
   const DescBase b = desc_base_mnmajor(b_saddr, kTile);
 #pragma unroll
   for (int ks = 0; ks < kTile / 16; ++ks)
-    mma_ts(d_tmem, a_tmem + ks * 8, desc_at(b, kstep_mnmajor(ks)), idesc,
-           (accumulate || ks > 0) ? 1u : 0u);
+    if (lead)
+      mma_ts(d_tmem, a_tmem + ks * 8, desc_at(b, kstep_mnmajor(ks)), idesc,
+             (accumulate || ks > 0) ? 1u : 0u);
+}
+__device__ __forceinline__ void issue_accumulate(uint32_t d_tmem, uint32_t a_tmem,
+                                                 uint32_t b_saddr, uint32_t idesc,
+                                                 bool accumulate) {
+  issue_accumulate(true, d_tmem, a_tmem, b_saddr, idesc, accumulate);
 }
 
 template <int FMT> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
