@@ -666,6 +666,9 @@ extern "C" int evg_causal_attention_fwd(const void* q, const void* k, const void
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
     return fail(EVG_EALIGN, "causal_attention_fwd: q/k/v/o must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
+  if (tune("attention.variant") != 1)  // default: two query tiles per block, warp-specialised
+    return attn::launch_fwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, q, k, v, o, lse, B, H, S, scale,
+                                 st);
   if (D == 128) {
     return dtype == EVG_BF16 ? launch_fwd<128, 1>(q, k, v, o, lse, B, H, S, scale, st)
                              : launch_fwd<128, 0>(q, k, v, o, lse, B, H, S, scale, st);

@@ -90,6 +90,9 @@ __device__ __forceinline__ BlockSetup carve(uint8_t* raw, size_t tile_region_byt
 }
 constexpr size_t kControlBytes = 24 * 8 + 64;
 
+// Two-tile warp-specialised forward (attention_fwd2.cu).
+int launch_fwd2_any(int head_dim, int fmt, const void* q, const void* k, const void* v, void* o,
+                    float* lse, int64_t B, int64_t H, int64_t S, float scale, cudaStream_t stream);
 // Pipelined backward (attention_bwd2.cu): scratch = two float32 arrays padded
 // to whole tiles per (batch, head). fmt: 0 float16, 1 bfloat16.
 int64_t bwd2_workspace_bytes(int64_t B, int64_t H, int64_t S);
