@@ -528,8 +528,14 @@ def run_ours(args):
     peaks, peak_source = measured_peaks()
     wl = WORKLOADS[args.workload](device)
 
+    # Leg 1 (value): K steps between one event pair, nothing else on the stream.
+    # Leg 2 (roofline): the same K steps again with an event pair around forward and
+    # backward of every step (the extra event records cost a few microseconds per
+    # step, which is why they are kept out of leg 1).
     with ClockSampler(local) as clocks:
-        ms, totals, launches, n_sets = measure_device(wl, args.steps, args.warmup, world)
+        ms, _unused, launches, n_sets = measure_device(wl, args.steps, args.warmup, world,
+                                                       sections=False)
+        _ms2, totals, _l2, _n2 = measure_device(wl, args.steps, args.warmup, world, sections=True)
     step_ms = ms / args.steps
     if wl.bound == "hbm":
         metric = f"fwd+bwd achieved HBM GB/s ({wl.name})"
@@ -567,7 +573,8 @@ def run_ours(args):
         "dtype": wl.dtype, "data": "synthetic",
         "config": {**wl.config(), "l2": f"{n_sets} rotating input set(s), each pass reads data not in L2",
                    "parallelism": f"rows x{world}" if world > 1 else "1 gpu",
-                   "launch": "eager, current stream"},
+                   "launch": "eager, current stream",
+                   "roofline_loop": "same K steps re-run with CUDA events around forward and backward"},
         "e2e": e2e,
         "gpu_launches": launches,
         "roofline": roofline,

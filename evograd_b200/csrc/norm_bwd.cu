@@ -226,14 +226,17 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
   if (tid == 0)
     for (int64_t i = 0; i < stages && i < n_mine; ++i) issue(i);
 
-  float acc_w[VPT][N];
-  float acc_b[LN ? VPT : 1][N];
+  // Element-wise float32 work is done on packed pairs (f32x2): element 2p and
+  // 2p+1 of a vector share one instruction.
+  constexpr int P = N / 2;  // pairs per 128-bit input vector
+  f32x2 acc_w[VPT][P];
+  f32x2 acc_b[LN ? VPT : 1][P];
 #pragma unroll
   for (int k = 0; k < VPT; ++k)
 #pragma unroll
-    for (int j = 0; j < N; ++j) {
-      acc_w[k][j] = 0.f;
-      if constexpr (LN) acc_b[k][j] = 0.f;
+    for (int j = 0; j < P; ++j) {
+      acc_w[k][j] = 0ull;
+      if constexpr (LN) acc_b[k][j] = 0ull;
     }
   const float inv_cols = 1.0f / (float)cols;
   float rs_next = 0.f, mu_next = 0.f;
@@ -255,11 +258,10 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
     mbar_wait(&full[s], parity, ctx, 401);
     const uint8_t* sx = ring + (size_t)s * 2 * row_bytes;
     const uint8_t* sg = sx + row_bytes;
+    const f32x2 rs2 = f2_splat(rs), nmr2 = f2_splat(nmr);
 
-    float xh[VPT][N], gy[VPT][N];
-    float c[NV];
-#pragma unroll
-    for (int q = 0; q < NV; ++q) c[q] = 0.f;
+    f32x2 xh[VPT][P], gy[VPT][P];
+    f32x2 c0 = 0ull, c1 = 0ull;  // sum g*xh, sum g (g = dy*w), per pair lane
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int idx = tid + k * THREADS;
@@ -270,26 +272,40 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
         xv = *reinterpret_cast<const uint4*>(sx + (size_t)idx * 16);
         gv = *reinterpret_cast<const uint4*>(sg + (size_t)idx * 16);
       }
-      unpack<T>(xv, xh[k]);
-      unpack<T>(gv, gy[k]);
+      float xf[N], gf[N];
+      unpack<T>(xv, xf);
+      unpack<T>(gv, gf);  // padded vectors have dy = 0 and add nothing below
 #pragma unroll
       for (int qq = 0; qq < Q; ++qq) {
         const float4 wv = w4[qq * nvec + sidx];
-        const float wj[4] = {wv.x, wv.y, wv.z, wv.w};
+        const f32x2 wp[2] = {f2_make(wv.x, wv.y), f2_make(wv.z, wv.w)};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int e = 4 * qq + j;
-          xh[k][e] = LN ? fmaf(xh[k][e], rs, nmr) : xh[k][e] * rs;
-          const float g = gy[k][e] * wj[j];  // padded vectors have dy = 0
-          c[0] = fmaf(g, xh[k][e], c[0]);
-          if constexpr (LN) c[1] += g;
+        for (int h = 0; h < 2; ++h) {
+          const int pi = 2 * qq + h;
+          const f32x2 xp = f2_make(xf[2 * pi], xf[2 * pi + 1]);
+          gy[k][pi] = f2_make(gf[2 * pi], gf[2 * pi + 1]);
+          xh[k][pi] = LN ? f2_fma(xp, rs2, nmr2) : f2_mul(xp, rs2);
+          const f32x2 g = f2_mul(gy[k][pi], wp[h]);
+          c0 = f2_fma(g, xh[k][pi], c0);
+          if constexpr (LN) c1 = f2_add(c1, g);
         }
+      }
+    }
+    float c[NV];
+    {
+      float lo, hi;
+      f2_split(c0, lo, hi);
+      c[0] = lo + hi;
+      if constexpr (LN) {
+        f2_split(c1, lo, hi);
+        c[1] = lo + hi;
       }
     }
     block_allreduce<NV, SumOp>(c, scratch, phase);  // everyone is done with stage s
     if (tid == 0 && i + stages < n_mine) issue(i + stages);
-    const float a_x = -rs * (c[0] * inv_cols);
-    const float a_0 = LN ? -rs * (c[1] * inv_cols) : 0.f;
+    // dx = rs*g - rs*mean(g) - rs*mean(g*xh)*xh
+    const f32x2 a_x = f2_splat(-rs * (c[0] * inv_cols));
+    const f32x2 a_0 = f2_splat(LN ? -rs * (c[1] * inv_cols) : 0.f);
     T* dr = dx + row * cols;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
@@ -299,14 +315,15 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
 #pragma unroll
         for (int qq = 0; qq < Q; ++qq) {
           const float4 wv = w4[qq * nvec + idx];
-          const float wj[4] = {wv.x, wv.y, wv.z, wv.w};
+          const f32x2 wp[2] = {f2_make(wv.x, wv.y), f2_make(wv.z, wv.w)};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int e = 4 * qq + j;
-            const float g = gy[k][e] * wj[j];
-            o[e] = fmaf(xh[k][e], a_x, fmaf(g, rs, a_0));
-            acc_w[k][e] = fmaf(gy[k][e], xh[k][e], acc_w[k][e]);
-            if constexpr (LN) acc_b[k][e] += gy[k][e];
+          for (int h = 0; h < 2; ++h) {
+            const int pi = 2 * qq + h;
+            const f32x2 g = f2_mul(gy[k][pi], wp[h]);
+            const f32x2 op = f2_fma(xh[k][pi], a_x, f2_fma(g, rs2, a_0));
+            f2_split(op, o[2 * pi], o[2 * pi + 1]);
+            acc_w[k][pi] = f2_fma(gy[k][pi], xh[k][pi], acc_w[k][pi]);
+            if constexpr (LN) acc_b[k][pi] = f2_add(acc_b[k][pi], gy[k][pi]);
           }
         }
         st_vec(dr + (size_t)idx * N, pack<T>(o));
@@ -322,13 +339,15 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
     if (idx < nvec) {
 #pragma unroll
       for (int qq = 0; qq < Q; ++qq) {
-        *reinterpret_cast<float4*>(pw + (size_t)idx * N + 4 * qq) =
-            make_float4(acc_w[k][4 * qq], acc_w[k][4 * qq + 1], acc_w[k][4 * qq + 2],
-                        acc_w[k][4 * qq + 3]);
-        if constexpr (LN)
-          *reinterpret_cast<float4*>(pb + (size_t)idx * N + 4 * qq) =
-              make_float4(acc_b[k][4 * qq], acc_b[k][4 * qq + 1], acc_b[k][4 * qq + 2],
-                          acc_b[k][4 * qq + 3]);
+        float a0, a1, a2, a3;
+        f2_split(acc_w[k][2 * qq], a0, a1);
+        f2_split(acc_w[k][2 * qq + 1], a2, a3);
+        *reinterpret_cast<float4*>(pw + (size_t)idx * N + 4 * qq) = make_float4(a0, a1, a2, a3);
+        if constexpr (LN) {
+          f2_split(acc_b[k][2 * qq], a0, a1);
+          f2_split(acc_b[k][2 * qq + 1], a2, a3);
+          *reinterpret_cast<float4*>(pb + (size_t)idx * N + 4 * qq) = make_float4(a0, a1, a2, a3);
+        }
       }
     }
   }
