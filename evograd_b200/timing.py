@@ -42,7 +42,7 @@ def rotation_count(bytes_per_set: int, device=None) -> int:
     return max(2, -(-need // max(1, bytes_per_set)) + 1)
 
 
-def time_steps(step, steps: int, warmup: int, *, barrier=None) -> float:
+def time_steps(step, steps: int, warmup: int, *, barrier=None, finalize=None) -> float:
     """Runs ``step(i)`` warmup+steps times; returns milliseconds for EXACTLY
     ``steps`` iterations measured with CUDA events on the current stream,
     bracketed by a barrier and a device synchronise on both sides."""
@@ -57,6 +57,8 @@ def time_steps(step, steps: int, warmup: int, *, barrier=None) -> float:
     start.record()
     for i in range(steps):
         step(warmup + i)
+    if finalize is not None:
+        finalize()  # e.g. join a side stream: everything a step produced is done before `stop`
     stop.record()
     torch.cuda.synchronize()
     if barrier is not None:
