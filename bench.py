@@ -624,7 +624,10 @@ def run_ours(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per backward launch from the ncu
 # captures summarised under profiles/ (None until a capture exists).
-TRAFFIC_NCU = {}
+TRAFFIC_NCU = {
+    # norm_bwd_ring_kernel + colreduce_kernel, profiles/layernorm_bf16_16384x4096.md
+    "layernorm": 376.5e6 + 9.7e6,
+}
 
 
 def run_reference(args):
