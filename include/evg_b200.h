@@ -226,7 +226,8 @@ int64_t evg_causal_attention_bwd_workspace_bytes(int64_t B, int64_t H, int64_t S
  * dS = P*(dP - delta); dQ = scale*dS K; dK = scale*dS^T Q.  Deterministic:
  * dK/dV are accumulated by the block that owns a key tile and dQ by the block
  * that owns a query tile, so no atomics and no float32 dq buffer are used.
- * workspace holds delta[B,H,S] float32.
+ * workspace holds two float32 arrays padded to whole 128-row tiles per (batch,
+ * head): delta and the log-sum-exp in log2 units.
  */
 int evg_causal_attention_bwd(const void* dout, const void* q, const void* k,
                              const void* v, const void* o, const float* lse,
