@@ -237,6 +237,37 @@ __device__ __forceinline__ void block_allreduce(float (&v)[NV], float* scratch /
   phase ^= 1;
 }
 
+// Block all-reduce (sum) for a block of exactly WARPS warps (a multiple of 4):
+// like block_allreduce, but the per-warp partials are read back with 128-bit
+// shared loads. `scratch` holds [2][NV][WARPS] floats, 16-byte aligned.
+template <int NV, int WARPS>
+__device__ __forceinline__ void block_allreduce_sum_fixed(float (&v)[NV], float* scratch,
+                                                          int& phase) {
+  static_assert(WARPS % 4 == 0, "WARPS must be a multiple of 4");
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
+  }
+  float* buf = scratch + phase * (NV * WARPS);
+  if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) buf[i * WARPS + (threadIdx.x >> 5)] = v[i];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float s = 0.f;
+#pragma unroll
+    for (int q = 0; q < WARPS / 4; ++q) {
+      const float4 p = *reinterpret_cast<const float4*>(buf + i * WARPS + 4 * q);
+      s += (p.x + p.y) + (p.z + p.w);
+    }
+    v[i] = s;
+  }
+  phase ^= 1;
+}
+
 #endif  // __CUDACC__
 
 }  // namespace evg

@@ -245,15 +245,25 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
     if constexpr (LN) mu_next = mean[first];
   }
 
+  // Loop state is carried incrementally (stage, parity, row pointers): at ~16
+  // elements per thread and row, a runtime division per row would be a visible
+  // share of the instruction budget.
+  int s = 0;
+  uint32_t parity = 0;
+  const size_t row_step = (size_t)gridDim.x * cols;
+  T* dr = dx + first * cols;
+  const float* rstd_p = rstd + first;
+  const float* mean_p = LN ? mean + first : nullptr;
   for (int64_t i = 0; i < n_mine; ++i) {
-    const int s = (int)(i % stages);
-    const uint32_t parity = (uint32_t)((i / stages) & 1);
-    const int64_t row = first + i * gridDim.x;
     const float rs = rs_next;
     const float nmr = LN ? -mu_next * rs : 0.f;
     if (i + 1 < n_mine) {  // statistics of the next row, off the critical path
-      rs_next = rstd[row + gridDim.x];
-      if constexpr (LN) mu_next = mean[row + gridDim.x];
+      rstd_p += gridDim.x;
+      rs_next = *rstd_p;
+      if constexpr (LN) {
+        mean_p += gridDim.x;
+        mu_next = *mean_p;
+      }
     }
     mbar_wait(&full[s], parity, ctx, 401);
     const uint8_t* sx = ring + (size_t)s * 2 * row_bytes;
@@ -301,12 +311,11 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
         c[1] = lo + hi;
       }
     }
-    block_allreduce<NV, SumOp>(c, scratch, phase);  // everyone is done with stage s
+    block_allreduce_sum_fixed<NV, THREADS / 32>(c, scratch, phase);  // all done with stage s
     if (tid == 0 && i + stages < n_mine) issue(i + stages);
     // dx = rs*g - rs*mean(g) - rs*mean(g*xh)*xh
     const f32x2 a_x = f2_splat(-rs * (c[0] * inv_cols));
     const f32x2 a_0 = f2_splat(LN ? -rs * (c[1] * inv_cols) : 0.f);
-    T* dr = dx + row * cols;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int idx = tid + k * THREADS;
@@ -328,6 +337,11 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
         }
         st_vec(dr + (size_t)idx * N, pack<T>(o));
       }
+    }
+    dr += row_step;
+    if (++s == stages) {
+      s = 0;
+      parity ^= 1;
     }
   }
   // One group per block: the partial row goes out straight from registers.
