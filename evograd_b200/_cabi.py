@@ -88,8 +88,23 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
          c_int, c_void_p],
     ),
+    "evg_fused_add_rmsnorm_fwd": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int,
+         c_void_p],
+    ),
+    "evg_fused_add_rmsnorm_bwd_workspace_bytes": (c_int64, [c_int64, c_int64, c_int]),
+    "evg_fused_add_rmsnorm_bwd": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p],
+    ),
     "evg_swiglu_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "evg_swiglu_bwd": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]
+    ),
+    "evg_geglu_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "evg_geglu_bwd": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]
     ),
     "evg_rope": (

@@ -8,6 +8,7 @@
 // The result is bit-reproducible from run to run for a given launch shape.
 #include <mutex>
 
+#include "norm_reduce.cuh"
 #include "rowcfg.cuh"
 #include "sm100_umma.cuh"
 
@@ -419,41 +420,6 @@ norm_bwd_generic_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   }
 }
 
-// Stage 2: out[c] = sum_p partial[p][c]. Block = 32 columns x 32 row slices;
-// a slice adds its rows p = y, y+32, ... with four independent accumulators
-// (so four loads are in flight per thread), the slices are then added in
-// order. Fixed order throughout: bit-reproducible. gridDim.y = dweight / dbias.
-template <typename T>
-__global__ void __launch_bounds__(1024)
-colreduce_kernel(const float* __restrict__ partial, int blocks, int64_t cols, T* out_w, T* out_b,
-                 float* out_f32) {
-  __shared__ float tile[32][33];
-  const int which = blockIdx.y;
-  const float* src = partial + (size_t)which * blocks * cols;
-  const int64_t col = (int64_t)blockIdx.x * 32 + threadIdx.x;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  if (col < cols) {
-    int p = threadIdx.y;
-    for (; p + 96 < blocks; p += 128) {
-      s0 += src[(size_t)p * cols + col];
-      s1 += src[(size_t)(p + 32) * cols + col];
-      s2 += src[(size_t)(p + 64) * cols + col];
-      s3 += src[(size_t)(p + 96) * cols + col];
-    }
-    for (; p < blocks; p += 32) s0 += src[(size_t)p * cols + col];
-  }
-  tile[threadIdx.y][threadIdx.x] = (s0 + s1) + (s2 + s3);
-  __syncthreads();
-  if (threadIdx.y == 0 && col < cols) {
-    float t = tile[0][threadIdx.x];
-#pragma unroll
-    for (int i = 1; i < 32; ++i) t += tile[i][threadIdx.x];
-    T* out = which == 0 ? out_w : out_b;
-    if (out) out[col] = from_f32<T>(t);
-    if (out_f32) out_f32[(size_t)which * cols + col] = t;
-  }
-}
-
 int read_norm_status(int reset) {
   int code = 0;
   if (cudaMemcpyFromSymbol(&code, g_norm_device_status, sizeof(int)) != cudaSuccess) {
@@ -474,12 +440,6 @@ struct BwdPlan {
   int blocks = 0;
   size_t smem = 0;
 };
-
-int max_partial_blocks() {
-  int per_sm = tune("norm_bwd.blocks_per_sm");
-  if (per_sm <= 0) per_sm = 2;
-  return device_info().sm_count * per_sm;
-}
 
 // `block_limit` > 0 bounds the number of partial rows (callers with a fixed scratch).
 template <typename T, bool LN>

@@ -203,6 +203,56 @@ def rmsnorm_bwd(dy, x, weight, rstd, *, partials_f32: bool = False):
     return dx.view(x.shape), dweight
 
 
+def fused_add_rmsnorm_fwd(x, residual, weight, eps: float = 1e-6):
+    """``out = rmsnorm(x + residual) * weight`` with the reference's rounding points
+    (ops/level2/fused_add_rms_norm/forward_ref.py:6-14). Returns ``(out, rstd)``;
+    rstd is float32 ``[rows]``; the sum itself is not kept."""
+    dev = _require_cuda(x, residual, weight)
+    _same("x", x, "residual", residual)
+    _check_param("weight", weight, x)
+    hidden = x.shape[-1]
+    x2, r2 = _rows_view(x, hidden), _rows_view(residual, hidden)
+    rows = x2.shape[0]
+    out = torch.empty_like(x2)
+    rstd = torch.empty(rows, device=dev, dtype=torch.float32)
+    if rows == 0:
+        return out.view(x.shape), rstd
+    with torch.cuda.device(dev):
+        call("evg_fused_add_rmsnorm_fwd", x2.data_ptr(), r2.data_ptr(),
+             weight.contiguous().data_ptr(), out.data_ptr(), rstd.data_ptr(), rows, hidden,
+             float(eps), _dtype_enum(x), _stream(dev))
+    return out.view(x.shape), rstd
+
+
+def fused_add_rmsnorm_bwd(dout, x, residual, weight, rstd, *, partials_f32: bool = False):
+    """Returns ``(dx, dweight)``; the gradient of ``residual`` equals ``dx``.
+    ``dweight`` is float32 when ``partials_f32``."""
+    dev = _require_cuda(dout, x, residual, weight, rstd)
+    _same("dout", dout, "x", x)
+    _same("x", x, "residual", residual)
+    _check_param("weight", weight, x)
+    hidden = x.shape[-1]
+    x2, r2, g2 = _rows_view(x, hidden), _rows_view(residual, hidden), _rows_view(dout, hidden)
+    rows = x2.shape[0]
+    if rstd.numel() != rows or rstd.dtype != torch.float32:
+        raise ValueError("rstd must be float32 with one entry per row")
+    dx = torch.empty_like(x2)
+    en = _dtype_enum(x)
+    out_dtype = torch.float32 if partials_f32 else x.dtype
+    if rows == 0:
+        return dx.view(x.shape), torch.zeros(hidden, device=dev, dtype=out_dtype)
+    with torch.cuda.device(dev):
+        ws_bytes = lib.evg_fused_add_rmsnorm_bwd_workspace_bytes(rows, hidden, en)
+        ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+        dweight = torch.empty(hidden, device=dev, dtype=out_dtype)
+        call("evg_fused_add_rmsnorm_bwd", g2.data_ptr(), x2.data_ptr(), r2.data_ptr(),
+             weight.contiguous().data_ptr(), rstd.contiguous().data_ptr(), dx.data_ptr(),
+             None if partials_f32 else dweight.data_ptr(),
+             dweight.data_ptr() if partials_f32 else None, ws.data_ptr(), ws_bytes, rows, hidden,
+             en, _stream(dev))
+    return dx.view(x.shape), dweight
+
+
 def cast_from_f32(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     """Round a float32 tensor to ``dtype`` (after an all-reduce of partial sums)."""
     dev = _require_cuda(src)
@@ -216,8 +266,8 @@ def cast_from_f32(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return dst
 
 
-# ------------------------------------------------------------------- swiglu
-def swiglu_fwd(a, b):
+# ------------------------------------------------------------ swiglu / geglu
+def _glu_fwd(symbol, a, b):
     dev = _require_cuda(a, b)
     _same("a", a, "b", b)
     a2, b2 = a.contiguous(), b.contiguous()
@@ -225,21 +275,19 @@ def swiglu_fwd(a, b):
     if a2.numel() == 0:
         return c
     with torch.cuda.device(dev):
-        call("evg_swiglu_fwd", a2.data_ptr(), b2.data_ptr(), c.data_ptr(), a2.numel(),
+        call(symbol, a2.data_ptr(), b2.data_ptr(), c.data_ptr(), a2.numel(),
              _dtype_enum(a), _stream(dev))
     return c
 
 
-def swiglu_bwd(dc, a, b, *, in_place: bool = False):
-    """Returns ``(da, db)``. ``in_place`` writes them over ``a`` and ``b`` (which
-    must then be contiguous), as the swiglu declaration permits."""
+def _glu_bwd(symbol, dc, a, b, in_place):
     dev = _require_cuda(dc, a, b)
     _same("a", a, "b", b)
     _same("dc", dc, "a", a)
     dc2 = dc.contiguous()
     if in_place:
         if not (a.is_contiguous() and b.is_contiguous()):
-            raise ValueError("in_place swiglu backward needs contiguous a and b")
+            raise ValueError("in_place backward needs contiguous a and b")
         a2, b2, da, db = a, b, a, b
     else:
         a2, b2 = a.contiguous(), b.contiguous()
@@ -247,9 +295,29 @@ def swiglu_bwd(dc, a, b, *, in_place: bool = False):
     if a2.numel() == 0:
         return da, db
     with torch.cuda.device(dev):
-        call("evg_swiglu_bwd", dc2.data_ptr(), a2.data_ptr(), b2.data_ptr(), da.data_ptr(),
+        call(symbol, dc2.data_ptr(), a2.data_ptr(), b2.data_ptr(), da.data_ptr(),
              db.data_ptr(), a2.numel(), _dtype_enum(a), _stream(dev))
     return da, db
+
+
+def swiglu_fwd(a, b):
+    return _glu_fwd("evg_swiglu_fwd", a, b)
+
+
+def swiglu_bwd(dc, a, b, *, in_place: bool = False):
+    """Returns ``(da, db)``. ``in_place`` writes them over ``a`` and ``b`` (which
+    must then be contiguous), as the swiglu declaration permits."""
+    return _glu_bwd("evg_swiglu_bwd", dc, a, b, in_place)
+
+
+def geglu_fwd(a, b):
+    """c = gelu_tanh(a) * b (ops/level1/geglu/forward_ref.py:6-9)."""
+    return _glu_fwd("evg_geglu_fwd", a, b)
+
+
+def geglu_bwd(dc, a, b, *, in_place: bool = False):
+    """Returns ``(da, db)`` of the geglu pair; ``in_place`` as for swiglu."""
+    return _glu_bwd("evg_geglu_bwd", dc, a, b, in_place)
 
 
 # --------------------------------------------------------------------- rope

@@ -161,6 +161,36 @@ int evg_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* weight,
                             float* dweight_f32, int64_t rows, int64_t hidden,
                             int dtype, void* stream);
 
+/* ------------------------------------------------------- fused add + rmsnorm
+ * s = dtype(x + residual); rstd = rsqrt(mean(float(s)^2) + eps);
+ * out = dtype(dtype(s * dtype(rstd)) * weight): the rounding points of
+ * fused_add_rms_norm_forward_ref,
+ * ops/level2/fused_add_rms_norm/forward_ref.py:6-14. Saved state is float32
+ * rstd[rows] only; s is re-formed from x and residual by the backward.
+ * replaces: the fused_add_rms_norm candidate pair derived from
+ * ops/level2/fused_add_rms_norm/__init__.py:76-122 (forward_with_saved).
+ */
+int evg_fused_add_rmsnorm_fwd(const void* x, const void* residual,
+                              const void* weight, void* out, float* rstd,
+                              int64_t rows, int64_t hidden, float eps,
+                              int dtype, void* stream);
+/* Bytes of scratch evg_fused_add_rmsnorm_bwd needs (partial dweight rows). */
+int64_t evg_fused_add_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t hidden,
+                                                  int dtype);
+/*
+ * dx (which is also the gradient of residual: both reach the output through
+ * s) and dweight [hidden]; `dweight_f32` (optional, [hidden]) receives the
+ * unrounded float32 column sums for a caller that all-reduces before rounding.
+ * replaces: backward_from_saved of the same declaration (returns dx, dr,
+ * dweight with dx == dr, __init__.py:96-99).
+ */
+int evg_fused_add_rmsnorm_bwd(const void* dout, const void* x,
+                              const void* residual, const void* weight,
+                              const float* rstd, void* dx, void* dweight,
+                              float* dweight_f32, void* workspace,
+                              int64_t workspace_bytes, int64_t rows,
+                              int64_t hidden, int dtype, void* stream);
+
 /* ------------------------------------------------------------------- swiglu
  * c = round(silu(float(a))) * b  with the product taken in dtype, exactly the
  * rounding points of swiglu_forward_ref, ops/level1/swiglu/forward_ref.py:6-9.
@@ -175,6 +205,19 @@ int evg_swiglu_fwd(const void* a, const void* b, void* c, int64_t n, int dtype,
  */
 int evg_swiglu_bwd(const void* dc, const void* a, const void* b, void* da,
                    void* db, int64_t n, int dtype, void* stream);
+
+/* -------------------------------------------------------------------- geglu
+ * c = round(gelu_tanh(float(a))) * b, the rounding points of
+ * geglu_forward_ref, ops/level1/geglu/forward_ref.py:6-9
+ * (gelu_tanh(a) = a/2 * (1 + tanh(sqrt(2/pi) * (a + 0.044715 a^3)))).
+ * Same calling convention as the swiglu pair; da/db may alias a/b.
+ * replaces: the geglu candidate pair derived from
+ * ops/level1/geglu/__init__.py:52-84.
+ */
+int evg_geglu_fwd(const void* a, const void* b, void* c, int64_t n, int dtype,
+                  void* stream);
+int evg_geglu_bwd(const void* dc, const void* a, const void* b, void* da,
+                  void* db, int64_t n, int dtype, void* stream);
 
 /* --------------------------------------------------------------------- rope
  * Rotate-half (GPT-NeoX / Llama) rotary embedding of a 4-D tensor whose last

@@ -59,6 +59,19 @@ CASES = {
         ({"rows": 64, "cols": 512}, "bfloat16"),
         ({"rows": 17, "cols": 255}, "bfloat16"),
     ],
+    "geglu": [
+        ({"rows": 8, "cols": 64}, "float32"),
+        ({"rows": 32, "cols": 256}, "float16"),
+        ({"rows": 64, "cols": 512}, "bfloat16"),
+        ({"rows": 17, "cols": 255}, "bfloat16"),
+    ],
+    "fused_add_rms_norm": [
+        ({"rows": 8, "cols": 64}, "float32"),
+        ({"rows": 32, "cols": 256}, "float16"),
+        ({"rows": 64, "cols": 512}, "bfloat16"),
+        ({"rows": 17, "cols": 513}, "bfloat16"),
+        ({"rows": 8, "cols": 4096}, "bfloat16"),
+    ],
     "rope": [
         ({"B": 1, "n_heads": 4, "T": 16, "head_dim": 64}, "float32"),
         ({"B": 1, "n_heads": 4, "T": 16, "head_dim": 64}, "float16"),
@@ -147,13 +160,20 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference/src",
                     help="path to the reference's src/ directory")
+    ap.add_argument("--only", nargs="*", default=None,
+                    help="regenerate only these operators (the index keeps the others)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import evograd  # noqa: F401
 
     torch.set_num_threads(1)  # one summation order, whatever the host
     index = {}
+    index_path = HERE / "index.json"
+    if args.only and index_path.exists():
+        index = json.loads(index_path.read_text())
     for op_name, cases in CASES.items():
+        if args.only and op_name not in args.only:
+            continue
         for dims, dtype in cases:
             if op_name == "causal_attention":
                 tensors, scalars = _attention_case(evograd, dims, dtype)
