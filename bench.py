@@ -253,6 +253,52 @@ class SwiGLUWL(Workload):
         return {"workload": self.name, "shape": [self.rows, self.cols], "saved": "a,b by reference"}
 
 
+class GeGLUWL(SwiGLUWL):
+    name, pair = "geglu_bf16_32768x14336", "geglu"
+
+    def cpu_step(self, s):
+        from oracle import autograd_oracle as ao
+        return ao.oracle("geglu", s)
+
+
+class FusedAddRMSNormWL(Workload):
+    """Residual add fused into RMSNorm at the Llama-3-8B hidden width."""
+    name, kernels_per_step, pair = "fused_add_rms_norm_bf16_32768x4096", 3, "fused_add_rms_norm"
+    rows, hidden, eps = 32768, 4096, 1e-6
+
+    def __init__(self, device):
+        super().__init__(device)
+        nb = self.rows * self.hidden * 2
+        self.fwd_work, self.bwd_work = 3 * nb, 4 * nb  # x, r -> out ; dout, x, r -> dx
+
+    def make(self, device, salt=0):
+        g = _gen(device, self.rows * 100003 + self.hidden + salt)
+        s = {k: _randn((self.rows, self.hidden), BF16, device, g) for k in ("x", "r")}
+        s["weight"] = _randn((self.hidden,), BF16, device, g)
+        s["dout"] = _randn((self.rows, self.hidden), BF16, device, g)
+        s["eps"] = self.eps
+        return s
+
+    def inputs_of(self, s):
+        return [s["x"], s["r"], s["weight"], s["dout"]]
+
+    def forward(self, s):
+        out, saved = self.fwd(s["x"], s["r"], s["weight"], self.eps)
+        return [out], saved
+
+    def backward(self, s, saved):
+        dx, _dr, dw = self.bwd(s["dout"], saved)  # dr is dx itself
+        return [dx, dw]
+
+    def cpu_step(self, s):
+        from oracle import autograd_oracle as ao
+        return ao.oracle("fused_add_rms_norm", s)
+
+    def config(self):
+        return {"workload": self.name, "shape": [self.rows, self.hidden], "eps": self.eps,
+                "saved": "rstd f32 (x, r by reference; the sum is re-formed)"}
+
+
 class RopeWL(Workload):
     name, kernels_per_step = "rope_bf16_qk_8x4096x32x128", 2
     B, S, H, D, theta = 8, 4096, 32, 128, 10000.0
@@ -333,7 +379,8 @@ class AttentionWL(Workload):
 
 
 WORKLOADS = {"softmax": SoftmaxWL, "layernorm": LayerNormWL, "rmsnorm": RMSNormWL,
-             "swiglu": SwiGLUWL, "rope": RopeWL, "attention": AttentionWL}
+             "swiglu": SwiGLUWL, "rope": RopeWL, "attention": AttentionWL,
+             "geglu": GeGLUWL, "fused_add_rms_norm": FusedAddRMSNormWL}
 
 
 # --------------------------------------------------------------------------
@@ -536,20 +583,26 @@ def run_ours(args):
     # Leg 1 (value): K steps between one event pair. Each step is one CUDA-graph
     # replay of the public pair calls (forward, backward, and at N > 1 the NCCL
     # all-reduce), so the host's launch path is not what is being timed.
-    # Leg 2 (roofline): the same K steps launched eagerly with an event pair around
-    # forward and backward of every step.
+    # Leg 2 (roofline): K replays of the backward alone (its row kernel and the
+    # column reduce) between one event pair; if capture is refused, the same K
+    # steps launched eagerly with an event pair around forward and backward.
     launch_mode = "cuda graph replay (one graph per step)"
+    roofline_loop = "K graph replays of the backward alone between one CUDA event pair"
     with ClockSampler(local) as clocks:
         try:
-            step_ms, _f, _b, n_sets = measure_graphs(wl, args.steps, args.warmup, world)
+            step_ms, _f, bwd_ms, n_sets = measure_graphs(wl, args.steps, args.warmup, world)
             launches = wl.kernels_per_step * args.steps
         except Exception as exc:  # capture refused: the same calls, launched eagerly
             launch_mode = f"eager, current stream ({type(exc).__name__})"
+            roofline_loop = "same K steps launched eagerly with CUDA events around forward and backward"
             torch.cuda.synchronize()
             ms, _unused, launches, n_sets = measure_device(wl, args.steps, args.warmup, world,
                                                            sections=False)
             step_ms = ms / args.steps
-        _ms2, totals, _l2, _n2 = measure_device(wl, args.steps, args.warmup, world, sections=True)
+            _ms2, totals, _l2, _n2 = measure_device(wl, args.steps, args.warmup, world,
+                                                    sections=True)
+            bwd_total, bwd_n = totals["bwd"]
+            bwd_ms = bwd_total / bwd_n
     if wl.bound == "hbm":
         metric = f"fwd+bwd achieved HBM GB/s ({wl.name})"
         unit, value = "GB/s", _rate(wl.step_work, step_ms) * world
@@ -558,8 +611,6 @@ def run_ours(args):
         unit, value = "TFLOP/s", wl.step_work / (step_ms * 1e-3) / 1e12 * world
 
     # roofline of the dominant launch: the backward (largest share of the step)
-    bwd_total, bwd_n = totals["bwd"]
-    bwd_ms = bwd_total / bwd_n
     if wl.bound == "hbm":
         achieved, peak, runit = _rate(wl.bwd_work, bwd_ms), peaks["hbm_gbs"], "GB/s"
     else:
@@ -587,7 +638,7 @@ def run_ours(args):
         "config": {**wl.config(), "l2": f"{n_sets} rotating input set(s), each pass reads data not in L2",
                    "parallelism": f"rows x{world}" if world > 1 else "1 gpu",
                    "launch": launch_mode,
-                   "roofline_loop": "same K steps launched eagerly with CUDA events around forward and backward"},
+                   "roofline_loop": roofline_loop},
         "e2e": e2e,
         "gpu_launches": launches,
         "roofline": roofline,

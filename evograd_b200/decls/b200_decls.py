@@ -11,7 +11,7 @@ Attributes
                       ``F.scaled_dot_product_attention(..., is_causal=True)`` as
                       at ops/level3/llama3_decoder_layer/forward_ref.py:107,
                       float32 reference dtype.
-    softmax, layernorm, rmsnorm, swiglu, rope
+    softmax, layernorm, rmsnorm, swiglu, rope, geglu, fused_add_rms_norm
                       the built-in declarations with one extra named benchmark
                       suite ``"b200"`` holding the baseline configuration's exact
                       shape/dtype (and, where the input recipe differs from the
@@ -151,6 +151,10 @@ rmsnorm = _with_b200(
     _rmsnorm_b200_inputs,
 )
 swiglu = _with_b200("swiglu", [Workload(dims=dict(rows=32768, cols=14336), dtype="bfloat16")])
+geglu = _with_b200("geglu", [Workload(dims=dict(rows=32768, cols=14336), dtype="bfloat16")])
+fused_add_rms_norm = _with_b200(
+    "fused_add_rms_norm", [Workload(dims=dict(rows=32768, cols=4096), dtype="bfloat16")]
+)
 # The reference layout is [B, heads, T, head_dim] with one tensor per call; the
 # [B, S, H, D] q-and-k form of the baseline config is served by
 # evograd_b200.ops.rope_qk_fwd / rope_qk_bwd and timed by bench.py.
