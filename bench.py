@@ -154,6 +154,24 @@ class SoftmaxWL(Workload):
         return {"workload": self.name, "shape": [self.rows, self.cols], "saved": "y"}
 
 
+class SoftmaxVocabWL(SoftmaxWL):
+    """Softmax over Llama-3 logits rows (the reference's own benchmark grid,
+    ops/level1/softmax/__init__.py:31-37): 128256 columns do not fit one block's
+    registers, so this exercises the wide-row path."""
+    name, dtype = "softmax_bf16_4096x128256", "bf16"
+    rows, cols = 4096, 128256
+
+    def __init__(self, device):
+        Workload.__init__(self, device)
+        nb = self.rows * self.cols * 2
+        self.fwd_work, self.bwd_work = 2 * nb, 3 * nb
+
+    def make(self, device, salt=0):
+        g = _gen(device, self.rows * 100003 + self.cols + salt)
+        return {"x": _randn((self.rows, self.cols), BF16, device, g),
+                "dy": _randn((self.rows, self.cols), BF16, device, g)}
+
+
 class NormWL(Workload):
     kind = "layernorm"
     rows, hidden, eps = 16384, 4096, 1e-5
@@ -380,7 +398,8 @@ class AttentionWL(Workload):
 
 WORKLOADS = {"softmax": SoftmaxWL, "layernorm": LayerNormWL, "rmsnorm": RMSNormWL,
              "swiglu": SwiGLUWL, "rope": RopeWL, "attention": AttentionWL,
-             "geglu": GeGLUWL, "fused_add_rms_norm": FusedAddRMSNormWL}
+             "geglu": GeGLUWL, "fused_add_rms_norm": FusedAddRMSNormWL,
+             "softmax_vocab": SoftmaxVocabWL}
 
 
 # --------------------------------------------------------------------------

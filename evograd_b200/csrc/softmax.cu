@@ -1,6 +1,7 @@
 // Row softmax forward/backward for sm_100a. HBM-bound: forward reads x and
 // writes y; backward reads y and dy and writes dx. The only saved state is y.
 #include "rowcfg.cuh"
+#include "softmax_wide.cuh"
 
 namespace evg {
 namespace {
@@ -228,6 +229,11 @@ int launch_softmax_fwd(const void* x, void* y, int64_t rows, int64_t cols, cudaS
     EVG_ROWCFG_LIST(EVG_X)
 #undef EVG_X
   }
+  if (vec_ok && !tune("rows.force_generic")) {  // wider than any register shape
+    bool handled = false;
+    const int rc = softmax_wide_fwd(DtypeOf<T>::value, x, y, rows, cols, stream, &handled);
+    if (rc || handled) return rc;
+  }
   const int threads = cols >= 4096 ? 1024 : (cols >= 256 ? 256 : 64);
   if (vec_ok) {
     auto kern = softmax_fwd_generic_kernel<T, true>;
@@ -260,6 +266,11 @@ int launch_softmax_bwd(const void* y, const void* dy, void* dx, int64_t rows, in
   }
     EVG_ROWCFG_LIST(EVG_X)
 #undef EVG_X
+  }
+  if (vec_ok && !tune("rows.force_generic")) {  // wider than any register shape
+    bool handled = false;
+    const int rc = softmax_wide_bwd(DtypeOf<T>::value, y, dy, dx, rows, cols, stream, &handled);
+    if (rc || handled) return rc;
   }
   const int threads = cols >= 4096 ? 1024 : (cols >= 256 ? 256 : 64);
   if (vec_ok) {

@@ -47,6 +47,8 @@ CASES = {
         ((32, 4096), ("float16", "bfloat16")), ((64, 2048), ("float16", "bfloat16")),
         ((3, 1), ("float32",)), ((7, 131), ("bfloat16",)), ((4, 33000), ("float32",)),
         ((2, 128256), ("bfloat16",)), ((5, 8192), ("float32",)), ((1, 16384), ("float32",)),
+        ((300, 128256), ("float16",)), ((9, 70000), ("float16",)), ((3, 131072), ("bfloat16",)),
+        ((2, 262144), ("bfloat16", "float32")), ((2, 600000), ("float32",)),
     ) for dt in dts],
     "layernorm": [(dict(rows=r, hidden=h), dt) for (r, h), dts in (
         ((8, 64), ("float32",)), ((17, 128), ("float32",)), ((32, 256), ("float16", "bfloat16")),
@@ -140,6 +142,29 @@ def test_every_launch_shape_gives_the_same_answer(op, knobs):
         for key in set_keys:
             _cabi.tune_set(key, 0)
     assert_checks(checks, f"{op} {knobs}")
+
+
+@pytest.mark.parametrize("knobs", [
+    {"softmax.no_cluster": 1}, {"softmax.cluster": 2}, {"softmax.cluster": 4},
+    {"softmax.cluster": 8}, {"softmax.cluster": 8, "softmax.cluster_stages": 2},
+    {"softmax.cluster": 8, "softmax.cluster_stages": 1},
+])
+def test_wide_softmax_cluster_shapes_agree(knobs):
+    """Vocabulary-width rows: every cluster size / stage count (and the generic
+    multi-pass kernel) passes the gate on the same inputs."""
+    from evograd_b200 import _cabi
+
+    dims, dtype = dict(rows=37, cols=128256), "bfloat16"
+    inputs = to_device(ao.make_inputs("softmax", dims, dtype))
+    try:
+        for k, v in knobs.items():
+            _cabi.tune_set(k, v)
+        checks = ao.verify_pair("softmax", __import__("_util").load_pair("softmax"), inputs, dims,
+                                dtype, strict=True, reference_dtype=torch.float32)
+    finally:
+        for k in knobs:
+            _cabi.tune_set(k, 0)
+    assert_checks(checks, f"softmax wide {knobs}")
 
 
 def test_rope_baseline_layout_q_and_k_in_one_launch():
