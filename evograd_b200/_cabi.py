@@ -99,6 +99,7 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p],
     ),
+    "evg_selftest_bounded_wait": (c_int, [c_int64, c_void_p, c_void_p]),
     "evg_swiglu_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "evg_swiglu_bwd": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]

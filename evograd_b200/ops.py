@@ -434,6 +434,17 @@ def device_status(reset: bool = True) -> None:
     call("evg_device_status", 1 if reset else 0)
 
 
+def selftest_bounded_wait(limit_cycles: int = 2_000_000, device=None) -> int:
+    """Launch the bounded-wait self-test (a wait nothing satisfies, given up after
+    ``limit_cycles``) and return the abort word the block recorded. The sticky
+    status is left set: the next :func:`device_status` raises EVG_ETIMEOUT once."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = torch.zeros(1, device=dev, dtype=torch.int32)
+    with torch.cuda.device(dev):
+        call("evg_selftest_bounded_wait", int(limit_cycles), word.data_ptr(), _stream(dev))
+    return int(word.item())
+
+
 def flush_l2(buffer: torch.Tensor) -> None:
     """Overwrite ``buffer`` (larger than L2) so cached lines of other tensors are evicted."""
     dev = _require_cuda(buffer)

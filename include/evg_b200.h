@@ -288,6 +288,18 @@ int evg_causal_attention_bwd(const void* dout, const void* q, const void* k,
  */
 int evg_device_status(int reset);
 
+/*
+ * Self-test of the bounded-wait protocol: launches one small block that waits
+ * (through the same helper as the product kernels) for a barrier phase nothing
+ * completes, gives up after `limit_cycles` SM cycles (0 < limit <= 4e8) and
+ * returns normally. `observed_abort_word` (device pointer, optional) receives
+ * the block's abort word (the id of the wait that gave up, 901). Afterwards
+ * evg_device_status() reports EVG_ETIMEOUT once; the context stays usable.
+ * No reference counterpart: the reference has no device-side waits.
+ */
+int evg_selftest_bounded_wait(int64_t limit_cycles, int* observed_abort_word,
+                              void* stream);
+
 /* ------------------------------------------------------------------ helpers
  * dst[i] = round_to_dtype(src[i]) for float32 src; used after the cross-GPU
  * all-reduce of float32 dweight/dbias partial sums.
