@@ -6,7 +6,8 @@ RMSNorm (``[2, hidden]`` / ``[hidden]`` floats per step):
 
     softmax, swiglu     contiguous row blocks, no exchange
     rope                contiguous batch blocks, tables replicated, no exchange
-    layernorm, rmsnorm  contiguous row blocks; every rank forms float32
+    layernorm, rmsnorm, fused_add_rms_norm
+                        contiguous row blocks; every rank forms float32
                         dweight/dbias over ITS rows, one all_reduce(SUM), and only
                         then rounds to the parameter dtype (rounding before the sum
                         would not match a single-device float32 accumulation)
@@ -53,18 +54,22 @@ class NormKernels:
     rmsnorm_fwd: object
     rmsnorm_bwd: object  # (dy, x, w, rstd, partials_f32=True) -> (dx, dw_f32)
     cast_from_f32: object
+    add_rms_fwd: object = None  # (x, r, w, eps) -> (out, rstd)
+    add_rms_bwd: object = None  # (dout, x, r, w, rstd, partials_f32=True) -> (dx, dw_f32)
 
     @staticmethod
     def cuda() -> "NormKernels":
         from . import ops
 
         return NormKernels(ops.layernorm_fwd, ops.layernorm_bwd, ops.rmsnorm_fwd, ops.rmsnorm_bwd,
-                           ops.cast_from_f32)
+                           ops.cast_from_f32, ops.fused_add_rmsnorm_fwd, ops.fused_add_rmsnorm_bwd)
 
 
 class ShardedNorm:
     """LayerNorm / RMSNorm autograd pair over a row shard with the cross-rank
-    parameter-gradient reduction. ``kind`` is "layernorm" or "rmsnorm"."""
+    parameter-gradient reduction. ``kind`` is "layernorm", "rmsnorm" or
+    "fused_add_rms_norm" (whose forward also takes ``residual`` and whose backward
+    returns ``(dx, dr, dweight)`` with ``dr is dx``)."""
 
     def __init__(self, kind: str, group=None, kernels: NormKernels | None = None,
                  overlap_comm: bool = False):
@@ -72,8 +77,8 @@ class ShardedNorm:
         side stream, so the next kernels on the caller's stream (for example the
         next step's forward) run while the 16-32 KB exchange is in flight. The
         returned parameter gradients are then only valid after :meth:`finish`."""
-        if kind not in ("layernorm", "rmsnorm"):
-            raise ValueError(f"kind must be layernorm or rmsnorm, got {kind!r}")
+        if kind not in ("layernorm", "rmsnorm", "fused_add_rms_norm"):
+            raise ValueError(f"kind must be layernorm, rmsnorm or fused_add_rms_norm, got {kind!r}")
         self.kind = kind
         self.group = group
         self.k = kernels or NormKernels.cuda()
@@ -82,7 +87,12 @@ class ShardedNorm:
         self._comm_stream = None
         self._pending = None
 
-    def forward_with_saved(self, x_shard, weight, bias=None, eps: float = 1e-5):
+    def forward_with_saved(self, x_shard, weight, bias=None, eps: float = 1e-5, residual=None):
+        if self.kind == "fused_add_rms_norm":
+            if residual is None:
+                raise ValueError("fused_add_rms_norm needs the residual shard")
+            out, rstd = self.k.add_rms_fwd(x_shard, residual, weight, eps)
+            return out, (x_shard, residual, weight, rstd)
         if self.kind == "layernorm":
             if bias is None:
                 raise ValueError("layernorm needs a bias")
@@ -98,6 +108,9 @@ class ShardedNorm:
         if self.kind == "layernorm":
             x, weight, mean, rstd = saved
             dx, partial, _ = self.k.layernorm_bwd(dy_shard, x, weight, mean, rstd, partials_f32=True)
+        elif self.kind == "fused_add_rms_norm":
+            x, residual, weight, rstd = saved
+            dx, partial = self.k.add_rms_bwd(dy_shard, x, residual, weight, rstd, partials_f32=True)
         else:
             x, weight, rstd = saved
             dx, partial = self.k.rmsnorm_bwd(dy_shard, x, weight, rstd, partials_f32=True)
@@ -123,6 +136,8 @@ class ShardedNorm:
             rounded = self.k.cast_from_f32(partial, weight.dtype)
         if self.kind == "layernorm":
             return dx, rounded[0], rounded[1]
+        if self.kind == "fused_add_rms_norm":
+            return dx, dx, rounded
         return dx, rounded
 
 

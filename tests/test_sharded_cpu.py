@@ -58,7 +58,23 @@ def _cpu_kernels() -> NormKernels:
         dx = (g - xh * (g * xh).mean(-1, keepdim=True)) * rstd[:, None]
         return dx.to(x.dtype), (dy.float() * xh).sum(0)
 
-    return NormKernels(ln_fwd, ln_bwd, rms_fwd, rms_bwd, lambda t, dtype: t.to(dtype))
+    def add_rms_fwd(x, r, w, eps):
+        s_ = x + r  # rounded to the input dtype, as the trusted forward does
+        rstd = torch.rsqrt(s_.float().pow(2).mean(-1) + eps)
+        return (s_ * rstd[:, None].to(s_.dtype)) * w, rstd
+
+    def add_rms_bwd(dout, x, r, w, rstd, partials_f32=False):
+        assert partials_f32
+        s_ = (x + r).float()
+        rb = rstd.to(x.dtype).float()[:, None]
+        g = dout.float() * w.float()
+        c = (g * s_).mean(-1, keepdim=True)
+        dx = g * rb - s_ * (rstd[:, None] ** 3) * c
+        t = (s_ * rb).to(x.dtype).float()
+        return dx.to(x.dtype), (dout.float() * t).sum(0)
+
+    return NormKernels(ln_fwd, ln_bwd, rms_fwd, rms_bwd, lambda t, dtype: t.to(dtype),
+                       add_rms_fwd, add_rms_bwd)
 
 
 def _free_port():
@@ -67,39 +83,51 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def _dims(kind):
+    return dict(rows=37, cols=96) if kind == "fused_add_rms_norm" else dict(rows=37, hidden=96)
+
+
 def _worker(rank, world, port, kind, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        dims = dict(rows=37, hidden=96)  # odd row count: shards of 19 and 18
+        dims = _dims(kind)  # odd row count: shards of 19 and 18
         inputs = ao.make_inputs(kind, dims, "bfloat16")
         a, b = block_range(dims["rows"], world, rank)
         sn = ShardedNorm(kind, kernels=_cpu_kernels())
-        y, saved = sn.forward_with_saved(inputs["x"][a:b], inputs["weight"], inputs.get("bias"), 1e-5)
-        grads = sn.backward_from_saved(inputs["dy"][a:b], saved)
+        if kind == "fused_add_rms_norm":
+            y, saved = sn.forward_with_saved(inputs["x"][a:b], inputs["weight"], None,
+                                             inputs["eps"], residual=inputs["r"][a:b])
+            grads = sn.backward_from_saved(inputs["dout"][a:b], saved)
+            assert grads[1] is grads[0]
+            grads = (grads[0], grads[2])
+        else:
+            y, saved = sn.forward_with_saved(inputs["x"][a:b], inputs["weight"], inputs.get("bias"), 1e-5)
+            grads = sn.backward_from_saved(inputs["dy"][a:b], saved)
         assert sn.collectives == 1
         out[rank] = {"span": (a, b), "y": y, "dx": grads[0], "params": [g for g in grads[1:]]}
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm"])
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm", "fused_add_rms_norm"])
 def test_two_ranks_match_the_full_input_oracle(kind):
     world, port = 2, _free_port()
     mgr = mp.Manager()
     out = mgr.dict()
     mp.spawn(_worker, args=(world, port, kind, out), nprocs=world, join=True)
-    dims = dict(rows=37, hidden=96)
+    dims = _dims(kind)
     inputs = ao.make_inputs(kind, dims, "bfloat16")
     y_ref, g_ref = ao.oracle(kind, inputs, reference_dtype=torch.float32)
     spec = ao.OPS[kind]
+    param_names = [n for n in spec.grad_names() if n not in ("dx", "dr")]
     for rank in range(world):
         a, b = out[rank]["span"]
         assert ao.check("y", out[rank]["y"], y_ref[a:b], *ao.STRICT_TOLERANCES["bfloat16"]).ok
         assert ao.check("dx", out[rank]["dx"], g_ref["dx"][a:b], *ao.STRICT_TOLERANCES["bfloat16"]).ok
-        for name, g in zip(spec.grad_names()[1:], out[rank]["params"]):
+        for name, g in zip(param_names, out[rank]["params"]):
             assert g.dtype == torch.bfloat16
-            c = ao.check(name, g, g_ref[name], *ao.STRICT_TOLERANCES["bfloat16"])
+            c = ao.check(name, g, g_ref[name], *spec.strict_tolerance_for(dims, "bfloat16", name))
             assert c.ok, (name, c)
     # every rank holds the same rounded parameter gradients
     for g0, g1 in zip(out[0]["params"], out[1]["params"]):
