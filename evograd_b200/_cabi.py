@@ -99,6 +99,19 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p],
     ),
+    "evg_causal_gqa_attention_fwd": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+         c_int64, c_float, c_int, c_void_p],
+    ),
+    "evg_causal_gqa_attention_bwd_workspace_bytes": (
+        c_int64, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]
+    ),
+    "evg_causal_gqa_attention_bwd": (
+        c_int,
+        [c_void_p] * 10 + [c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int,
+                           c_void_p],
+    ),
     "evg_selftest_bounded_wait": (c_int, [c_int64, c_void_p, c_void_p]),
     "evg_swiglu_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "evg_swiglu_bwd": (

@@ -667,8 +667,8 @@ extern "C" int evg_causal_attention_fwd(const void* q, const void* k, const void
     return fail(EVG_EALIGN, "causal_attention_fwd: q/k/v/o must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   if (tune("attention.variant") != 1)  // default: two query tiles per block, warp-specialised
-    return attn::launch_fwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, q, k, v, o, lse, B, H, S, scale,
-                                 st);
+    return attn::launch_fwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, q, k, v, o, lse, B, H, H, S,
+                                 scale, st);
   if (D == 128) {
     return dtype == EVG_BF16 ? launch_fwd<128, 1>(q, k, v, o, lse, B, H, S, scale, st)
                              : launch_fwd<128, 0>(q, k, v, o, lse, B, H, S, scale, st);
@@ -702,7 +702,7 @@ extern "C" int evg_causal_attention_bwd(const void* dout, const void* q, const v
   float* delta = (float*)workspace;
   if (tune("attention.variant") != 1)  // default: warp-specialised, pipelined kernels
     return attn::launch_bwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, dout, q, k, v, o, lse, dq, dk,
-                                 dv, delta, B, H, S, scale, st);
+                                 dv, delta, B, H, H, S, scale, st);
   if (D == 128) {
     return dtype == EVG_BF16
                ? launch_bwd<128, 1>(dout, q, k, v, o, lse, dq, dk, dv, delta, B, H, S, scale, st)
@@ -713,3 +713,74 @@ extern "C" int evg_causal_attention_bwd(const void* dout, const void* q, const v
              : launch_bwd<64, 0>(dout, q, k, v, o, lse, dq, dk, dv, delta, B, H, S, scale, st);
 }
 
+
+// ---------------------------------------------------- grouped-query attention
+namespace {
+bool tensor_core_shape(int64_t D, int dtype) {
+  return (D == 64 || D == 128) && (dtype == EVG_BF16 || dtype == EVG_F16);
+}
+int check_gqa_args(const char* what, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                   int dtype) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0)
+    return fail(EVG_EBADSHAPE, "%s: B=%lld Hq=%lld Hkv=%lld S=%lld D=%lld must be positive", what,
+                (long long)B, (long long)Hq, (long long)Hkv, (long long)S, (long long)D);
+  if (Hq % Hkv != 0)
+    return fail(EVG_EBADSHAPE, "%s: %lld query heads are not a multiple of %lld k/v heads", what,
+                (long long)Hq, (long long)Hkv);
+  if (dtype != EVG_BF16 && dtype != EVG_F16 && dtype != EVG_F32)
+    return fail(EVG_EDTYPE, "%s: dtype %d", what, dtype);
+  if (D > 256) return fail(EVG_EUNSUPPORTED, "%s: head_dim %lld > 256", what, (long long)D);
+  if (B * Hq > 65535 || S > (1 << 24))
+    return fail(EVG_EUNSUPPORTED, "%s: B*Hq=%lld (max 65535) or S=%lld too large", what,
+                (long long)(B * Hq), (long long)S);
+  return EVG_OK;
+}
+}  // namespace
+
+extern "C" int evg_causal_gqa_attention_fwd(const void* q, const void* k, const void* v, void* o,
+                                            float* lse, int64_t B, int64_t Hq, int64_t Hkv,
+                                            int64_t S, int64_t D, float scale, int dtype,
+                                            void* stream) {
+  if (!q || !k || !v || !o || !lse)
+    return fail(EVG_ENULL, "causal_gqa_attention_fwd: null pointer argument");
+  if (int rc = check_gqa_args("causal_gqa_attention_fwd", B, Hq, Hkv, S, D, dtype)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tensor_core_shape(D, dtype) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o))
+    return attn::launch_fwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, q, k, v, o, lse, B, Hq, Hkv, S,
+                                 scale, st);
+  return attn::launch_generic_fwd(dtype, q, k, v, o, lse, B, Hq, Hkv, S, D, scale, st);
+}
+
+extern "C" int64_t evg_causal_gqa_attention_bwd_workspace_bytes(int64_t B, int64_t Hq,
+                                                                int64_t Hkv, int64_t S, int64_t D,
+                                                                int dtype) {
+  (void)Hkv;
+  if (B <= 0 || Hq <= 0 || S <= 0) return 0;
+  // the tensor-core path needs the larger scratch; it also covers the generic one
+  (void)D; (void)dtype;
+  return attn::bwd2_workspace_bytes(B, Hq, S);
+}
+
+extern "C" int evg_causal_gqa_attention_bwd(const void* dout, const void* q, const void* k,
+                                            const void* v, const void* o, const float* lse,
+                                            void* dq, void* dk, void* dv, void* workspace,
+                                            int64_t workspace_bytes, int64_t B, int64_t Hq,
+                                            int64_t Hkv, int64_t S, int64_t D, float scale,
+                                            int dtype, void* stream) {
+  if (!dout || !q || !k || !v || !o || !lse || !dq || !dk || !dv)
+    return fail(EVG_ENULL, "causal_gqa_attention_bwd: null pointer argument");
+  if (int rc = check_gqa_args("causal_gqa_attention_bwd", B, Hq, Hkv, S, D, dtype)) return rc;
+  const int64_t need = evg_causal_gqa_attention_bwd_workspace_bytes(B, Hq, Hkv, S, D, dtype);
+  if (!workspace || workspace_bytes < need)
+    return fail(EVG_EWORKSPACE, "causal_gqa_attention_bwd: workspace %lld bytes, need %lld",
+                (long long)workspace_bytes, (long long)need);
+  cudaStream_t st = (cudaStream_t)stream;
+  bool aligned = aligned16(workspace);
+  for (const void* p : {dout, q, k, v, o, (const void*)dq, (const void*)dk, (const void*)dv})
+    aligned = aligned && aligned16(p);
+  if (tensor_core_shape(D, dtype) && aligned)
+    return attn::launch_bwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, dout, q, k, v, o, lse, dq, dk,
+                                 dv, (float*)workspace, B, Hq, Hkv, S, scale, st);
+  return attn::launch_generic_bwd(dtype, dout, q, k, v, o, lse, dq, dk, dv, workspace,
+                                  workspace_bytes, B, Hq, Hkv, S, D, scale, st);
+}

@@ -134,7 +134,8 @@ __global__ void __launch_bounds__(kThreads2, 1)
 attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                     const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
-                    void* __restrict__ dq_ptr, int S, int S_pad, float scale, long long wait_limit) {
+                    void* __restrict__ dq_ptr, int S, int S_pad, int group, float scale,
+                    long long wait_limit) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   BlockSetup bs = carve(smem_raw, 7 * TB);
@@ -157,6 +158,7 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const Roles r = roles();
   const int qtile = gridDim.x - 1 - blockIdx.x;  // heaviest tiles first
   const int bh = blockIdx.y;
+  const int bh_kv = bh / group;  // `group` query heads share one k/v head
   const int q0 = qtile * kTile;
   const int n_it = qtile + 1;
   const float scale_log2 = scale * kLog2e;
@@ -194,10 +196,10 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int ks = j % 3, vs = j & 1;
       if (j >= 3) mbar_wait(k_empty + ks, ((j / 3) - 1) & 1, ctx, 501);
       mbar_expect_tx(k_full + ks, TB);
-      load_tile<HD>(sK[ks], &map_k, j * kTile, bh, k_full + ks);
+      load_tile<HD>(sK[ks], &map_k, j * kTile, bh_kv, k_full + ks);
       if (j >= 2) mbar_wait(v_empty + vs, ((j >> 1) - 1) & 1, ctx, 510);
       mbar_expect_tx(v_full + vs, TB);
-      load_tile<HD>(sV[vs], &map_v, j * kTile, bh, v_full + vs);
+      load_tile<HD>(sV[vs], &map_v, j * kTile, bh_kv, v_full + vs);
     }
   } else if (r.is_mma) {
     // All 32 lanes run this program; `lead` predicates the tcgen05 instructions.
@@ -313,7 +315,7 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                       const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
                       void* __restrict__ dk_ptr, void* __restrict__ dv_ptr, int S, int S_pad,
-                      float scale, long long wait_limit) {
+                      int group, float scale, long long wait_limit) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   BlockSetup bs = carve(smem_raw, 6 * TB + 2048);
@@ -334,7 +336,11 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const int kv0 = kvt * kTile;
   const int n_q = S_pad / kTile;
   const int n_it = n_q - kvt;
-  const int n_chunks = 2 * n_it;
+  // Grouped-query attention: the block owns key tile `kvt` of k/v head `bh` and
+  // walks the query tiles of each of the `group` query heads bh*group + hh in
+  // turn (iteration git = hh * n_it + it), accumulating dK/dV in TMEM across them.
+  const int n_git = group * n_it;
+  const int n_chunks = 2 * n_git;
   const float scale_log2 = scale * kLog2e;
 
   if (threadIdx.x == 0) {
@@ -365,15 +371,20 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     mbar_expect_tx(kv_full, 2 * TB);
     load_tile<HD>(sK, &map_k, kv0, bh, kv_full);
     load_tile<HD>(sV, &map_v, kv0, bh, kv_full);
-    for (int it = 0; it < n_it; ++it) {
-      const int st = it & 1;
+    int it = 0, bhq = bh * group;
+    for (int git = 0; git < n_git; ++git) {
+      const int st = git & 1;
       const int q0 = (kvt + it) * kTile;
-      if (it >= 2) mbar_wait(q_empty + st, ((it - 2) >> 1) & 1, ctx, 601);
+      if (git >= 2) mbar_wait(q_empty + st, ((git - 2) >> 1) & 1, ctx, 601);
       mbar_expect_tx(q_full + st, 2 * TB + 1024);
-      load_tile<HD>(sQ[st], &map_q, q0, bh, q_full + st);
-      load_tile<HD>(sDO[st], &map_do, q0, bh, q_full + st);
-      bulk_load_1d(s_stat + st * 256, lse2_pad + (size_t)bh * S_pad + q0, 512, q_full + st);
-      bulk_load_1d(s_stat + st * 256 + 128, delta_pad + (size_t)bh * S_pad + q0, 512, q_full + st);
+      load_tile<HD>(sQ[st], &map_q, q0, bhq, q_full + st);
+      load_tile<HD>(sDO[st], &map_do, q0, bhq, q_full + st);
+      bulk_load_1d(s_stat + st * 256, lse2_pad + (size_t)bhq * S_pad + q0, 512, q_full + st);
+      bulk_load_1d(s_stat + st * 256 + 128, delta_pad + (size_t)bhq * S_pad + q0, 512, q_full + st);
+      if (++it == n_it) {
+        it = 0;
+        ++bhq;
+      }
     }
   } else if (r.is_mma) {
     const bool lead = elect_one();
@@ -431,9 +442,10 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   } else if (r.is_compute) {
     const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
     const int kv_glob = kv0 + r.row;
+    int it = 0;  // query-tile index within the current query head
     for (int c = 0; c < n_chunks; ++c) {
-      const int b = c & 1, it = c >> 1, st = it & 1, hq = c & 1;
-      if (hq == 0) mbar_wait(q_full + st, (it >> 1) & 1, ctx, 606);  // row statistics landed
+      const int b = c & 1, git = c >> 1, st = git & 1, hq = c & 1;
+      if (hq == 0) mbar_wait(q_full + st, (git >> 1) & 1, ctx, 606);  // row statistics landed
       mbar_wait(sdp_full + b, (c >> 1) & 1, ctx, 607);
       __syncwarp();
       tc_fence_after_sync();
@@ -481,6 +493,7 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tmem_st16(tPb[b] + lane_base + r.half * 32, dd);
       tmem_wait_st();
       warp_arrive(pds_full + b, r.lane);
+      if (hq == 1 && ++it == n_it) it = 0;
     }
     mbar_wait(done, 0, ctx, 608);
     __syncwarp();
@@ -512,11 +525,12 @@ int reserve_smem(Kernel kernel, size_t bytes) {
 template <int HD, int FMT>
 int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, const void* o,
                 const float* lse, void* dq, void* dk, void* dv, float* workspace, int64_t B,
-                int64_t H, int64_t S, float scale, cudaStream_t stream) {
+                int64_t H, int64_t Hkv, int64_t S, float scale, cudaStream_t stream) {
   CUtensorMap mq, mk, mv, mdo;
+  const int group = (int)(H / Hkv);
   if (!encode_tile_map_16bit(&mq, q, FMT, HD, S, B * H, kTile) ||
-      !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * H, kTile) ||
-      !encode_tile_map_16bit(&mv, v, FMT, HD, S, B * H, kTile) ||
+      !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * Hkv, kTile) ||
+      !encode_tile_map_16bit(&mv, v, FMT, HD, S, B * Hkv, kTile) ||
       !encode_tile_map_16bit(&mdo, dout, FMT, HD, S, B * H, kTile))
     return fail(EVG_ELAUNCH, "causal_attention_bwd: cuTensorMapEncodeTiled failed");
   const int64_t n_q = (S + kTile - 1) / kTile;
@@ -537,8 +551,9 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
     const size_t smem = 6 * tile_bytes<HD>() + 2048 + kControlBytes + 1024;
     auto kern = attn_bwd2_dkdv_kernel<HD, FMT>;
     if (int rc = reserve_smem(kern, smem)) return rc;
-    kern<<<grid, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv, (int)S,
-                                            (int)S_pad, scale, limit);
+    dim3 grid_kv((unsigned)n_q, (unsigned)(B * Hkv));
+    kern<<<grid_kv, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
+                                               (int)S, (int)S_pad, group, scale, limit);
     if (int rc = check_launch("causal_attention_bwd dkdv")) return rc;
   }
   {
@@ -546,7 +561,7 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
     auto kern = attn_bwd2_dq_kernel<HD, FMT>;
     if (int rc = reserve_smem(kern, smem)) return rc;
     kern<<<grid, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq, (int)S,
-                                            (int)S_pad, scale, limit);
+                                            (int)S_pad, group, scale, limit);
     if (int rc = check_launch("causal_attention_bwd dq")) return rc;
   }
   return EVG_OK;
@@ -578,15 +593,17 @@ int64_t bwd2_workspace_bytes(int64_t B, int64_t H, int64_t S) {
 
 int launch_bwd2_any(int head_dim, int fmt, const void* dout, const void* q, const void* k,
                     const void* v, const void* o, const float* lse, void* dq, void* dk, void* dv,
-                    float* workspace, int64_t B, int64_t H, int64_t S, float scale,
+                    float* workspace, int64_t B, int64_t H, int64_t Hkv, int64_t S, float scale,
                     cudaStream_t stream) {
   if (head_dim == 128)
-    return fmt == 1
-               ? launch_bwd2<128, 1>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, S, scale, stream)
-               : launch_bwd2<128, 0>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, S, scale, stream);
-  return fmt == 1
-             ? launch_bwd2<64, 1>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, S, scale, stream)
-             : launch_bwd2<64, 0>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, S, scale, stream);
+    return fmt == 1 ? launch_bwd2<128, 1>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, Hkv,
+                                          S, scale, stream)
+                    : launch_bwd2<128, 0>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, Hkv,
+                                          S, scale, stream);
+  return fmt == 1 ? launch_bwd2<64, 1>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, Hkv, S,
+                                       scale, stream)
+                  : launch_bwd2<64, 0>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, Hkv, S,
+                                       scale, stream);
 }
 
 }  // namespace attn

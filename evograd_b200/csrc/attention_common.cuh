@@ -91,15 +91,28 @@ __device__ __forceinline__ BlockSetup carve(uint8_t* raw, size_t tile_region_byt
 constexpr size_t kControlBytes = 24 * 8 + 64;
 
 // Two-tile warp-specialised forward (attention_fwd2.cu).
+// H query heads share Hkv key/value heads (H % Hkv == 0; Hkv == H is plain
+// multi-head attention): query head h reads k/v head h / (H / Hkv).
 int launch_fwd2_any(int head_dim, int fmt, const void* q, const void* k, const void* v, void* o,
-                    float* lse, int64_t B, int64_t H, int64_t S, float scale, cudaStream_t stream);
+                    float* lse, int64_t B, int64_t H, int64_t Hkv, int64_t S, float scale,
+                    cudaStream_t stream);
 // Pipelined backward (attention_bwd2.cu): scratch = two float32 arrays padded
 // to whole tiles per (batch, head). fmt: 0 float16, 1 bfloat16.
 int64_t bwd2_workspace_bytes(int64_t B, int64_t H, int64_t S);
 int launch_bwd2_any(int head_dim, int fmt, const void* dout, const void* q, const void* k,
                     const void* v, const void* o, const float* lse, void* dq, void* dk, void* dv,
-                    float* workspace, int64_t B, int64_t H, int64_t S, float scale,
+                    float* workspace, int64_t B, int64_t H, int64_t Hkv, int64_t S, float scale,
                     cudaStream_t stream);
+// CUDA-core kernels for float32 and head sizes other than 64 / 128
+// (attention_generic.cu). Scratch: one float32 per query row.
+int64_t generic_bwd_workspace_bytes(int64_t B, int64_t Hq, int64_t S);
+int launch_generic_fwd(int dtype, const void* q, const void* k, const void* v, void* o,
+                       float* lse, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                       float scale, cudaStream_t stream);
+int launch_generic_bwd(int dtype, const void* dout, const void* q, const void* k, const void* v,
+                       const void* o, const float* lse, void* dq, void* dk, void* dv,
+                       void* workspace, int64_t workspace_bytes, int64_t B, int64_t Hq,
+                       int64_t Hkv, int64_t S, int64_t D, float scale, cudaStream_t stream);
 
 }  // namespace attn
 }  // namespace evg

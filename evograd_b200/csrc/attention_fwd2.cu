@@ -33,7 +33,8 @@ template <int HD, int FMT>
 __global__ void __launch_bounds__(kFwd2Threads, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, void* __restrict__ o_ptr,
-                 float* __restrict__ lse_ptr, int S, float scale_log2, long long wait_limit) {
+                 float* __restrict__ lse_ptr, int S, int group, float scale_log2,
+                 long long wait_limit) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   BlockSetup bs = carve(smem_raw, 6 * TB);
@@ -52,6 +53,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const int n_tiles = (S + kTile - 1) / kTile;
   const int pair = gridDim.x - 1 - blockIdx.x;  // heaviest pairs first
   const int bh = blockIdx.y;
+  const int bh_kv = bh / group;  // grouped-query attention: `group` query heads per k/v head
   const int qt[2] = {2 * pair, 2 * pair + 1};
   const bool b_active = qt[1] < n_tiles;
   const int n_kv[2] = {qt[0] + 1, b_active ? qt[1] + 1 : 0};
@@ -89,10 +91,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int st = j & 1;
         if (j >= 2) mbar_wait(k_empty + st, ((j >> 1) - 1) & 1, ctx, 701);
         mbar_expect_tx(k_full + st, TB);
-        load_tile<HD>(sK[st], &map_k, j * kTile, bh, k_full + st);
+        load_tile<HD>(sK[st], &map_k, j * kTile, bh_kv, k_full + st);
         if (j >= 2) mbar_wait(v_empty + st, ((j >> 1) - 1) & 1, ctx, 702);
         mbar_expect_tx(v_full + st, TB);
-        load_tile<HD>(sV[st], &map_v, j * kTile, bh, v_full + st);
+        load_tile<HD>(sV[st], &map_v, j * kTile, bh_kv, v_full + st);
       }
     }
   } else if (warp == 1) {
@@ -272,11 +274,11 @@ const bool g_fwd2_status_registered = (register_device_status(read_fwd2_status),
 
 template <int HD, int FMT>
 int launch_fwd2(const void* q, const void* k, const void* v, void* o, float* lse, int64_t B,
-                int64_t H, int64_t S, float scale, cudaStream_t stream) {
+                int64_t H, int64_t Hkv, int64_t S, float scale, cudaStream_t stream) {
   CUtensorMap mq, mk, mv;
   if (!encode_tile_map_16bit(&mq, q, FMT, HD, S, B * H, kTile) ||
-      !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * H, kTile) ||
-      !encode_tile_map_16bit(&mv, v, FMT, HD, S, B * H, kTile))
+      !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * Hkv, kTile) ||
+      !encode_tile_map_16bit(&mv, v, FMT, HD, S, B * Hkv, kTile))
     return fail(EVG_ELAUNCH, "causal_attention_fwd: cuTensorMapEncodeTiled failed");
   const size_t smem = 6 * tile_bytes<HD>() + kControlBytes + 1024;
   auto kern = attn_fwd2_kernel<HD, FMT>;
@@ -289,7 +291,8 @@ int launch_fwd2(const void* q, const void* k, const void* v, void* o, float* lse
   dim3 grid((unsigned)((n_tiles + 1) / 2), (unsigned)(B * H));
   const int t = tune("attention.wait_limit");
   const long long limit = t > 0 ? (long long)t * 1000000ll : 2000000000ll;
-  kern<<<grid, kFwd2Threads, smem, stream>>>(mq, mk, mv, o, lse, (int)S, scale * kLog2e, limit);
+  kern<<<grid, kFwd2Threads, smem, stream>>>(mq, mk, mv, o, lse, (int)S, (int)(H / Hkv),
+                                             scale * kLog2e, limit);
   return check_launch("causal_attention_fwd");
 }
 
@@ -298,12 +301,13 @@ int launch_fwd2(const void* q, const void* k, const void* v, void* o, float* lse
 namespace attn {
 
 int launch_fwd2_any(int head_dim, int fmt, const void* q, const void* k, const void* v, void* o,
-                    float* lse, int64_t B, int64_t H, int64_t S, float scale, cudaStream_t stream) {
+                    float* lse, int64_t B, int64_t H, int64_t Hkv, int64_t S, float scale,
+                    cudaStream_t stream) {
   if (head_dim == 128)
-    return fmt == 1 ? launch_fwd2<128, 1>(q, k, v, o, lse, B, H, S, scale, stream)
-                    : launch_fwd2<128, 0>(q, k, v, o, lse, B, H, S, scale, stream);
-  return fmt == 1 ? launch_fwd2<64, 1>(q, k, v, o, lse, B, H, S, scale, stream)
-                  : launch_fwd2<64, 0>(q, k, v, o, lse, B, H, S, scale, stream);
+    return fmt == 1 ? launch_fwd2<128, 1>(q, k, v, o, lse, B, H, Hkv, S, scale, stream)
+                    : launch_fwd2<128, 0>(q, k, v, o, lse, B, H, Hkv, S, scale, stream);
+  return fmt == 1 ? launch_fwd2<64, 1>(q, k, v, o, lse, B, H, Hkv, S, scale, stream)
+                  : launch_fwd2<64, 0>(q, k, v, o, lse, B, H, Hkv, S, scale, stream);
 }
 
 }  // namespace attn

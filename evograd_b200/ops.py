@@ -428,6 +428,65 @@ def causal_attention_bwd(do, q, k, v, o, lse, scale: float | None = None):
     return dq, dk, dv
 
 
+def _check_gqa(q, k, v):
+    if q.ndim != 4 or k.ndim != 4:
+        raise ValueError(f"attention expects [B, H, S, D], got {tuple(q.shape)} / {tuple(k.shape)}")
+    _same("k", k, "v", v)
+    if q.dtype != k.dtype or q.device != k.device:
+        raise ValueError("q and k must share dtype and device")
+    B, Hq, S, D = q.shape
+    if k.shape[0] != B or k.shape[2] != S or k.shape[3] != D or Hq % k.shape[1] != 0:
+        raise ValueError(f"q {tuple(q.shape)} and k/v {tuple(k.shape)} do not form grouped-query "
+                         "attention (same B, S, D; query heads a multiple of k/v heads)")
+    return B, Hq, k.shape[1], S, D
+
+
+def causal_gqa_attention_fwd(q, k, v, scale: float | None = None):
+    """Causal attention with ``Hq`` query heads sharing ``Hkv`` key/value heads:
+    q ``[B, Hq, S, D]``, k/v ``[B, Hkv, S, D]`` (any of float32 / float16 / bfloat16,
+    D <= 256; 16-bit with D in {64, 128} runs on the tensor cores). Returns
+    ``(o, lse)`` with ``lse`` float32 ``[B, Hq, S]``."""
+    dev = _require_cuda(q, k, v)
+    B, Hq, Hkv, S, D = _check_gqa(q, k, v)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    q2, k2, v2 = q.contiguous(), k.contiguous(), v.contiguous()
+    o = torch.empty_like(q2)
+    lse = torch.empty(B, Hq, S, device=dev, dtype=torch.float32)
+    if q2.numel() == 0:
+        return o, lse
+    with torch.cuda.device(dev):
+        call("evg_causal_gqa_attention_fwd", q2.data_ptr(), k2.data_ptr(), v2.data_ptr(),
+             o.data_ptr(), lse.data_ptr(), B, Hq, Hkv, S, D, float(scale), _dtype_enum(q),
+             _stream(dev))
+    return o, lse
+
+
+def causal_gqa_attention_bwd(do, q, k, v, o, lse, scale: float | None = None):
+    """Returns ``(dq, dk, dv)``; dk/dv are summed over the query heads of each group."""
+    dev = _require_cuda(do, q, k, v, o, lse)
+    B, Hq, Hkv, S, D = _check_gqa(q, k, v)
+    _same("do", do, "q", q)
+    _same("o", o, "q", q)
+    if lse.dtype != torch.float32 or tuple(lse.shape) != (B, Hq, S):
+        raise ValueError("lse must be float32 [B, Hq, S]")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    do2, q2, k2, v2, o2 = (t.contiguous() for t in (do, q, k, v, o))
+    dq, dk, dv = torch.empty_like(q2), torch.empty_like(k2), torch.empty_like(v2)
+    if q2.numel() == 0:
+        return dq, dk, dv
+    en = _dtype_enum(q)
+    with torch.cuda.device(dev):
+        ws_bytes = lib.evg_causal_gqa_attention_bwd_workspace_bytes(B, Hq, Hkv, S, D, en)
+        ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
+        call("evg_causal_gqa_attention_bwd", do2.data_ptr(), q2.data_ptr(), k2.data_ptr(),
+             v2.data_ptr(), o2.data_ptr(), lse.contiguous().data_ptr(), dq.data_ptr(),
+             dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws_bytes, B, Hq, Hkv, S, D, float(scale),
+             en, _stream(dev))
+    return dq, dk, dv
+
+
 def device_status(reset: bool = True) -> None:
     """Synchronise and raise :class:`EvgError` (EVG_ETIMEOUT) if a bounded wait inside
     an attention kernel gave up since the last reset."""

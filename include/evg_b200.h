@@ -279,6 +279,31 @@ int evg_causal_attention_bwd(const void* dout, const void* q, const void* k,
                              int64_t S, int64_t D, float scale, int dtype,
                              void* stream);
 
+/* ------------------------------------------- causal grouped-query attention
+ * The same attention with Hq query heads sharing Hkv key/value heads
+ * (Hq % Hkv == 0): q, o, dout, dq are [B,Hq,S,D]; k, v, dk, dv are [B,Hkv,S,D];
+ * query head h reads k/v head h / (Hq/Hkv); dk/dv sum over the query heads of
+ * a group inside one block (deterministic, no atomics). Equivalent to
+ * repeat_interleave of k and v followed by scaled_dot_product_attention, as at
+ * ops/level3/llama3_decoder_layer/forward_ref.py:100-107, without materialising
+ * the repeated tensors. 16-bit inputs with D in {64,128} run on the tensor-core
+ * kernels; float32 inputs and other head sizes (D <= 256; the decoder block's
+ * small correctness shapes, __init__.py:52-61) run on plain CUDA-core kernels.
+ */
+int evg_causal_gqa_attention_fwd(const void* q, const void* k, const void* v,
+                                 void* o, float* lse, int64_t B, int64_t Hq,
+                                 int64_t Hkv, int64_t S, int64_t D, float scale,
+                                 int dtype, void* stream);
+int64_t evg_causal_gqa_attention_bwd_workspace_bytes(int64_t B, int64_t Hq,
+                                                     int64_t Hkv, int64_t S,
+                                                     int64_t D, int dtype);
+int evg_causal_gqa_attention_bwd(const void* dout, const void* q, const void* k,
+                                 const void* v, const void* o, const float* lse,
+                                 void* dq, void* dk, void* dv, void* workspace,
+                                 int64_t workspace_bytes, int64_t B, int64_t Hq,
+                                 int64_t Hkv, int64_t S, int64_t D, float scale,
+                                 int dtype, void* stream);
+
 /*
  * Synchronises the current device (the one exception to "nothing synchronises")
  * and reports the sticky device-side status of the attention kernels: every

@@ -108,6 +108,18 @@ def causal_attention_forward_sdpa(q, k, v):
     return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
 
 
+def causal_gqa_attention_forward(q, k, v):
+    """Grouped-query causal attention as the decoder block spells it
+    (ops/level3/llama3_decoder_layer/forward_ref.py:100-107): each k/v head is
+    repeated across its query group, then scaled_dot_product_attention.
+    q is [B, Hq, S, D]; k, v are [B, Hkv, S, D]."""
+    repeat = q.shape[1] // k.shape[1]
+    if repeat > 1:
+        k = k.repeat_interleave(repeat, dim=1)
+        v = v.repeat_interleave(repeat, dim=1)
+    return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+
+
 # --------------------------------------------------------------------------
 # declarations (only what the oracle needs from opdecl/activity.py:179-337)
 

@@ -162,3 +162,43 @@ def test_bad_arguments_raise():
     q32 = torch.zeros(1, 1, 64, 128, device="cuda")
     with pytest.raises(TypeError):
         ops.causal_attention_fwd(q32, q32, q32)
+
+
+GQA_SHAPES = [
+    # (B, Hq, Hkv, S, D, dtype): tensor-core path
+    (1, 8, 2, 300, 128, "bfloat16"), (2, 4, 1, 129, 64, "float16"), (1, 4, 4, 128, 128, "bfloat16"),
+    (1, 6, 3, 513, 128, "bfloat16"),
+    # CUDA-core path: float32 and other head sizes (the decoder block's small cases)
+    (2, 4, 1, 17, 16, "float32"), (1, 4, 1, 32, 32, "float32"), (1, 2, 2, 200, 128, "float32"),
+    (1, 4, 2, 77, 80, "bfloat16"), (1, 2, 1, 65, 32, "float16"), (1, 3, 1, 40, 256, "float32"),
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,D,dtype", GQA_SHAPES)
+def test_grouped_query_attention_matches_the_oracle(B, Hq, Hkv, S, D, dtype):
+    from evograd_b200 import ops
+
+    dt = getattr(torch, dtype)
+    torch.manual_seed(S * 1009 + D * 31 + Hq)
+    q = (torch.randn(B, Hq, S, D) * 0.5).to(dt)
+    k = (torch.randn(B, Hkv, S, D) * 0.5).to(dt)
+    v = (torch.randn(B, Hkv, S, D) * 0.5).to(dt)
+    do = (torch.randn(B, Hq, S, D) * 0.5).to(dt)
+    qr, kr, vr = (t.float().requires_grad_(True) for t in (q, k, v))
+    o_ref = ao.causal_gqa_attention_forward(qr, kr, vr)
+    g_ref = torch.autograd.grad(o_ref, [qr, kr, vr], grad_outputs=do.float())
+    qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+    o, lse = ops.causal_gqa_attention_fwd(qd, kd, vd)
+    dq, dk, dv = ops.causal_gqa_attention_bwd(dod, qd, kd, vd, o, lse)
+    assert tuple(lse.shape) == (B, Hq, S) and dk.shape == k.shape and dv.shape == v.shape
+    if dtype == "float32":
+        tol_o, tol_g = (1e-5, 1e-5), (2e-5, 1e-5)
+    else:
+        tol_o, tol_g = O_TOL, (GRAD_MAX_ABS, 0.0)
+    checks = [ao.check("o", o, o_ref.detach().to(dt), *tol_o)]
+    for n, got, ref in zip(("dq", "dk", "dv"), (dq, dk, dv), g_ref):
+        checks.append(ao.check(n, got, ref.to(dt), *tol_g))
+    assert_checks(checks, f"gqa {B}x{Hq}/{Hkv}x{S}x{D} {dtype}")
+    # deterministic: same bits on a second run
+    dq2, dk2, dv2 = ops.causal_gqa_attention_bwd(dod, qd, kd, vd, o, lse)
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2) and torch.equal(dq, dq2)
