@@ -321,8 +321,12 @@ def geglu_bwd(dc, a, b, *, in_place: bool = False):
 
 
 # --------------------------------------------------------------------- rope
-def _rope_launch(xs, layout: str, cos, sin, inverse: bool):
-    """Rotate 1 or 2 tensors in one launch. ``layout`` is "bhtd" or "bthd"."""
+def _rope_launch(xs, layout: str, cos, sin, inverse: bool, outs=None):
+    """Rotate 1 or 2 tensors in one launch. ``layout`` is "bhtd" or "bthd" and names
+    the axis order of the tensors' SHAPES; inputs and outputs may be strided views
+    (last dimension contiguous), so a rotation can also change the memory layout
+    (for example read [B, T, H, D] memory through a transposed view and write
+    contiguous [B, H, T, D]). ``outs`` supplies the output tensors."""
     dev = _require_cuda(*xs, cos, sin)
     if layout not in ("bhtd", "bthd"):
         raise ValueError(f"layout must be 'bhtd' or 'bthd', got {layout!r}")
@@ -344,13 +348,20 @@ def _rope_launch(xs, layout: str, cos, sin, inverse: bool):
         raise ValueError(f"table width {cos.shape[1]} is neither head_dim nor head_dim/2")
     cos, sin = cos.contiguous(), sin.contiguous()
     arr = (RopeTensor * len(xs))()
-    outs = []
+    given, outs = outs, []
     keep = []
     for i, x in enumerate(xs):
         if x.stride(3) != 1:
             x = x.contiguous()
         keep.append(x)
-        y = torch.empty(x.shape, device=dev, dtype=x.dtype)
+        if given is None:
+            y = torch.empty(x.shape, device=dev, dtype=x.dtype)
+        else:
+            y = given[i]
+            if tuple(y.shape) != tuple(x.shape) or y.dtype != x.dtype or y.stride(3) != 1 \
+                    or y.device != x.device:
+                raise ValueError("rope output must match the input's shape, dtype and device and "
+                                 "have a contiguous last dimension")
         outs.append(y)
         arr[i] = RopeTensor(x.data_ptr(), y.data_ptr(), x.shape[h_axis], x.stride(0),
                             x.stride(h_axis), x.stride(t_axis), y.stride(0), y.stride(h_axis),
@@ -361,21 +372,21 @@ def _rope_launch(xs, layout: str, cos, sin, inverse: bool):
     return outs
 
 
-def rope_fwd(x, cos, sin, *, layout: str = "bhtd"):
-    return _rope_launch([x], layout, cos, sin, False)[0]
+def rope_fwd(x, cos, sin, *, layout: str = "bhtd", out=None):
+    return _rope_launch([x], layout, cos, sin, False, None if out is None else [out])[0]
 
 
-def rope_bwd(dy, cos, sin, *, layout: str = "bhtd"):
-    return _rope_launch([dy], layout, cos, sin, True)[0]
+def rope_bwd(dy, cos, sin, *, layout: str = "bhtd", out=None):
+    return _rope_launch([dy], layout, cos, sin, True, None if out is None else [out])[0]
 
 
-def rope_qk_fwd(q, k, cos, sin, *, layout: str = "bthd"):
+def rope_qk_fwd(q, k, cos, sin, *, layout: str = "bthd", outs=None):
     """Rotate q and k (possibly different head counts) in one launch."""
-    return tuple(_rope_launch([q, k], layout, cos, sin, False))
+    return tuple(_rope_launch([q, k], layout, cos, sin, False, outs))
 
 
-def rope_qk_bwd(dq, dk, cos, sin, *, layout: str = "bthd"):
-    return tuple(_rope_launch([dq, dk], layout, cos, sin, True))
+def rope_qk_bwd(dq, dk, cos, sin, *, layout: str = "bthd", outs=None):
+    return tuple(_rope_launch([dq, dk], layout, cos, sin, True, outs))
 
 
 # --------------------------------------------------------- causal attention

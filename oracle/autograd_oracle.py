@@ -120,6 +120,43 @@ def causal_gqa_attention_forward(q, k, v):
     return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
 
 
+def llama3_decoder_layer_forward(x, input_norm_weight, q_weight, k_weight, v_weight, o_weight,
+                                 post_norm_weight, gate_weight, up_weight, down_weight, cos, sin,
+                                 eps=1e-5):
+    """One Llama-3 decoder layer, ops/level3/llama3_decoder_layer/forward_ref.py:53-117:
+    RMSNorm (float32 statistics, normalised value cast to the input dtype, then
+    the gain) -> q/k/v projections (weights [out, in]) -> rotate-half RoPE in
+    float32 -> grouped-query causal SDPA -> o projection + residual -> RMSNorm
+    -> silu(gate.float()) * up.float() cast back -> down projection + residual.
+    Head counts come from the weight shapes and cos.shape[-1]."""
+    F = torch.nn.functional
+
+    def rms_norm(t, w):  # forward_ref.py:33-37
+        t32 = t.float()
+        rrms = torch.rsqrt(t32.pow(2).mean(-1, keepdim=True) + eps)
+        return (t32 * rrms).to(t.dtype) * w
+
+    def rope(t):  # forward_ref.py:40-50
+        half = t.shape[-1] // 2
+        t32 = t.float()
+        rot = torch.cat((-t32[..., half:], t32[..., :half]), dim=-1)
+        return (t32 * cos[None, None].float() + rot * sin[None, None].float()).to(t.dtype)
+
+    batch, tokens, _hidden = x.shape
+    head_dim = cos.shape[-1]
+    n_heads, n_kv = q_weight.shape[0] // head_dim, k_weight.shape[0] // head_dim
+    h = rms_norm(x, input_norm_weight)
+    q = F.linear(h, q_weight).view(batch, tokens, n_heads, head_dim).transpose(1, 2)
+    k = F.linear(h, k_weight).view(batch, tokens, n_kv, head_dim).transpose(1, 2)
+    v = F.linear(h, v_weight).view(batch, tokens, n_kv, head_dim).transpose(1, 2)
+    attn = causal_gqa_attention_forward(rope(q), rope(k), v)
+    attn = attn.transpose(1, 2).reshape(batch, tokens, n_heads * head_dim)
+    x = x + F.linear(attn, o_weight)
+    h = rms_norm(x, post_norm_weight)
+    act = (F.silu(F.linear(h, gate_weight).float()) * F.linear(h, up_weight).float()).to(h.dtype)
+    return x + F.linear(act, down_weight)
+
+
 # --------------------------------------------------------------------------
 # declarations (only what the oracle needs from opdecl/activity.py:179-337)
 
@@ -186,6 +223,14 @@ def _fused_add_rms_norm_tolerance(dims, dtype, result, atol, rtol):
     return atol, rtol
 
 
+def _decoder_layer_tolerance(dims, dtype, result, atol, rtol):
+    """ops/level3/llama3_decoder_layer/__init__.py:228-233: the three longest
+    reductions get 1.5x the atol."""
+    if result in ("dk_weight", "dv_weight", "ddown_weight"):
+        atol = atol * 1.5
+    return atol, rtol
+
+
 OPS = {
     "softmax": OpSpec("softmax", softmax_forward, (("x", True),), "y", dims=("rows", "cols")),
     "layernorm": OpSpec(
@@ -205,6 +250,18 @@ OPS = {
         (("x", True), ("r", True), ("weight", True)), "out",
         scalars={"eps": 1e-6}, dims=("rows", "cols"),
         tolerance_hook=_fused_add_rms_norm_tolerance, strict_exempt=("dweight",),
+    ),
+    # reference_dtype is float32 in the declaration: always check this operator
+    # with oracle(..., reference_dtype=torch.float32).
+    "llama3_decoder_layer": OpSpec(
+        "llama3_decoder_layer", llama3_decoder_layer_forward,
+        (("x", True), ("input_norm_weight", True), ("q_weight", True), ("k_weight", True),
+         ("v_weight", True), ("o_weight", True), ("post_norm_weight", True), ("gate_weight", True),
+         ("up_weight", True), ("down_weight", True), ("cos", False), ("sin", False)), "out",
+        scalars={"eps": 1e-5},
+        dims=("B", "T", "hidden", "head_dim", "q_out", "kv_out", "intermediate"),
+        tolerances={"float32": (1e-4, 1e-4), "bfloat16": (5e-2, 2e-2)},
+        tolerance_hook=_decoder_layer_tolerance,
     ),
     "rope": OpSpec("rope", rope_forward, (("x", True), ("cos", False), ("sin", False)), "y",
                    dims=("B", "n_heads", "T", "head_dim")),
@@ -268,6 +325,39 @@ def make_inputs(op: str, dims: dict, dtype: str, device: str = "cpu") -> dict:
                 "weight": torch.randn((c,), device=device, dtype=dt),
                 "eps": 1e-6,
                 "dout": torch.randn((r, c), device=device, dtype=dt)}
+    if op == "llama3_decoder_layer":  # llama3_decoder_layer/__init__.py:64-135
+        B, T, hidden = dims["B"], dims["T"], dims["hidden"]
+        hd, q_out, kv_out, inter = dims["head_dim"], dims["q_out"], dims["kv_out"], dims["intermediate"]
+        if q_out % hd or kv_out % hd or (q_out // hd) % (kv_out // hd) or q_out != hidden:
+            raise ValueError("inconsistent decoder-layer dimensions")
+        torch.manual_seed(T * 100003 + hidden * 1009 + hd)
+
+        def weight(o_f, i_f):  # fan-in scaling
+            return (torch.randn((o_f, i_f), device=device, dtype=torch.float32) * i_f ** -0.5).to(dt)
+
+        def gain(width):
+            return (1.0 + 0.1 * torch.randn((width,), device=device, dtype=torch.float32)).to(dt)
+
+        positions = torch.arange(T, device=device, dtype=torch.float32)[:, None]
+        inv_freq = 500000.0 ** (-torch.arange(0, hd, 2, device=device, dtype=torch.float32) / hd)
+        angles = torch.cat((positions * inv_freq[None, :],) * 2, dim=-1)
+        # dict order = order of the random draws in the reference
+        return {
+            "x": torch.randn((B, T, hidden), device=device, dtype=dt) * 0.5,
+            "input_norm_weight": gain(hidden),
+            "q_weight": weight(q_out, hidden),
+            "k_weight": weight(kv_out, hidden),
+            "v_weight": weight(kv_out, hidden),
+            "o_weight": weight(hidden, q_out),
+            "post_norm_weight": gain(hidden),
+            "gate_weight": weight(inter, hidden),
+            "up_weight": weight(inter, hidden),
+            "down_weight": weight(hidden, inter),
+            "cos": angles.cos().to(dt),
+            "sin": angles.sin().to(dt),
+            "eps": 1e-5,
+            "dout": torch.randn((B, T, hidden), device=device, dtype=dt) * 0.5 * (B * T) ** -0.5,
+        }
     if op == "rope":  # rope/__init__.py:30-62, theta = 500000 (models.py:259-261)
         B, H, T, D = dims["B"], dims["n_heads"], dims["T"], dims["head_dim"]
         if D % 2:

@@ -78,6 +78,16 @@ CASES = {
         ({"B": 1, "n_heads": 4, "T": 16, "head_dim": 64}, "bfloat16"),
         ({"B": 1, "n_heads": 2, "T": 129, "head_dim": 128}, "bfloat16"),
     ],
+    "llama3_decoder_layer": [  # the declaration's own correctness workloads
+        ({"B": 1, "T": 32, "hidden": 128, "head_dim": 32, "q_out": 128, "kv_out": 32,
+          "intermediate": 352}, "float32"),
+        ({"B": 2, "T": 17, "hidden": 64, "head_dim": 16, "q_out": 64, "kv_out": 16,
+          "intermediate": 176}, "float32"),
+        ({"B": 1, "T": 32, "hidden": 128, "head_dim": 32, "q_out": 128, "kv_out": 32,
+          "intermediate": 352}, "bfloat16"),
+        ({"B": 2, "T": 17, "hidden": 64, "head_dim": 16, "q_out": 64, "kv_out": 16,
+          "intermediate": 176}, "bfloat16"),
+    ],
     "causal_attention": [
         ({"B": 1, "H": 1, "S": 160, "D": 128}, "bfloat16"),
         ({"B": 2, "H": 1, "S": 64, "D": 128}, "float16"),
