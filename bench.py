@@ -113,6 +113,11 @@ class Workload:
     def step_work(self):
         return self.fwd_work + self.bwd_work
 
+    def cpu_sample(self):
+        """(work done by one cpu_step, description): the bounded sample of the
+        workload that the host-CPU legs time."""
+        return self.step_work, f"full {self.name} step"
+
 
 def _load_pair(op):
     path = os.path.join(ROOT, "evograd_b200", "pairs", f"{op}.py")
@@ -391,15 +396,97 @@ class AttentionWL(Workload):
         sl = {k: v[:1, :heads] for k, v in s.items()}
         return ao.oracle("causal_attention", sl, forward=ao.causal_attention_forward_sdpa)
 
+    def cpu_sample(self):
+        return (self.step_work * 2 / (self.B * self.H),
+                f"2 of {self.B * self.H} (batch, head) units per step, rate scaled per unit")
+
     def config(self):
         return {"workload": self.name, "shape": [self.B, self.H, self.S, self.D],
                 "scale": 1 / math.sqrt(self.D), "saved": "o, lse f32"}
 
 
+class DecoderLayerWL(Workload):
+    """One Llama-3-8B decoder layer at 4096 tokens (the largest timed case of
+    ops/level3/llama3_decoder_layer/__init__.py:35-45): this package's kernels
+    plus library GEMMs. Work = GEMM + attention FLOPs (causal-halved), backward
+    2x the GEMMs and 2.5x the attention."""
+    name, bound, pair = "llama3_decoder_layer_bf16_1x4096", "tensor", "llama3_decoder_layer"
+    kernels_per_step = 8 + 17  # own launches: 8 forward, 17 backward (GEMMs not counted)
+    B, T, hidden, hd, q_out, kv_out, inter = 1, 4096, 4096, 128, 4096, 1024, 14336
+
+    def __init__(self, device):
+        super().__init__(device)
+        bt = self.B * self.T
+        gemm = 2 * bt * (self.hidden * (self.q_out + 2 * self.kv_out) + self.q_out * self.hidden
+                         + 3 * self.hidden * self.inter)
+        attn = 4 * self.B * (self.q_out // self.hd) * self.T * self.T * self.hd * 0.5
+        self.fwd_work, self.bwd_work = gemm + attn, 2 * gemm + 2.5 * attn
+
+    def dims(self):
+        return dict(B=self.B, T=self.T, hidden=self.hidden, head_dim=self.hd, q_out=self.q_out,
+                    kv_out=self.kv_out, intermediate=self.inter)
+
+    def make(self, device, salt=0):
+        g = _gen(device, self.T * 100003 + self.hidden * 1009 + self.hd + salt)
+
+        def weight(o_f, i_f):
+            return _randn((o_f, i_f), BF16, device, g, i_f ** -0.5)
+
+        pos = torch.arange(self.T, device=device, dtype=torch.float32)[:, None]
+        inv = 500000.0 ** (-torch.arange(0, self.hd, 2, device=device, dtype=torch.float32) / self.hd)
+        ang = torch.cat((pos * inv[None, :],) * 2, dim=-1)
+        return {
+            "x": _randn((self.B, self.T, self.hidden), BF16, device, g, 0.5),
+            "input_norm_weight": _randn((self.hidden,), BF16, device, g, 0.1, 1.0),
+            "q_weight": weight(self.q_out, self.hidden), "k_weight": weight(self.kv_out, self.hidden),
+            "v_weight": weight(self.kv_out, self.hidden), "o_weight": weight(self.hidden, self.q_out),
+            "post_norm_weight": _randn((self.hidden,), BF16, device, g, 0.1, 1.0),
+            "gate_weight": weight(self.inter, self.hidden), "up_weight": weight(self.inter, self.hidden),
+            "down_weight": weight(self.hidden, self.inter),
+            "cos": ang.cos().to(BF16), "sin": ang.sin().to(BF16), "eps": 1e-5,
+            "dout": _randn((self.B, self.T, self.hidden), BF16, device, g,
+                           0.5 * (self.B * self.T) ** -0.5),
+        }
+
+    _ARGS = ("x", "input_norm_weight", "q_weight", "k_weight", "v_weight", "o_weight",
+             "post_norm_weight", "gate_weight", "up_weight", "down_weight", "cos", "sin")
+
+    def inputs_of(self, s):
+        return [s[k] for k in self._ARGS] + [s["dout"]]
+
+    def forward(self, s):
+        out, saved = self.fwd(*[s[k] for k in self._ARGS], s["eps"])
+        return [out], saved
+
+    def backward(self, s, saved):
+        return list(self.bwd(s["dout"], saved, s["eps"]))
+
+    def cpu_step(self, s, tokens=512):
+        from oracle import autograd_oracle as ao
+        sl = dict(s)
+        for k in ("x", "dout"):
+            sl[k] = s[k][:, :tokens]
+        for k in ("cos", "sin"):
+            sl[k] = s[k][:tokens]
+        return ao.oracle("llama3_decoder_layer", sl)
+
+    def cpu_sample(self, tokens=512):
+        bt = self.B * tokens
+        gemm = 2 * bt * (self.hidden * (self.q_out + 2 * self.kv_out) + self.q_out * self.hidden
+                         + 3 * self.hidden * self.inter)
+        attn = 4 * self.B * (self.q_out // self.hd) * tokens * tokens * self.hd * 0.5
+        return 3 * gemm + 3.5 * attn, f"the first {tokens} of {self.T} tokens per step"
+
+    def config(self):
+        return {"workload": self.name, **self.dims(),
+                "saved": "rstd x2, rotated q/k, v, o, lse f32, residual stream, gate, up",
+                "gemms": "cuBLAS via torch.mm/addmm"}
+
+
 WORKLOADS = {"softmax": SoftmaxWL, "layernorm": LayerNormWL, "rmsnorm": RMSNormWL,
              "swiglu": SwiGLUWL, "rope": RopeWL, "attention": AttentionWL,
              "geglu": GeGLUWL, "fused_add_rms_norm": FusedAddRMSNormWL,
-             "softmax_vocab": SoftmaxVocabWL}
+             "softmax_vocab": SoftmaxVocabWL, "decoder_layer": DecoderLayerWL}
 
 
 # --------------------------------------------------------------------------
@@ -675,11 +762,9 @@ def run_ours(args):
 
     if rank == 0 and world == 1 and not args.no_cpu:
         sec, reps, cores = measure_cpu(wl)
-        cpu_val = (wl.step_work / sec / 1e9) if wl.bound == "hbm" else wl.step_work / sec / 1e12
-        sample = f"full {wl.name} step x{reps} (median)"
-        if args.workload == "attention":
-            cpu_val = cpu_val * 2 / (wl.B * wl.H)
-            sample = f"2 of {wl.B * wl.H} (batch, head) units x{reps}, rate scaled per unit"
+        work, sample = wl.cpu_sample()
+        cpu_val = (work / sec / 1e9) if wl.bound == "hbm" else work / sec / 1e12
+        sample = f"{sample} x{reps} (median)"
         line["cpu_baseline"] = {"value": round(cpu_val, 3), "unit": unit, "cores": cores,
                                 "kind": "port", "sample": sample, "s_per_step": round(sec, 4)}
 
@@ -722,11 +807,7 @@ def run_reference(args):
     sec = (time.perf_counter() - t0) / steps
     hbm = wl.bound == "hbm"
     unit = "GB/s" if hbm else "TFLOP/s"
-    work = wl.step_work
-    sample = f"full {wl.name} step"
-    if args.workload == "attention":
-        work = work * 2 / (wl.B * wl.H)
-        sample = f"2 of {wl.B * wl.H} (batch, head) units per step"
+    work, sample = wl.cpu_sample()
     value = work / sec / (1e9 if hbm else 1e12)
     cores = torch.get_num_threads()
     line = {
