@@ -781,7 +781,14 @@ def run_ours(args):
 # captures summarised under profiles/ (None until a capture exists).
 TRAFFIC_NCU = {
     # norm_bwd_ring_kernel + colreduce_kernel, profiles/layernorm_bf16_16384x4096.md
-    "layernorm": 376.5e6 + 9.7e6,
+    "layernorm": 375.9e6 + 9.7e6,
+    # captured at a quarter / an eighth of the rows and scaled by the row count:
+    # profiles/rmsnorm_and_fused_add_bf16_8192x4096.md
+    "rmsnorm": 4 * (134.3e6 + 37.4e6) + 4.9e6,
+    "fused_add_rms_norm": 4 * (201.4e6 + 44.5e6) + 4.9e6,
+    # profiles/softmax_bf16_512x128256.md, profiles/geglu_bf16_4096x14336.md
+    "softmax_vocab": 8 * 360.7e6,
+    "geglu": 8 * 541.9e6,
 }
 
 
@@ -839,7 +846,16 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--attention-shape", default=None, metavar="B,H,S",
                     help="smaller causal-attention case (profiling captures only; head_dim stays 128)")
+    ap.add_argument("--rows", type=int, default=None,
+                    help="fewer rows for the chosen row-wise workload (profiling captures only)")
     args = ap.parse_args()
+    if args.rows:
+        cls = WORKLOADS[args.workload]
+        if not hasattr(cls, "rows"):
+            ap.error(f"--rows does not apply to workload {args.workload}")
+        cls.rows = args.rows
+        if isinstance(getattr(cls, "name", None), str) and cls.name:
+            cls.name = f"{cls.name}_rows{args.rows}"
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.attention_shape:
