@@ -118,6 +118,11 @@ class Workload:
         workload that the host-CPU legs time."""
         return self.step_work, f"full {self.name} step"
 
+    def pipeline_spec(self):
+        """(operator, row inputs, parameters, row outputs, parameter gradients) for
+        evograd_b200.host_pipeline, or None when the workload has no row pipeline."""
+        return None
+
 
 def _load_pair(op):
     path = os.path.join(ROOT, "evograd_b200", "pairs", f"{op}.py")
@@ -154,6 +159,9 @@ class SoftmaxWL(Workload):
     def cpu_step(self, s):
         from oracle import autograd_oracle as ao
         return ao.oracle("softmax", s)
+
+    def pipeline_spec(self):
+        return "softmax", ["x", "dy"], [], ["y", "dx"], []
 
     def config(self):
         return {"workload": self.name, "shape": [self.rows, self.cols], "saved": "y"}
@@ -228,6 +236,11 @@ class NormWL(Workload):
         if self.sharded is not None:
             self.sharded.finish()
 
+    def pipeline_spec(self):
+        if self.kind == "layernorm":
+            return "layernorm", ["x", "dy"], ["weight", "bias"], ["y", "dx"], ["dweight", "dbias"]
+        return "rmsnorm", ["x", "dy"], ["weight"], ["y", "dx"], ["dweight"]
+
     def cpu_step(self, s):
         from oracle import autograd_oracle as ao
         return ao.oracle(self.kind, s)
@@ -271,6 +284,9 @@ class SwiGLUWL(Workload):
     def cpu_step(self, s):
         from oracle import autograd_oracle as ao
         return ao.oracle("swiglu", s)
+
+    def pipeline_spec(self):
+        return self.pair, ["a", "b", "dc"], [], ["c", "da", "db"], []
 
     def config(self):
         return {"workload": self.name, "shape": [self.rows, self.cols], "saved": "a,b by reference"}
@@ -316,6 +332,9 @@ class FusedAddRMSNormWL(Workload):
     def cpu_step(self, s):
         from oracle import autograd_oracle as ao
         return ao.oracle("fused_add_rms_norm", s)
+
+    def pipeline_spec(self):
+        return "fused_add_rms_norm", ["x", "r", "dout"], ["weight"], ["out", "dx"], ["dweight"]
 
     def config(self):
         return {"workload": self.name, "shape": [self.rows, self.hidden], "eps": self.eps,
@@ -595,12 +614,45 @@ def measure_graphs(wl, steps, warmup, world):
 
 
 def measure_e2e(wl, steps, warmup, world):
-    """e2e leg: pinned host inputs -> H2D -> fwd -> bwd -> D2H of every result."""
+    """e2e leg: pinned host inputs -> H2D -> fwd -> bwd -> D2H of every result.
+    Row-wise workloads go through evograd_b200.host_pipeline (rows cut into
+    chunks; copy-in, kernels and copy-out of different chunks overlap on three
+    streams); the others copy, compute and copy back in sequence."""
     from evograd_b200.timing import time_steps
 
     device = torch.device("cuda", torch.cuda.current_device())
     dev_set = wl.make(device)
     host = {k: (v.cpu().pin_memory() if torch.is_tensor(v) else v) for k, v in dev_set.items()}
+    spec = wl.pipeline_spec() if world == 1 else None
+    if spec is not None:
+        from evograd_b200.host_pipeline import pipeline_for
+
+        op, row_names, param_names, out_names, grad_names = spec
+        n_chunks = int(os.environ.get("EVG_E2E_CHUNKS", "8"))
+        pipe, finish = pipeline_for(op, eps=dev_set.get("eps", 1e-5), chunks=n_chunks)
+        host_rows = {n: host[n] for n in row_names}
+        params = {n: dev_set[n] for n in param_names}
+        like = host[row_names[0]]
+        host_out = {n: torch.empty_like(like).pin_memory() for n in out_names}
+        host_grads = {n: torch.empty_like(host[param_names[0]]).pin_memory() for n in grad_names}
+        dtype = like.dtype
+        h2d = sum(t.numel() * t.element_size() for t in host_rows.values()) + \
+            sum(host[n].numel() * host[n].element_size() for n in param_names)
+        d2h = sum(t.numel() * t.element_size() for t in (*host_out.values(), *host_grads.values()))
+        del dev_set
+        live = [None]
+
+        def step(_i):
+            for n in param_names:
+                params[n].copy_(host[n], non_blocking=True)
+            live[0] = pipe.run(host_rows, params, host_out, host_grads,
+                               (lambda total: finish(total, dtype)) if finish else None)
+
+        ms = time_steps(step, steps, warmup, barrier=_barrier_fn(world))
+        del live, params, host_rows, host_out
+        torch.cuda.empty_cache()
+        return ms, h2d, d2h, (f"host_pipeline: {n_chunks} row chunks, copy-in / kernels / copy-out "
+                              "overlapped on three streams")
     outs = wl.step(dev_set)
     host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
     h2d = sum(v.numel() * v.element_size() for v in host.values() if torch.is_tensor(v))
@@ -621,7 +673,7 @@ def measure_e2e(wl, steps, warmup, world):
     ms = _max_over_ranks(ms, world)
     del dev_set, host, host_out
     torch.cuda.empty_cache()
-    return ms, h2d, d2h
+    return ms, h2d, d2h, "sequential: copy in, kernels, copy out"
 
 
 def measure_cpu(wl, budget_s=12.0, max_reps=10, threads=None):
@@ -729,12 +781,13 @@ def run_ours(args):
     e2e = None
     if not args.no_e2e:
         e2e_steps = max(3, min(args.steps, 10))
-        e2e_ms, h2d, d2h = measure_e2e(wl, e2e_steps, max(3, min(args.warmup, 3)), world)
+        e2e_ms, h2d, d2h, e2e_mode = measure_e2e(wl, e2e_steps, max(3, min(args.warmup, 3)), world)
         e2e_step_ms = e2e_ms / e2e_steps
         e2e_value = (_rate(wl.step_work, e2e_step_ms) if wl.bound == "hbm"
                      else wl.step_work / (e2e_step_ms * 1e-3) / 1e12) * world
         e2e = {"value": round(e2e_value, 2), "unit": unit, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_step_ms, 4), "steps": e2e_steps}
+               "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_step_ms, 4), "steps": e2e_steps,
+               "path": e2e_mode}
 
     line = {
         "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world,
