@@ -575,40 +575,43 @@ def _make_sets(wl):
 
 
 def measure_graphs(wl, steps, warmup, world):
-    """Per-operator leg with launch overhead removed: one CUDA graph per input
-    set for the full step, the forward alone and the backward alone; K replays
-    of each are timed. Returns (step_ms, fwd_ms, bwd_ms, n_sets) per launch."""
+    """Device leg with the host launch path removed: the K timed steps (cycling
+    through the rotating input sets) are captured into ONE CUDA graph, for the
+    full step, the forward alone and the backward alone, and one replay of each
+    is timed between a CUDA event pair. W eager steps plus one untimed replay
+    come first. (One graph per step would put a graph-launch gap of several
+    microseconds between steps, which is a third of the float32 softmax step.)
+    Returns (step_ms, fwd_ms, bwd_ms, n_sets) per step."""
     from evograd_b200.timing import time_steps
 
     sets = _make_sets(wl)
+    n = len(sets)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):  # warm-up outside capture (lazy init, attributes)
-        for s_ in sets[:1]:
-            wl.step(s_)
+        for i in range(max(warmup, 1)):
+            wl.step(sets[i % n])
+        saved = [wl.forward(s_)[1] for s_ in sets]  # state the backward-only graph consumes
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
-    g_step, g_fwd, g_bwd, keep = [], [], [], []
-    for s_ in sets:
+
+    def capture(body):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            keep.append(wl.step(s_))
-        g_step.append(g)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            outs, saved = wl.forward(s_)
-        keep.append(outs)
-        g_fwd.append(g)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            keep.append(wl.backward(s_, saved))
-        g_bwd.append(g)
-    n = len(sets)
+            for i in range(steps):
+                body(i)  # results are dropped: the graph's pool reuses their memory
+        return g
+
+    bodies = (lambda i: wl.step(sets[i % n]),
+              lambda i: wl.forward(sets[i % n]),
+              lambda i: wl.backward(sets[i % n], saved[i % n]))
     res = []
-    for graphs in (g_step, g_fwd, g_bwd):
-        ms = time_steps(lambda i: graphs[i % n].replay(), steps, warmup, barrier=_barrier_fn(world))
+    for body in bodies:
+        g = capture(body)
+        ms = time_steps(lambda _i: g.replay(), 1, 1, barrier=_barrier_fn(world))
         res.append(_max_over_ranks(ms, world) / steps)
-    del g_step, g_fwd, g_bwd, keep, sets
+        del g
+    del saved, sets
     torch.cuda.empty_cache()
     return res[0], res[1], res[2], n
 
@@ -738,14 +741,14 @@ def run_ours(args):
     peaks, peak_source = measured_peaks()
     wl = WORKLOADS[args.workload](device)
 
-    # Leg 1 (value): K steps between one event pair. Each step is one CUDA-graph
-    # replay of the public pair calls (forward, backward, and at N > 1 the NCCL
+    # Leg 1 (value): K steps between one event pair, captured as one CUDA graph of
+    # the public pair calls (forward, backward, and at N > 1 the NCCL
     # all-reduce), so the host's launch path is not what is being timed.
-    # Leg 2 (roofline): K replays of the backward alone (its row kernel and the
-    # column reduce) between one event pair; if capture is refused, the same K
+    # Leg 2 (roofline): K backward launches alone (row kernel and column reduce),
+    # again one graph between one event pair; if capture is refused, the same K
     # steps launched eagerly with an event pair around forward and backward.
-    launch_mode = "cuda graph replay (one graph per step)"
-    roofline_loop = "K graph replays of the backward alone between one CUDA event pair"
+    launch_mode = "cuda graph replay (the K steps captured in one graph)"
+    roofline_loop = "one replay of a graph holding K backward launches, between one CUDA event pair"
     with ClockSampler(local) as clocks:
         try:
             step_ms, _f, bwd_ms, n_sets = measure_graphs(wl, args.steps, args.warmup, world)
