@@ -317,3 +317,16 @@ def test_geglu_forward_matches_reference_rounding():
     # identical except where the float32 gelu sits within an ulp of a bf16 tie
     assert (c == ref).float().mean().item() >= 0.995
     assert torch.allclose(c.float(), ref.float(), atol=1e-6, rtol=2 ** -6)
+
+
+def test_l2cache_stand_in_clears_without_triton():
+    """Same interface as evograd.bench.fair.L2Cache; the buffer is overwritten."""
+    from evograd_b200.bench_support import L2Cache
+
+    cache = L2Cache(min_bytes=1 << 20)
+    before = cache._cache[:4096].clone()
+    cache.clear()
+    cache.clear()
+    torch.cuda.synchronize()
+    assert cache._cache.numel() >= 2 * torch.cuda.get_device_properties(0).L2_cache_size
+    assert cache._cache[:4096].shape == before.shape
