@@ -424,6 +424,48 @@ class AttentionWL(Workload):
                 "scale": 1 / math.sqrt(self.D), "saved": "o, lse f32"}
 
 
+class EvoAttentionWL(Workload):
+    """AlphaFold-3 triangle attention (S == N == 256, 4 heads of 32): the largest
+    family of the reference's evoattention grid
+    (ops/level1/evoattention/__init__.py:44-56). Runs on the CUDA-core kernels."""
+    name, bound, kernels_per_step, pair = "evoattention_bf16_1x256x4x256x32", "tensor", 4, \
+        "evoattention"
+    B, S, H, N, D = 1, 256, 4, 256, 32
+
+    def __init__(self, device):
+        super().__init__(device)
+        fwd = 4 * self.B * self.S * self.H * self.N * self.N * self.D
+        self.fwd_work, self.bwd_work = fwd, 2.5 * fwd
+
+    def make(self, device, salt=0):
+        g = _gen(device, ((((self.B * 131 + self.S) * 131 + self.H) * 131 + self.N) * 131) + self.D + salt)
+        shape = (self.B, self.S, self.N, self.H, self.D)
+        s = {k: _randn(shape, BF16, device, g, 0.5) for k in ("q", "k", "v", "do")}
+        keep = torch.rand((self.B, self.S, 1, 1, self.N), device=device, generator=g) > 0.5
+        keep[..., 0] = True
+        s["res_mask"] = torch.where(keep, 0.0, -1e9).to(torch.float32)
+        s["pair_bias"] = _randn((self.B, 1, self.H, self.N, self.N), F32, device, g, 0.5)
+        return s
+
+    def inputs_of(self, s):
+        return [s[k] for k in ("q", "k", "v", "res_mask", "pair_bias", "do")]
+
+    def forward(self, s):
+        o, saved = self.fwd(s["q"], s["k"], s["v"], s["res_mask"], s["pair_bias"])
+        return [o], saved
+
+    def backward(self, s, saved):
+        return list(self.bwd(s["do"], saved))
+
+    def cpu_step(self, s):
+        from oracle import autograd_oracle as ao
+        return ao.oracle("evoattention", s)
+
+    def config(self):
+        return {"workload": self.name, "shape": [self.B, self.S, self.N, self.H, self.D],
+                "saved": "o, lse f32", "kernels": "CUDA cores (one warp per row), untuned"}
+
+
 class DecoderLayerWL(Workload):
     """One Llama-3-8B decoder layer at 4096 tokens (the largest timed case of
     ops/level3/llama3_decoder_layer/__init__.py:35-45): this package's kernels
@@ -505,7 +547,8 @@ class DecoderLayerWL(Workload):
 WORKLOADS = {"softmax": SoftmaxWL, "layernorm": LayerNormWL, "rmsnorm": RMSNormWL,
              "swiglu": SwiGLUWL, "rope": RopeWL, "attention": AttentionWL,
              "geglu": GeGLUWL, "fused_add_rms_norm": FusedAddRMSNormWL,
-             "softmax_vocab": SoftmaxVocabWL, "decoder_layer": DecoderLayerWL}
+             "softmax_vocab": SoftmaxVocabWL, "decoder_layer": DecoderLayerWL,
+             "evoattention": EvoAttentionWL}
 
 
 # --------------------------------------------------------------------------

@@ -112,6 +112,18 @@ SIGNATURES = {
         [c_void_p] * 10 + [c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int,
                            c_void_p],
     ),
+    "evg_evoattention_fwd": (
+        c_int,
+        [c_void_p] * 7 + [c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_void_p],
+    ),
+    "evg_evoattention_bwd_workspace_bytes": (
+        c_int64, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]
+    ),
+    "evg_evoattention_bwd": (
+        c_int,
+        [c_void_p] * 13 + [c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int,
+                           c_void_p],
+    ),
     "evg_selftest_bounded_wait": (c_int, [c_int64, c_void_p, c_void_p]),
     "evg_swiglu_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "evg_swiglu_bwd": (

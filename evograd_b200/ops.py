@@ -498,6 +498,68 @@ def causal_gqa_attention_bwd(do, q, k, v, o, lse, scale: float | None = None):
     return dq, dk, dv
 
 
+# ------------------------------------------------------------- evoattention
+def _check_evo(q, k, v, res_mask, pair_bias):
+    if q.ndim != 5:
+        raise ValueError(f"evoattention expects [B, S, N, H, D], got {tuple(q.shape)}")
+    _same("q", q, "k", k)
+    _same("q", q, "v", v)
+    B, S, N, H, D = q.shape
+    if res_mask.dtype != torch.float32 or res_mask.numel() != B * S * N:
+        raise ValueError(f"res_mask must be float32 with B*S*N entries ([B, S, 1, 1, N]), got "
+                         f"{res_mask.dtype} {tuple(res_mask.shape)}")
+    if pair_bias.dtype != torch.float32 or pair_bias.numel() != B * H * N * N:
+        raise ValueError(f"pair_bias must be float32 with B*H*N*N entries ([B, 1, H, N, N]), got "
+                         f"{pair_bias.dtype} {tuple(pair_bias.shape)}")
+    return B, S, N, H, D
+
+
+def evoattention_fwd(q, k, v, res_mask, pair_bias, scale: float | None = None):
+    """EvoformerAttention forward (ops/level1/evoattention/forward_ref.py:22-49).
+    Returns ``(o, lse)``; ``lse`` is float32 ``[B, S, H, N]``."""
+    dev = _require_cuda(q, k, v, res_mask, pair_bias)
+    B, S, N, H, D = _check_evo(q, k, v, res_mask, pair_bias)
+    if scale is None:
+        scale = D ** -0.5
+    q2, k2, v2 = q.contiguous(), k.contiguous(), v.contiguous()
+    o = torch.empty_like(q2)
+    lse = torch.empty(B, S, H, N, device=dev, dtype=torch.float32)
+    if q2.numel() == 0:
+        return o, lse
+    with torch.cuda.device(dev):
+        call("evg_evoattention_fwd", q2.data_ptr(), k2.data_ptr(), v2.data_ptr(),
+             res_mask.contiguous().data_ptr(), pair_bias.contiguous().data_ptr(), o.data_ptr(),
+             lse.data_ptr(), B, S, N, H, D, float(scale), _dtype_enum(q), _stream(dev))
+    return o, lse
+
+
+def evoattention_bwd(do, q, k, v, res_mask, pair_bias, o, lse, scale: float | None = None):
+    """Returns ``(dq, dk, dv, d_pair_bias)``; d_pair_bias is float32, shaped like pair_bias."""
+    dev = _require_cuda(do, q, k, v, res_mask, pair_bias, o, lse)
+    B, S, N, H, D = _check_evo(q, k, v, res_mask, pair_bias)
+    _same("do", do, "q", q)
+    _same("o", o, "q", q)
+    if lse.dtype != torch.float32 or lse.numel() != B * S * H * N:
+        raise ValueError("lse must be float32 [B, S, H, N]")
+    if scale is None:
+        scale = D ** -0.5
+    do2, q2, k2, v2, o2 = (t.contiguous() for t in (do, q, k, v, o))
+    dq, dk, dv = torch.empty_like(q2), torch.empty_like(k2), torch.empty_like(v2)
+    dbias = torch.empty(pair_bias.shape, device=dev, dtype=torch.float32)
+    if q2.numel() == 0:
+        return dq, dk, dv, dbias.zero_()
+    en = _dtype_enum(q)
+    with torch.cuda.device(dev):
+        ws_bytes = lib.evg_evoattention_bwd_workspace_bytes(B, S, N, H, D, en)
+        ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
+        call("evg_evoattention_bwd", do2.data_ptr(), q2.data_ptr(), k2.data_ptr(), v2.data_ptr(),
+             res_mask.contiguous().data_ptr(), pair_bias.contiguous().data_ptr(), o2.data_ptr(),
+             lse.contiguous().data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+             dbias.data_ptr(), ws.data_ptr(), ws_bytes, B, S, N, H, D, float(scale), en,
+             _stream(dev))
+    return dq, dk, dv, dbias
+
+
 def device_status(reset: bool = True) -> None:
     """Synchronise and raise :class:`EvgError` (EVG_ETIMEOUT) if a bounded wait inside
     an attention kernel gave up since the last reset."""

@@ -304,6 +304,33 @@ int evg_causal_gqa_attention_bwd(const void* dout, const void* q, const void* k,
                                  int64_t Hkv, int64_t S, int64_t D, float scale,
                                  int dtype, void* stream);
 
+/* ------------------------------------------------------------ evoattention
+ * AlphaFold-3 style EvoformerAttention over [B, S, N, H, D] tensors (S = MSA
+ * rows, N = residues): o = softmax(scale*q k^T + pair_bias + res_mask) v along
+ * the residue axis, ops/level1/evoattention/forward_ref.py:22-49. res_mask is
+ * float32 [B,S,N] (the reference's [B,S,1,1,N], additive per key), pair_bias
+ * float32 [B,H,N,N] (the reference's [B,1,H,N,N], shared by all MSA rows).
+ * lse is float32 [B,S,H,N]. Any of float32/float16/bfloat16, D <= 256,
+ * N <= 1024; plain CUDA-core kernels (residue counts are a few hundred).
+ * replaces: the evoattention candidate pair derived from
+ * ops/level1/evoattention/__init__.py:80-137.
+ */
+int evg_evoattention_fwd(const void* q, const void* k, const void* v,
+                         const float* res_mask, const float* pair_bias, void* o,
+                         float* lse, int64_t B, int64_t S, int64_t N, int64_t H,
+                         int64_t D, float scale, int dtype, void* stream);
+int64_t evg_evoattention_bwd_workspace_bytes(int64_t B, int64_t S, int64_t N,
+                                             int64_t H, int64_t D, int dtype);
+/* dq, dk, dv in the input layout and dtype; d_pair_bias float32 [B,H,N,N] =
+ * sum over the S axis of dS, accumulated in a fixed order without atomics. */
+int evg_evoattention_bwd(const void* dout, const void* q, const void* k,
+                         const void* v, const float* res_mask,
+                         const float* pair_bias, const void* o, const float* lse,
+                         void* dq, void* dk, void* dv, float* d_pair_bias,
+                         void* workspace, int64_t workspace_bytes, int64_t B,
+                         int64_t S, int64_t N, int64_t H, int64_t D, float scale,
+                         int dtype, void* stream);
+
 /*
  * Synchronises the current device (the one exception to "nothing synchronises")
  * and reports the sticky device-side status of the attention kernels: every

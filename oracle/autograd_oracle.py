@@ -108,6 +108,21 @@ def causal_attention_forward_sdpa(q, k, v):
     return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
 
 
+def evoattention_forward(q, k, v, res_mask, pair_bias):
+    """ops/level1/evoattention/forward_ref.py:22-49. q, k, v are
+    [B, N_seq, N_res, Head, Dim]; res_mask [B, N_seq, 1, 1, N_res] additive;
+    pair_bias [B, 1, Head, N_res, N_res]. q is scaled by Dim**-0.5 in the input
+    dtype, the scores get bias and mask, the softmax runs in float32 over the key
+    residue axis and is cast to the input dtype before the product with v."""
+    dtype = q.dtype
+    scale = q.shape[-1] ** -0.5
+    q_t, k_t, v_t = (t.transpose(-2, -3) for t in (q, k, v))
+    scores = torch.matmul(q_t * scale, k_t.transpose(-1, -2))
+    scores = scores + pair_bias + res_mask
+    probs = torch.softmax(scores.float(), dim=-1).to(dtype)
+    return torch.matmul(probs, v_t).transpose(-2, -3).contiguous()
+
+
 def causal_gqa_attention_forward(q, k, v):
     """Grouped-query causal attention as the decoder block spells it
     (ops/level3/llama3_decoder_layer/forward_ref.py:100-107): each k/v head is
@@ -189,6 +204,10 @@ class OpSpec:
     # against the float32-promoted oracle (the trusted forward rounds inside the
     # reduction's inputs); they keep the declared tolerance in strict mode.
     strict_exempt: tuple = ()
+    grad_overrides: dict = field(default_factory=dict)  # input name -> gradient name (Active(grad=...))
+
+    def grad_name(self, arg: str) -> str:  # activity.py:43-45
+        return self.grad_overrides.get(arg, "d" + arg)
 
     def strict_tolerance_for(self, dims: dict, dtype: str, result: str | None = None):
         if dtype != "float32" and result in self.strict_exempt:
@@ -200,7 +219,7 @@ class OpSpec:
         return "d" + self.output
 
     def grad_names(self) -> tuple:
-        return tuple("d" + n for n, active in self.args if active)
+        return tuple(self.grad_name(n) for n, active in self.args if active)
 
     def tolerance_for(self, dims: dict, dtype: str, result: str | None = None):
         """(atol, rtol) as OpDecl.tolerance_for (activity.py:517-528) with the
@@ -262,6 +281,15 @@ OPS = {
         dims=("B", "T", "hidden", "head_dim", "q_out", "kv_out", "intermediate"),
         tolerances={"float32": (1e-4, 1e-4), "bfloat16": (5e-2, 2e-2)},
         tolerance_hook=_decoder_layer_tolerance,
+    ),
+    "evoattention": OpSpec(
+        "evoattention", evoattention_forward,
+        (("q", True), ("k", True), ("v", True), ("res_mask", False), ("pair_bias", True)), "o",
+        dims=("B", "S", "H", "N", "D"),
+        tolerances={"float16": (2e-2, 2e-2), "bfloat16": (4e-2, 4e-2)},  # evoattention/__init__.py
+        tolerance_hook=lambda dims, dtype, result, atol, rtol:
+            (atol * 2.0, rtol) if result == "d_pair_bias" else (atol, rtol),
+        grad_overrides={"pair_bias": "d_pair_bias"},
     ),
     "rope": OpSpec("rope", rope_forward, (("x", True), ("cos", False), ("sin", False)), "y",
                    dims=("B", "n_heads", "T", "head_dim")),
@@ -358,6 +386,17 @@ def make_inputs(op: str, dims: dict, dtype: str, device: str = "cpu") -> dict:
             "eps": 1e-5,
             "dout": torch.randn((B, T, hidden), device=device, dtype=dt) * 0.5 * (B * T) ** -0.5,
         }
+    if op == "evoattention":  # evoattention/__init__.py:7-32
+        b, sq, h, n, dim = dims["B"], dims["S"], dims["H"], dims["N"], dims["D"]
+        torch.manual_seed((((b * 131 + sq) * 131 + h) * 131 + n) * 131 + dim)
+        q, k, v, do = (torch.randn((b, sq, n, h, dim), device=device, dtype=dt) * 0.5
+                       for _ in range(4))
+        keep = torch.rand((b, sq, 1, 1, n), device=device) > 0.5
+        keep[..., 0] = True  # key 0 is always kept: no query row is fully masked
+        res_mask = torch.where(keep, torch.zeros((), device=device, dtype=torch.float32),
+                               torch.full((), -1e9, device=device, dtype=torch.float32))
+        pair_bias = torch.randn((b, 1, h, n, n), device=device, dtype=torch.float32) * 0.5
+        return {"q": q, "k": k, "v": v, "res_mask": res_mask, "pair_bias": pair_bias, "do": do}
     if op == "rope":  # rope/__init__.py:30-62, theta = 500000 (models.py:259-261)
         B, H, T, D = dims["B"], dims["n_heads"], dims["T"], dims["head_dim"]
         if D % 2:
@@ -406,11 +445,11 @@ def oracle(op: str | OpSpec, inputs: dict, dout=None, *, reference_dtype=None, f
     for name, active in spec.args:
         value = inputs[name]
         if active:
-            out_dtypes["d" + name] = value.dtype
+            out_dtypes[spec.grad_name(name)] = value.dtype
             if reference_dtype is not None:
                 value = value.to(reference_dtype)
             value = value.detach().clone().requires_grad_(True)
-            leaves.append(("d" + name, value))
+            leaves.append((spec.grad_name(name), value))
         elif reference_dtype is not None and torch.is_tensor(value) and value.is_floating_point():
             value = value.to(reference_dtype)
         positional.append(value)

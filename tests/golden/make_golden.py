@@ -88,6 +88,13 @@ CASES = {
         ({"B": 2, "T": 17, "hidden": 64, "head_dim": 16, "q_out": 64, "kv_out": 16,
           "intermediate": 176}, "bfloat16"),
     ],
+    "evoattention": [  # the declaration's own correctness workloads (the fourth with B=1, H=2)
+        ({"B": 1, "S": 1, "H": 4, "N": 23, "D": 8}, "float16"),
+        ({"B": 1, "S": 2, "H": 4, "N": 64, "D": 16}, "float16"),
+        ({"B": 1, "S": 1, "H": 8, "N": 80, "D": 32}, "bfloat16"),
+        ({"B": 1, "S": 2, "H": 2, "N": 128, "D": 64}, "bfloat16"),
+        ({"B": 1, "S": 1, "H": 4, "N": 48, "D": 128}, "float16"),
+    ],
     "causal_attention": [
         ({"B": 1, "H": 1, "S": 160, "D": 128}, "bfloat16"),
         ({"B": 2, "H": 1, "S": 64, "D": 128}, "float16"),

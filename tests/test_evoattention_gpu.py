@@ -1,0 +1,74 @@
+"""GPU parity of the EvoformerAttention pair (additive key mask, trainable pair
+bias reduced over the MSA axis) against reference-generated vectors and the CPU
+oracle, through the candidate module and the C ABI."""
+
+import pytest
+import torch
+
+from _util import assert_checks, assert_unchanged, load_pair, run_pair, snapshot, to_device
+from conftest import golden_cases, load_golden
+from oracle import autograd_oracle as ao
+
+pytestmark = pytest.mark.gpu
+OP = "evoattention"
+
+
+@pytest.mark.parametrize("name", golden_cases(OP))
+def test_matches_reference_golden_vectors(name):
+    meta, t = load_golden(name)
+    dims, dtype = meta["dims"], meta["dtype"]
+    spec = ao.OPS[OP]
+    inputs = to_device({n: t[n] for n in [a for a, _ in spec.args] + [spec.upstream]})
+    snap = snapshot(inputs)
+    o, grads, saved = run_pair(OP, inputs)
+    assert_unchanged(inputs, snap)
+    got = {spec.output: o, **dict(zip(spec.grad_names(), grads))}
+    assert got["d_pair_bias"].dtype == torch.float32
+    assert tuple(got["d_pair_bias"].shape) == tuple(t["pair_bias"].shape)
+    declared = [ao.check(n, g, t[n], *spec.tolerance_for(dims, dtype, n)) for n, g in got.items()]
+    assert_checks(declared, f"{name} declared")
+    # against the float32-promoted reference: o within the 16-bit gate, gradients 2e-2 max-abs
+    strict = [ao.check("o", got["o"], t["o__f32ref"], 1e-2, 1.6e-2)]
+    for n in ("dq", "dk", "dv", "d_pair_bias"):
+        strict.append(ao.check(n, got[n], t[n + "__f32ref"], 2e-2, 1.6e-2))
+    assert_checks(strict, f"{name} strict")
+
+
+CASES = [
+    (dict(B=1, S=1, H=4, N=23, D=8), "float16"), (dict(B=1, S=2, H=4, N=64, D=16), "float16"),
+    (dict(B=1, S=1, H=8, N=80, D=32), "bfloat16"), (dict(B=2, S=2, H=4, N=128, D=64), "bfloat16"),
+    (dict(B=1, S=1, H=4, N=48, D=128), "float16"), (dict(B=1, S=3, H=2, N=129, D=24), "bfloat16"),
+    (dict(B=1, S=5, H=1, N=33, D=40), "float16"), (dict(B=1, S=16, H=4, N=256, D=32), "bfloat16"),
+]
+
+
+@pytest.mark.parametrize("dims,dtype", CASES)
+def test_pair_passes_the_declared_gate(dims, dtype):
+    inputs = ao.make_inputs(OP, dims, dtype)
+    dev = to_device(inputs)
+    snap = snapshot(dev)
+    assert_checks(ao.verify_pair(OP, load_pair(OP), dev, dims, dtype), f"{OP} {dims} {dtype}")
+    assert_unchanged(dev, snap)
+
+
+def test_gradients_are_bit_reproducible():
+    dims, dtype = dict(B=1, S=4, H=2, N=100, D=32), "bfloat16"
+    inputs = to_device(ao.make_inputs(OP, dims, dtype))
+    _, g1, _ = run_pair(OP, inputs)
+    _, g2, _ = run_pair(OP, inputs)
+    for a, b in zip(g1, g2):
+        assert torch.equal(a, b)
+
+
+def test_argument_checks():
+    from evograd_b200 import ops
+
+    q = torch.zeros(1, 1, 8, 2, 16, device="cuda", dtype=torch.bfloat16)
+    mask = torch.zeros(1, 1, 1, 1, 8, device="cuda")
+    bias = torch.zeros(1, 1, 2, 8, 8, device="cuda")
+    with pytest.raises(ValueError):
+        ops.evoattention_fwd(q, q, q, mask[..., :4], bias)
+    with pytest.raises(ValueError):
+        ops.evoattention_fwd(q, q, q, mask, bias.to(torch.bfloat16))
+    with pytest.raises(ValueError):
+        ops.evoattention_fwd(q[0], q[0], q[0], mask, bias)
