@@ -9,18 +9,22 @@
 //   pair_bias      : [B, H, N, N] float32, shared by all S rows, trainable
 //   d_pair_bias    : sum over S of dS, float32
 //
-// The residue counts are small (128-384, head sizes 8-128), so these are the
-// plain one-warp-per-row kernels of attention_generic.cu with the bias and mask
-// added to the scores; nothing here is tuned for speed. Every sum has a fixed
-// order: d_pair_bias is accumulated over the MSA rows inside the warp that owns
-// a (batch, head, query) row, without atomics. Saved state: o and the float32
+// The residue counts are small (128-384, head sizes 8-128), so these are
+// one-warp-per-row kernels on the CUDA cores: a block first stages the K and V
+// (or Q and dO) rows of its (batch, MSA row, head) in shared memory, padded so
+// that 32 lanes reading 32 different rows hit 32 different banks, and every warp
+// then walks several rows against them. (If the rows do not fit shared memory
+// the same code reads them from global memory.) Every sum has a fixed order:
+// d_pair_bias is accumulated over the MSA rows inside the warp that owns a
+// (batch, head, query) row, without atomics. Saved state: o and the float32
 // log-sum-exp [B, S, H, N].
 #include "evg_common.cuh"
 
 namespace evg {
 namespace {
 
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;
+constexpr int kRowsPerWarp = 4;  // forward and dK/dV: rows a warp walks per block
 constexpr int kMaxDT = 8;     // head_dim <= 256
 constexpr int kMaxChunks = 32;  // residues <= 1024 (d_pair_bias row kept in registers)
 
@@ -34,11 +38,62 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+// dot(a, b_row): a is float32 in shared memory (broadcast reads), b_row a row of
+// T in shared or global memory. 16-bit rows are read two elements at a time
+// when D is even (rows then start on 4-byte boundaries in every layout used).
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* a_smem, const T* b_row, int D) {
   float s = 0.f;
+  if constexpr (sizeof(T) == 2) {
+    if ((D & 1) == 0) {
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(b_row);
+      float s1 = 0.f;
+      for (int d = 0; d < D / 2; ++d) {
+        const uint32_t u = w[d];
+        T lo, hi;
+        memcpy(&lo, &u, 2);
+        const uint32_t uh = u >> 16;
+        memcpy(&hi, &uh, 2);
+        s = fmaf(a_smem[2 * d], to_f32<T>(lo), s);
+        s1 = fmaf(a_smem[2 * d + 1], to_f32<T>(hi), s1);
+      }
+      return s + s1;
+    }
+  }
   for (int d = 0; d < D; ++d) s = fmaf(a_smem[d], to_f32<T>(b_row[d]), s);
   return s;
+}
+
+// Row pitch (elements) of a staged [N, D] matrix: D + 2 puts consecutive rows
+// an odd number of 32-bit words apart whenever D is a multiple of 4.
+__host__ __device__ __forceinline__ int staged_pitch(int D) { return D + 2; }
+
+// All threads of the block copy N rows of D elements (row stride src_rs) into
+// shared memory with pitch staged_pitch(D): 16-byte global loads and 4-byte
+// shared stores when a row is a whole number of 16-byte vectors (the padded
+// pitch keeps rows 4-byte aligned only), element by element otherwise.
+template <typename T>
+__device__ __forceinline__ void stage_rows(T* dst, const T* src, int N, int D, size_t src_rs) {
+  const int P = staged_pitch(D);
+  constexpr int EPV = 16 / (int)sizeof(T);  // elements per 16-byte vector
+  if (D % EPV == 0 && src_rs % EPV == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const int vpr = D / EPV;  // vectors per row
+    int n = threadIdx.x / vpr, c = threadIdx.x - n * vpr;
+    const int dn = blockDim.x / vpr, dc = blockDim.x - dn * vpr;
+    while (n < N) {
+      const uint4 u = *reinterpret_cast<const uint4*>(src + (size_t)n * src_rs + c * EPV);
+      uint32_t* w = reinterpret_cast<uint32_t*>(dst + (size_t)n * P + c * EPV);
+      w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
+      n += dn;
+      c += dc;
+      if (c >= vpr) { c -= vpr; ++n; }
+    }
+    return;
+  }
+  for (int e = threadIdx.x; e < N * D; e += blockDim.x) {
+    const int n = e / D, d = e - n * D;
+    dst[n * P + d] = src[(size_t)n * src_rs + d];
+  }
 }
 
 struct EvoShape {
@@ -50,61 +105,76 @@ __device__ __forceinline__ size_t row_off(const EvoShape& sh, int b, int s, int 
   return ((((size_t)b * sh.S + s) * sh.N + n) * sh.H + h) * sh.D;
 }
 
+// `staged` != 0: the K and V rows of this (batch, MSA row, head) are first copied
+// into shared memory (after the per-warp float32 row buffers).
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 evo_fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                const float* __restrict__ mask, const float* __restrict__ bias,
-               T* __restrict__ o, float* __restrict__ lse, EvoShape sh) {
-  extern __shared__ float smem[];
+               T* __restrict__ o, float* __restrict__ lse, EvoShape sh, int staged) {
+  extern __shared__ __align__(16) float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int i = blockIdx.x * kWarps + warp;
   const int h = blockIdx.y, bs = blockIdx.z, b = bs / sh.S, s = bs % sh.S;
   const int N = sh.N, D = sh.D;
   float* qs = smem + warp * D;
-  if (i >= N) return;
-  const size_t rs = (size_t)sh.H * D;  // stride between residues
-  const T* qr = q + row_off(sh, b, s, i, h);
+  size_t rs = (size_t)sh.H * D;  // stride between residues
   const T* kb = k + row_off(sh, b, s, 0, h);
   const T* vb = v + row_off(sh, b, s, 0, h);
-  const float* brow = bias + (((size_t)b * sh.H + h) * N + i) * N;
+  if (staged) {
+    T* sk = reinterpret_cast<T*>(smem + kWarps * D);
+    T* sv = sk + (size_t)N * staged_pitch(D);
+    stage_rows<T>(sk, kb, N, D, rs);
+    stage_rows<T>(sv, vb, N, D, rs);
+    __syncthreads();
+    kb = sk;
+    vb = sv;
+    rs = staged_pitch(D);
+  }
   const float* mrow = mask + (size_t)bs * N;
-  for (int d = lane; d < D; d += 32) qs[d] = to_f32<T>(qr[d]);
-  __syncwarp();
-  float m = -INFINITY, l = 0.f;
-  float acc[kMaxDT];
+  for (int r = 0; r < kRowsPerWarp; ++r) {
+    const int i = (blockIdx.x * kWarps + warp) * kRowsPerWarp + r;
+    if (i >= N) break;
+    const T* qr = q + row_off(sh, b, s, i, h);
+    const float* brow = bias + (((size_t)b * sh.H + h) * N + i) * N;
+    __syncwarp();
+    for (int d = lane; d < D; d += 32) qs[d] = to_f32<T>(qr[d]);
+    __syncwarp();
+    float m = -INFINITY, l = 0.f;
+    float acc[kMaxDT];
 #pragma unroll
-  for (int t = 0; t < kMaxDT; ++t) acc[t] = 0.f;
-  for (int j0 = 0; j0 < N; j0 += 32) {
-    const int j = j0 + lane;
-    const float sc = j < N ? sh.scale * dot_row<T>(qs, kb + j * rs, D) + brow[j] + mrow[j]
-                           : -INFINITY;
-    const float m_new = fmaxf(m, warp_max(sc));
-    const float corr = expf(m - m_new);
-    const float p = expf(sc - m_new);
-    l = l * corr + warp_sum(p);
-    const float pr = round_to<T>(p);  // probabilities enter P V in the input dtype
+    for (int t = 0; t < kMaxDT; ++t) acc[t] = 0.f;
+    for (int j0 = 0; j0 < N; j0 += 32) {
+      const int j = j0 + lane;
+      const float sc = j < N ? sh.scale * dot_row<T>(qs, kb + j * rs, D) + brow[j] + mrow[j]
+                             : -INFINITY;
+      const float m_new = fmaxf(m, warp_max(sc));
+      const float corr = expf(m - m_new);
+      const float p = expf(sc - m_new);
+      l = l * corr + warp_sum(p);
+      const float pr = round_to<T>(p);  // probabilities enter P V in the input dtype
 #pragma unroll
-    for (int t = 0; t < kMaxDT; ++t) acc[t] *= corr;
-    const int n = min(32, N - j0);
-    for (int jj = 0; jj < n; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, pr, jj);
-      const T* vr = vb + (size_t)(j0 + jj) * rs;
+      for (int t = 0; t < kMaxDT; ++t) acc[t] *= corr;
+      const int n = min(32, N - j0);
+      for (int jj = 0; jj < n; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, pr, jj);
+        const T* vr = vb + (size_t)(j0 + jj) * rs;
 #pragma unroll
-      for (int t = 0; t < kMaxDT; ++t) {
-        const int d = lane + 32 * t;
-        if (d < D) acc[t] = fmaf(pj, to_f32<T>(vr[d]), acc[t]);
+        for (int t = 0; t < kMaxDT; ++t) {
+          const int d = lane + 32 * t;
+          if (d < D) acc[t] = fmaf(pj, to_f32<T>(vr[d]), acc[t]);
+        }
       }
+      m = m_new;
     }
-    m = m_new;
-  }
-  T* orow = o + row_off(sh, b, s, i, h);
-  const float inv = 1.0f / l;
+    T* orow = o + row_off(sh, b, s, i, h);
+    const float inv = 1.0f / l;
 #pragma unroll
-  for (int t = 0; t < kMaxDT; ++t) {
-    const int d = lane + 32 * t;
-    if (d < D) orow[d] = from_f32<T>(acc[t] * inv);
+    for (int t = 0; t < kMaxDT; ++t) {
+      const int d = lane + 32 * t;
+      if (d < D) orow[d] = from_f32<T>(acc[t] * inv);
+    }
+    if (lane == 0) lse[((size_t)bs * sh.H + h) * N + i] = m + logf(l);
   }
-  if (lane == 0) lse[((size_t)bs * sh.H + h) * N + i] = m + logf(l);
 }
 
 // delta[b,s,h,i] = sum_d do * o
@@ -124,29 +194,44 @@ evo_delta_kernel(const T* __restrict__ dout, const T* __restrict__ o, float* __r
 }
 
 // One warp per (batch, head, query row): walks the MSA rows, writes dq for each
-// and keeps the row of d_pair_bias (lane = key index mod 32) in registers.
+// and keeps the row of d_pair_bias (lane = key index mod 32) in registers. With
+// `staged`, the block re-stages K and V for every MSA row.
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 evo_dq_dbias_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T* __restrict__ k,
                     const T* __restrict__ v, const float* __restrict__ mask,
                     const float* __restrict__ bias, const float* __restrict__ lse,
                     const float* __restrict__ delta, T* __restrict__ dq,
-                    float* __restrict__ dbias, EvoShape sh) {
-  extern __shared__ float smem[];
+                    float* __restrict__ dbias, EvoShape sh, int staged) {
+  extern __shared__ __align__(16) float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int i = blockIdx.x * kWarps + warp;
   const int h = blockIdx.y, b = blockIdx.z;
   const int N = sh.N, D = sh.D;
   float* qs = smem + warp * 2 * D;
   float* gs = qs + D;
-  if (i >= N) return;
-  const size_t rs = (size_t)sh.H * D;
-  const float* brow = bias + (((size_t)b * sh.H + h) * N + i) * N;
+  T* sk = reinterpret_cast<T*>(smem + kWarps * 2 * D);
+  T* sv = sk + (size_t)N * staged_pitch(D);
+  const bool active = i < N;  // idle warps still take part in the block barriers
+  const float* brow = bias + (((size_t)b * sh.H + h) * N + (active ? i : 0)) * N;
   float db[kMaxChunks];
 #pragma unroll
   for (int c = 0; c < kMaxChunks; ++c) db[c] = 0.f;
   for (int s = 0; s < sh.S; ++s) {
     const int bs = b * sh.S + s;
+    size_t rs = (size_t)sh.H * D;
+    const T* kb = k + row_off(sh, b, s, 0, h);
+    const T* vb = v + row_off(sh, b, s, 0, h);
+    if (staged) {
+      __syncthreads();  // every warp is done with the previous MSA row's K and V
+      stage_rows<T>(sk, kb, N, D, rs);
+      stage_rows<T>(sv, vb, N, D, rs);
+      __syncthreads();
+      kb = sk;
+      vb = sv;
+      rs = staged_pitch(D);
+    }
+    if (!active) continue;
     const size_t off = row_off(sh, b, s, i, h);
     __syncwarp();
     for (int d = lane; d < D; d += 32) {
@@ -154,8 +239,6 @@ evo_dq_dbias_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T
       gs[d] = to_f32<T>(dout[off + d]);
     }
     __syncwarp();
-    const T* kb = k + row_off(sh, b, s, 0, h);
-    const T* vb = v + row_off(sh, b, s, 0, h);
     const float* mrow = mask + (size_t)bs * N;
     const size_t stat = ((size_t)bs * sh.H + h) * N + i;
     const float lse_i = lse[stat], delta_i = delta[stat];
@@ -191,6 +274,7 @@ evo_dq_dbias_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T
       if (d < D) dq[off + d] = from_f32<T>(sh.scale * acc[t]);
     }
   }
+  if (!active) return;
   float* drow = dbias + (((size_t)b * sh.H + h) * N + i) * N;
 #pragma unroll
   for (int c = 0; c < kMaxChunks; ++c) {
@@ -199,70 +283,101 @@ evo_dq_dbias_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T
   }
 }
 
-// One warp per key row of (batch, MSA row, head).
+// One warp per key row of (batch, MSA row, head); with `staged` the block first
+// copies the Q and dO rows into shared memory.
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 evo_dkdv_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T* __restrict__ k,
                 const T* __restrict__ v, const float* __restrict__ mask,
                 const float* __restrict__ bias, const float* __restrict__ lse,
                 const float* __restrict__ delta, T* __restrict__ dk, T* __restrict__ dv,
-                EvoShape sh) {
-  extern __shared__ float smem[];
+                EvoShape sh, int staged) {
+  extern __shared__ __align__(16) float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.x * kWarps + warp;
   const int h = blockIdx.y, bs = blockIdx.z, b = bs / sh.S, s = bs % sh.S;
   const int N = sh.N, D = sh.D;
   float* ks = smem + warp * 2 * D;
   float* vs = ks + D;
-  if (j >= N) return;
-  const size_t rs = (size_t)sh.H * D;
-  const size_t koff = row_off(sh, b, s, j, h);
-  for (int d = lane; d < D; d += 32) {
-    ks[d] = to_f32<T>(k[koff + d]);
-    vs[d] = to_f32<T>(v[koff + d]);
-  }
-  __syncwarp();
+  size_t rs = (size_t)sh.H * D;
   const T* qb = q + row_off(sh, b, s, 0, h);
   const T* gb = dout + row_off(sh, b, s, 0, h);
-  const float* bcol = bias + ((size_t)b * sh.H + h) * N * N + j;  // + i * N
-  const float mj = mask[(size_t)bs * N + j];
+  if (staged) {
+    T* sq = reinterpret_cast<T*>(smem + kWarps * 2 * D);
+    T* sg = sq + (size_t)N * staged_pitch(D);
+    stage_rows<T>(sq, qb, N, D, rs);
+    stage_rows<T>(sg, gb, N, D, rs);
+    __syncthreads();
+    qb = sq;
+    gb = sg;
+    rs = staged_pitch(D);
+  }
   const float* lrow = lse + ((size_t)bs * sh.H + h) * N;
   const float* drow = delta + ((size_t)bs * sh.H + h) * N;
-  float acc_k[kMaxDT], acc_v[kMaxDT];
-#pragma unroll
-  for (int t = 0; t < kMaxDT; ++t) acc_k[t] = acc_v[t] = 0.f;
-  for (int i0 = 0; i0 < N; i0 += 32) {
-    const int i = i0 + lane;
-    float p = 0.f, ds = 0.f;
-    if (i < N) {
-      p = expf(sh.scale * dot_row<T>(ks, qb + i * rs, D) + bcol[(size_t)i * N] + mj - lrow[i]);
-      ds = p * (dot_row<T>(vs, gb + i * rs, D) - drow[i]);
-      p = round_to<T>(p);  // P^T dO takes P in the input dtype, as P V does
+  for (int r = 0; r < kRowsPerWarp; ++r) {
+    const int j = (blockIdx.x * kWarps + warp) * kRowsPerWarp + r;
+    if (j >= N) break;
+    const size_t koff = row_off(sh, b, s, j, h);
+    __syncwarp();
+    for (int d = lane; d < D; d += 32) {
+      ks[d] = to_f32<T>(k[koff + d]);
+      vs[d] = to_f32<T>(v[koff + d]);
     }
-    const int n = min(32, N - i0);
-    for (int ii = 0; ii < n; ++ii) {
-      const float pi = __shfl_sync(0xffffffffu, p, ii);
-      const float di = __shfl_sync(0xffffffffu, ds, ii);
-      const T* qr = qb + (size_t)(i0 + ii) * rs;
-      const T* gr = gb + (size_t)(i0 + ii) * rs;
+    __syncwarp();
+    const float* bcol = bias + ((size_t)b * sh.H + h) * N * N + j;  // + i * N
+    const float mj = mask[(size_t)bs * N + j];
+    float acc_k[kMaxDT], acc_v[kMaxDT];
 #pragma unroll
-      for (int t = 0; t < kMaxDT; ++t) {
-        const int d = lane + 32 * t;
-        if (d < D) {
-          acc_v[t] = fmaf(pi, to_f32<T>(gr[d]), acc_v[t]);
-          acc_k[t] = fmaf(di, to_f32<T>(qr[d]), acc_k[t]);
+    for (int t = 0; t < kMaxDT; ++t) acc_k[t] = acc_v[t] = 0.f;
+    for (int i0 = 0; i0 < N; i0 += 32) {
+      const int i = i0 + lane;
+      float p = 0.f, ds = 0.f;
+      if (i < N) {
+        p = expf(sh.scale * dot_row<T>(ks, qb + i * rs, D) + bcol[(size_t)i * N] + mj - lrow[i]);
+        ds = p * (dot_row<T>(vs, gb + i * rs, D) - drow[i]);
+        p = round_to<T>(p);  // P^T dO takes P in the input dtype, as P V does
+      }
+      const int n = min(32, N - i0);
+      for (int ii = 0; ii < n; ++ii) {
+        const float pi = __shfl_sync(0xffffffffu, p, ii);
+        const float di = __shfl_sync(0xffffffffu, ds, ii);
+        const T* qr = qb + (size_t)(i0 + ii) * rs;
+        const T* gr = gb + (size_t)(i0 + ii) * rs;
+#pragma unroll
+        for (int t = 0; t < kMaxDT; ++t) {
+          const int d = lane + 32 * t;
+          if (d < D) {
+            acc_v[t] = fmaf(pi, to_f32<T>(gr[d]), acc_v[t]);
+            acc_k[t] = fmaf(di, to_f32<T>(qr[d]), acc_k[t]);
+          }
         }
       }
     }
-  }
 #pragma unroll
-  for (int t = 0; t < kMaxDT; ++t) {
-    const int d = lane + 32 * t;
-    if (d < D) {
-      dk[koff + d] = from_f32<T>(sh.scale * acc_k[t]);
-      dv[koff + d] = from_f32<T>(acc_v[t]);
+    for (int t = 0; t < kMaxDT; ++t) {
+      const int d = lane + 32 * t;
+      if (d < D) {
+        dk[koff + d] = from_f32<T>(sh.scale * acc_k[t]);
+        dv[koff + d] = from_f32<T>(acc_v[t]);
+      }
     }
   }
+}
+
+// Dynamic shared memory of a kernel with `bufs` float32 row buffers per warp
+// and (when it fits) two staged [N, D] matrices of T; *staged says which.
+template <typename T, typename Kernel>
+size_t evo_smem(Kernel kernel, int bufs, int64_t N, int64_t D, int* staged) {
+  const size_t base = (size_t)kWarps * bufs * D * sizeof(float);
+  const size_t want = base + 2 * (size_t)N * staged_pitch((int)D) * sizeof(T);
+  *staged = 0;
+  if (!tune("evoattention.no_stage") && want <= (size_t)device_info().max_smem_optin &&
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want) ==
+          cudaSuccess) {
+    *staged = 1;
+    return want;
+  }
+  cudaGetLastError();
+  return base;
 }
 
 int check_evo(const char* what, int64_t B, int64_t S, int64_t N, int64_t H, int64_t D, int dtype) {
@@ -294,9 +409,13 @@ extern "C" int evg_evoattention_fwd(const void* q, const void* k, const void* v,
   if (int rc = check_evo("evoattention_fwd", B, S, N, H, D, dtype)) return rc;
   const EvoShape sh{(int)B, (int)S, (int)N, (int)H, (int)D, scale};
   return EVG_DISPATCH_DTYPE(dtype, [&] {
-    dim3 grid((unsigned)((N + kWarps - 1) / kWarps), (unsigned)H, (unsigned)(B * S));
-    evo_fwd_kernel<T><<<grid, kWarps * 32, kWarps * D * sizeof(float), (cudaStream_t)stream>>>(
-        (const T*)q, (const T*)k, (const T*)v, res_mask, pair_bias, (T*)o, lse, sh);
+    const int rows_per_block = kWarps * kRowsPerWarp;
+    dim3 grid((unsigned)((N + rows_per_block - 1) / rows_per_block), (unsigned)H,
+              (unsigned)(B * S));
+    int staged = 0;
+    const size_t smem = evo_smem<T>(evo_fwd_kernel<T>, 1, N, D, &staged);
+    evo_fwd_kernel<T><<<grid, kWarps * 32, smem, (cudaStream_t)stream>>>(
+        (const T*)q, (const T*)k, (const T*)v, res_mask, pair_bias, (T*)o, lse, sh, staged);
     return check_launch("evoattention_fwd");
   });
 }
@@ -327,15 +446,19 @@ extern "C" int evg_evoattention_bwd(const void* dout, const void* q, const void*
   cudaStream_t st = (cudaStream_t)stream;
   return EVG_DISPATCH_DTYPE(dtype, [&] {
     const unsigned tiles = (unsigned)((N + kWarps - 1) / kWarps);
-    const size_t smem = (size_t)kWarps * 2 * D * sizeof(float);
+    const int rows_per_block = kWarps * kRowsPerWarp;
+    const unsigned wide_tiles = (unsigned)((N + rows_per_block - 1) / rows_per_block);
     evo_delta_kernel<T><<<dim3(tiles, (unsigned)H, (unsigned)(B * S)), kWarps * 32, 0, st>>>(
         (const T*)dout, (const T*)o, delta, sh);
+    int staged = 0;
+    size_t smem = evo_smem<T>(evo_dq_dbias_kernel<T>, 2, N, D, &staged);
     evo_dq_dbias_kernel<T><<<dim3(tiles, (unsigned)H, (unsigned)B), kWarps * 32, smem, st>>>(
         (const T*)dout, (const T*)q, (const T*)k, (const T*)v, res_mask, pair_bias, lse, delta,
-        (T*)dq, d_pair_bias, sh);
-    evo_dkdv_kernel<T><<<dim3(tiles, (unsigned)H, (unsigned)(B * S)), kWarps * 32, smem, st>>>(
-        (const T*)dout, (const T*)q, (const T*)k, (const T*)v, res_mask, pair_bias, lse, delta,
-        (T*)dk, (T*)dv, sh);
+        (T*)dq, d_pair_bias, sh, staged);
+    smem = evo_smem<T>(evo_dkdv_kernel<T>, 2, N, D, &staged);
+    evo_dkdv_kernel<T><<<dim3(wide_tiles, (unsigned)H, (unsigned)(B * S)), kWarps * 32, smem,
+                         st>>>((const T*)dout, (const T*)q, (const T*)k, (const T*)v, res_mask,
+                               pair_bias, lse, delta, (T*)dk, (T*)dv, sh, staged);
     return check_launch("evoattention_bwd");
   });
 }

@@ -51,6 +51,23 @@ def test_pair_passes_the_declared_gate(dims, dtype):
     assert_unchanged(dev, snap)
 
 
+def test_unstaged_path_gives_the_same_answer():
+    """With staging disabled the kernels read K/V (Q/dO) rows straight from global memory."""
+    from evograd_b200 import _cabi
+
+    dims, dtype = dict(B=1, S=3, H=2, N=129, D=24), "bfloat16"
+    inputs = to_device(ao.make_inputs(OP, dims, dtype))
+    o1, g1, _ = run_pair(OP, inputs)
+    try:
+        _cabi.tune_set("evoattention.no_stage", 1)
+        o2, g2, _ = run_pair(OP, inputs)
+    finally:
+        _cabi.tune_set("evoattention.no_stage", 0)
+    assert torch.equal(o1, o2)
+    for a, b in zip(g1, g2):
+        assert torch.equal(a, b)
+
+
 def test_gradients_are_bit_reproducible():
     dims, dtype = dict(B=1, S=4, H=2, N=100, D=32), "bfloat16"
     inputs = to_device(ao.make_inputs(OP, dims, dtype))
