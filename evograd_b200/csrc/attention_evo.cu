@@ -18,7 +18,17 @@
 // d_pair_bias is accumulated over the MSA rows inside the warp that owns a
 // (batch, head, query) row, without atomics. Saved state: o and the float32
 // log-sum-exp [B, S, H, N].
+#include <algorithm>
+
 #include "evg_common.cuh"
+
+// 16-bit element types only (the reference declares float16 | bfloat16).
+#define EVG_DISPATCH_DTYPE_16(dtype, ...)                               \
+  [&]() -> int {                                                        \
+    if ((dtype) == EVG_F16) { using T = __half; return __VA_ARGS__(); } \
+    using T = __nv_bfloat16;                                            \
+    return __VA_ARGS__();                                               \
+  }()
 
 namespace evg {
 namespace {
@@ -38,24 +48,36 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
-// dot(a, b_row): a is float32 in shared memory (broadcast reads), b_row a row of
-// T in shared or global memory. 16-bit rows are read two elements at a time
-// when D is even (rows then start on 4-byte boundaries in every layout used).
+// dot(a, b_row): a is float32 in shared memory (broadcast reads, 16-byte aligned),
+// b_row a row of T in shared or global memory. 16-bit rows are read as 32-bit
+// words when D is a multiple of 4 (rows then start on 4-byte boundaries in
+// every layout used).
+template <typename T>
+__device__ __forceinline__ void unpack_word(uint32_t u, float& lo, float& hi) {
+  T a, b;
+  const uint32_t uh = u >> 16;
+  memcpy(&a, &u, 2);
+  memcpy(&b, &uh, 2);
+  lo = to_f32<T>(a);
+  hi = to_f32<T>(b);
+}
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* a_smem, const T* b_row, int D) {
   float s = 0.f;
   if constexpr (sizeof(T) == 2) {
-    if ((D & 1) == 0) {
+    if ((D & 3) == 0) {  // four elements per step: one float4 of a, two words of b
       const uint32_t* w = reinterpret_cast<const uint32_t*>(b_row);
+      const float4* a4 = reinterpret_cast<const float4*>(a_smem);
       float s1 = 0.f;
-      for (int d = 0; d < D / 2; ++d) {
-        const uint32_t u = w[d];
-        T lo, hi;
-        memcpy(&lo, &u, 2);
-        const uint32_t uh = u >> 16;
-        memcpy(&hi, &uh, 2);
-        s = fmaf(a_smem[2 * d], to_f32<T>(lo), s);
-        s1 = fmaf(a_smem[2 * d + 1], to_f32<T>(hi), s1);
+      for (int d = 0; d < D / 4; ++d) {
+        const float4 a = a4[d];
+        float b0, b1, b2, b3;
+        unpack_word<T>(w[2 * d], b0, b1);
+        unpack_word<T>(w[2 * d + 1], b2, b3);
+        s = fmaf(a.x, b0, s);
+        s1 = fmaf(a.y, b1, s1);
+        s = fmaf(a.z, b2, s);
+        s1 = fmaf(a.w, b3, s1);
       }
       return s + s1;
     }
@@ -105,9 +127,10 @@ __device__ __forceinline__ size_t row_off(const EvoShape& sh, int b, int s, int 
   return ((((size_t)b * sh.S + s) * sh.N + n) * sh.H + h) * sh.D;
 }
 
+// DT = ceil(head_dim / 32) accumulators per lane (1, 2, 4 or 8).
 // `staged` != 0: the K and V rows of this (batch, MSA row, head) are first copied
 // into shared memory (after the per-warp float32 row buffers).
-template <typename T>
+template <typename T, int DT>
 __global__ void __launch_bounds__(kWarps * 32)
 evo_fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                const float* __restrict__ mask, const float* __restrict__ bias,
@@ -140,9 +163,9 @@ evo_fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __rest
     for (int d = lane; d < D; d += 32) qs[d] = to_f32<T>(qr[d]);
     __syncwarp();
     float m = -INFINITY, l = 0.f;
-    float acc[kMaxDT];
+    float acc[DT];
 #pragma unroll
-    for (int t = 0; t < kMaxDT; ++t) acc[t] = 0.f;
+    for (int t = 0; t < DT; ++t) acc[t] = 0.f;
     for (int j0 = 0; j0 < N; j0 += 32) {
       const int j = j0 + lane;
       const float sc = j < N ? sh.scale * dot_row<T>(qs, kb + j * rs, D) + brow[j] + mrow[j]
@@ -153,13 +176,13 @@ evo_fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __rest
       l = l * corr + warp_sum(p);
       const float pr = round_to<T>(p);  // probabilities enter P V in the input dtype
 #pragma unroll
-      for (int t = 0; t < kMaxDT; ++t) acc[t] *= corr;
+      for (int t = 0; t < DT; ++t) acc[t] *= corr;
       const int n = min(32, N - j0);
       for (int jj = 0; jj < n; ++jj) {
         const float pj = __shfl_sync(0xffffffffu, pr, jj);
         const T* vr = vb + (size_t)(j0 + jj) * rs;
 #pragma unroll
-        for (int t = 0; t < kMaxDT; ++t) {
+        for (int t = 0; t < DT; ++t) {
           const int d = lane + 32 * t;
           if (d < D) acc[t] = fmaf(pj, to_f32<T>(vr[d]), acc[t]);
         }
@@ -169,7 +192,7 @@ evo_fwd_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __rest
     T* orow = o + row_off(sh, b, s, i, h);
     const float inv = 1.0f / l;
 #pragma unroll
-    for (int t = 0; t < kMaxDT; ++t) {
+    for (int t = 0; t < DT; ++t) {
       const int d = lane + 32 * t;
       if (d < D) orow[d] = from_f32<T>(acc[t] * inv);
     }
@@ -196,28 +219,33 @@ evo_delta_kernel(const T* __restrict__ dout, const T* __restrict__ o, float* __r
 // One warp per (batch, head, query row): walks the MSA rows, writes dq for each
 // and keeps the row of d_pair_bias (lane = key index mod 32) in registers. With
 // `staged`, the block re-stages K and V for every MSA row.
-template <typename T>
+template <typename T, int DT, int MAXC>
 __global__ void __launch_bounds__(kWarps * 32)
 evo_dq_dbias_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T* __restrict__ k,
                     const T* __restrict__ v, const float* __restrict__ mask,
                     const float* __restrict__ bias, const float* __restrict__ lse,
                     const float* __restrict__ delta, T* __restrict__ dq,
-                    float* __restrict__ dbias, EvoShape sh, int staged) {
+                    float* __restrict__ dbias, EvoShape sh, int staged, int split) {
   extern __shared__ __align__(16) float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int i = blockIdx.x * kWarps + warp;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // blockIdx.z = b * split + part: the MSA rows are cut into `split` contiguous
+  // parts so that enough blocks exist; part p writes its own d_pair_bias slab
+  // (dbias + p * B*H*N*N), added up afterwards in part order.
+  const int h = blockIdx.y, b = blockIdx.z / split, part = blockIdx.z % split;
   const int N = sh.N, D = sh.D;
+  const int s_lo = (int)((long long)sh.S * part / split);
+  const int s_hi = (int)((long long)sh.S * (part + 1) / split);
   float* qs = smem + warp * 2 * D;
   float* gs = qs + D;
   T* sk = reinterpret_cast<T*>(smem + kWarps * 2 * D);
   T* sv = sk + (size_t)N * staged_pitch(D);
   const bool active = i < N;  // idle warps still take part in the block barriers
   const float* brow = bias + (((size_t)b * sh.H + h) * N + (active ? i : 0)) * N;
-  float db[kMaxChunks];
+  float db[MAXC];
 #pragma unroll
-  for (int c = 0; c < kMaxChunks; ++c) db[c] = 0.f;
-  for (int s = 0; s < sh.S; ++s) {
+  for (int c = 0; c < MAXC; ++c) db[c] = 0.f;
+  for (int s = s_lo; s < s_hi; ++s) {
     const int bs = b * sh.S + s;
     size_t rs = (size_t)sh.H * D;
     const T* kb = k + row_off(sh, b, s, 0, h);
@@ -242,11 +270,11 @@ evo_dq_dbias_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T
     const float* mrow = mask + (size_t)bs * N;
     const size_t stat = ((size_t)bs * sh.H + h) * N + i;
     const float lse_i = lse[stat], delta_i = delta[stat];
-    float acc[kMaxDT];
+    float acc[DT];
 #pragma unroll
-    for (int t = 0; t < kMaxDT; ++t) acc[t] = 0.f;
+    for (int t = 0; t < DT; ++t) acc[t] = 0.f;
 #pragma unroll
-    for (int c = 0; c < kMaxChunks; ++c) {
+    for (int c = 0; c < MAXC; ++c) {
       const int j0 = c * 32;
       if (j0 < N) {
         const int j = j0 + lane;
@@ -261,7 +289,7 @@ evo_dq_dbias_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T
           const float dj = __shfl_sync(0xffffffffu, ds, jj);
           const T* kr = kb + (size_t)(j0 + jj) * rs;
 #pragma unroll
-          for (int t = 0; t < kMaxDT; ++t) {
+          for (int t = 0; t < DT; ++t) {
             const int d = lane + 32 * t;
             if (d < D) acc[t] = fmaf(dj, to_f32<T>(kr[d]), acc[t]);
           }
@@ -269,15 +297,15 @@ evo_dq_dbias_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T
       }
     }
 #pragma unroll
-    for (int t = 0; t < kMaxDT; ++t) {
+    for (int t = 0; t < DT; ++t) {
       const int d = lane + 32 * t;
       if (d < D) dq[off + d] = from_f32<T>(sh.scale * acc[t]);
     }
   }
   if (!active) return;
-  float* drow = dbias + (((size_t)b * sh.H + h) * N + i) * N;
+  float* drow = dbias + ((((size_t)part * sh.B + b) * sh.H + h) * N + i) * N;
 #pragma unroll
-  for (int c = 0; c < kMaxChunks; ++c) {
+  for (int c = 0; c < MAXC; ++c) {
     const int j = c * 32 + lane;
     if (j < N) drow[j] = db[c];
   }
@@ -285,7 +313,7 @@ evo_dq_dbias_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T
 
 // One warp per key row of (batch, MSA row, head); with `staged` the block first
 // copies the Q and dO rows into shared memory.
-template <typename T>
+template <typename T, int DT>
 __global__ void __launch_bounds__(kWarps * 32)
 evo_dkdv_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T* __restrict__ k,
                 const T* __restrict__ v, const float* __restrict__ mask,
@@ -325,9 +353,9 @@ evo_dkdv_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T* __
     __syncwarp();
     const float* bcol = bias + ((size_t)b * sh.H + h) * N * N + j;  // + i * N
     const float mj = mask[(size_t)bs * N + j];
-    float acc_k[kMaxDT], acc_v[kMaxDT];
+    float acc_k[DT], acc_v[DT];
 #pragma unroll
-    for (int t = 0; t < kMaxDT; ++t) acc_k[t] = acc_v[t] = 0.f;
+    for (int t = 0; t < DT; ++t) acc_k[t] = acc_v[t] = 0.f;
     for (int i0 = 0; i0 < N; i0 += 32) {
       const int i = i0 + lane;
       float p = 0.f, ds = 0.f;
@@ -343,7 +371,7 @@ evo_dkdv_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T* __
         const T* qr = qb + (size_t)(i0 + ii) * rs;
         const T* gr = gb + (size_t)(i0 + ii) * rs;
 #pragma unroll
-        for (int t = 0; t < kMaxDT; ++t) {
+        for (int t = 0; t < DT; ++t) {
           const int d = lane + 32 * t;
           if (d < D) {
             acc_v[t] = fmaf(pi, to_f32<T>(gr[d]), acc_v[t]);
@@ -353,7 +381,7 @@ evo_dkdv_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T* __
       }
     }
 #pragma unroll
-    for (int t = 0; t < kMaxDT; ++t) {
+    for (int t = 0; t < DT; ++t) {
       const int d = lane + 32 * t;
       if (d < D) {
         dk[koff + d] = from_f32<T>(sh.scale * acc_k[t]);
@@ -361,6 +389,27 @@ evo_dkdv_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T* __
       }
     }
   }
+}
+
+// d_pair_bias = sum over the `split` slabs, in slab order.
+__global__ void evo_dbias_reduce_kernel(const float* __restrict__ slabs, float* __restrict__ out,
+                                        int64_t n, int split) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n;
+       e += (int64_t)gridDim.x * blockDim.x) {
+    float a = slabs[e];
+    for (int p = 1; p < split; ++p) a += slabs[(size_t)p * n + e];
+    out[e] = a;
+  }
+}
+
+// Parts the MSA axis is cut into for the dq / d_pair_bias kernel: enough for
+// about four blocks per SM, at most 16 and at most S.
+int evo_split(int64_t B, int64_t S, int64_t N, int64_t H) {
+  const int64_t blocks = ((N + kWarps - 1) / kWarps) * H * B;
+  int64_t split = (4 * (int64_t)device_info().sm_count + blocks - 1) / blocks;
+  if (split > 16) split = 16;
+  if (split > S) split = S;
+  return split < 1 ? 1 : (int)split;
 }
 
 // Dynamic shared memory of a kernel with `bufs` float32 row buffers per warp
@@ -384,8 +433,8 @@ int check_evo(const char* what, int64_t B, int64_t S, int64_t N, int64_t H, int6
   if (B <= 0 || S <= 0 || N <= 0 || H <= 0 || D <= 0)
     return fail(EVG_EBADSHAPE, "%s: B=%lld S=%lld N=%lld H=%lld D=%lld must be positive", what,
                 (long long)B, (long long)S, (long long)N, (long long)H, (long long)D);
-  if (dtype != EVG_BF16 && dtype != EVG_F16 && dtype != EVG_F32)
-    return fail(EVG_EDTYPE, "%s: dtype %d", what, dtype);
+  if (dtype != EVG_BF16 && dtype != EVG_F16)  // the declaration's dtypes (float16|bfloat16)
+    return fail(EVG_EDTYPE, "%s: dtype %d (supported: float16, bfloat16)", what, dtype);
   if (D > 32 * kMaxDT || N > 32 * kMaxChunks)
     return fail(EVG_EUNSUPPORTED, "%s: head_dim %lld (max 256) or residues %lld (max 1024)", what,
                 (long long)D, (long long)N);
@@ -393,6 +442,76 @@ int check_evo(const char* what, int64_t B, int64_t S, int64_t N, int64_t H, int6
     return fail(EVG_EUNSUPPORTED, "%s: H=%lld or B*S=%lld above 65535", what, (long long)H,
                 (long long)(B * S));
   return EVG_OK;
+}
+
+inline int evo_dt(int D) { return D <= 32 ? 1 : D <= 64 ? 2 : D <= 128 ? 4 : 8; }
+
+template <typename T>
+int launch_evo_fwd(const void* q, const void* k, const void* v, const float* res_mask,
+                   const float* pair_bias, void* o, float* lse, const EvoShape& sh,
+                   cudaStream_t stream) {
+  const int N = sh.N, D = sh.D, dt = evo_dt(D);
+  const int rows_per_block = kWarps * kRowsPerWarp;
+  dim3 grid((unsigned)((N + rows_per_block - 1) / rows_per_block), (unsigned)sh.H,
+            (unsigned)(sh.B * sh.S));
+#define EVG_EVO_FWD(DT_)                                                                     \
+  if (dt == DT_) {                                                                           \
+    int staged = 0;                                                                          \
+    auto kern = evo_fwd_kernel<T, DT_>;                                                      \
+    const size_t smem = evo_smem<T>(kern, 1, N, D, &staged);                                 \
+    kern<<<grid, kWarps * 32, smem, stream>>>((const T*)q, (const T*)k, (const T*)v,         \
+                                              res_mask, pair_bias, (T*)o, lse, sh, staged);  \
+  }
+  EVG_EVO_FWD(1) EVG_EVO_FWD(2) EVG_EVO_FWD(4) EVG_EVO_FWD(8)
+#undef EVG_EVO_FWD
+  return check_launch("evoattention_fwd");
+}
+
+template <typename T>
+int launch_evo_bwd(const void* dout, const void* q, const void* k, const void* v,
+                   const float* res_mask, const float* pair_bias, const void* o,
+                   const float* lse, void* dq, void* dk, void* dv, float* d_pair_bias,
+                   float* workspace, const EvoShape& sh, cudaStream_t st) {
+  const int64_t B = sh.B, S = sh.S, N = sh.N, H = sh.H, D = sh.D;
+  float* delta = workspace;
+  const int split = evo_split(B, S, N, H);
+  float* slabs = split > 1 ? delta + B * S * H * N : d_pair_bias;
+  const int dt = evo_dt((int)D);
+  const bool few_chunks = N <= 384;
+  const unsigned tiles = (unsigned)((N + kWarps - 1) / kWarps);
+  const int rows_per_block = kWarps * kRowsPerWarp;
+  const unsigned wide_tiles = (unsigned)((N + rows_per_block - 1) / rows_per_block);
+  evo_delta_kernel<T><<<dim3(tiles, (unsigned)H, (unsigned)(B * S)), kWarps * 32, 0, st>>>(
+      (const T*)dout, (const T*)o, delta, sh);
+#define EVG_EVO_DQ(DT_, MAXC_)                                                                   \
+  if (dt == DT_ && few_chunks == (MAXC_ == 12)) {                                                \
+    int staged = 0;                                                                              \
+    auto kern = evo_dq_dbias_kernel<T, DT_, MAXC_>;                                              \
+    const size_t smem = evo_smem<T>(kern, 2, N, D, &staged);                                     \
+    kern<<<dim3(tiles, (unsigned)H, (unsigned)(B * split)), kWarps * 32, smem, st>>>(            \
+        (const T*)dout, (const T*)q, (const T*)k, (const T*)v, res_mask, pair_bias, lse, delta,  \
+        (T*)dq, slabs, sh, staged, split);                                                       \
+  }
+  EVG_EVO_DQ(1, 12) EVG_EVO_DQ(2, 12) EVG_EVO_DQ(4, 12) EVG_EVO_DQ(8, 12)
+  EVG_EVO_DQ(1, 32) EVG_EVO_DQ(2, 32) EVG_EVO_DQ(4, 32) EVG_EVO_DQ(8, 32)
+#undef EVG_EVO_DQ
+  if (split > 1) {
+    const int64_t n = B * H * N * N;
+    evo_dbias_reduce_kernel<<<(unsigned)std::min<int64_t>((n + 255) / 256, 4096), 256, 0, st>>>(
+        slabs, d_pair_bias, n, split);
+  }
+#define EVG_EVO_DKDV(DT_)                                                                        \
+  if (dt == DT_) {                                                                               \
+    int staged = 0;                                                                              \
+    auto kern = evo_dkdv_kernel<T, DT_>;                                                         \
+    const size_t smem = evo_smem<T>(kern, 2, N, D, &staged);                                     \
+    kern<<<dim3(wide_tiles, (unsigned)H, (unsigned)(B * S)), kWarps * 32, smem, st>>>(           \
+        (const T*)dout, (const T*)q, (const T*)k, (const T*)v, res_mask, pair_bias, lse, delta,  \
+        (T*)dk, (T*)dv, sh, staged);                                                             \
+  }
+  EVG_EVO_DKDV(1) EVG_EVO_DKDV(2) EVG_EVO_DKDV(4) EVG_EVO_DKDV(8)
+#undef EVG_EVO_DKDV
+  return check_launch("evoattention_bwd");
 }
 
 }  // namespace
@@ -408,15 +527,8 @@ extern "C" int evg_evoattention_fwd(const void* q, const void* k, const void* v,
     return fail(EVG_ENULL, "evoattention_fwd: null pointer argument");
   if (int rc = check_evo("evoattention_fwd", B, S, N, H, D, dtype)) return rc;
   const EvoShape sh{(int)B, (int)S, (int)N, (int)H, (int)D, scale};
-  return EVG_DISPATCH_DTYPE(dtype, [&] {
-    const int rows_per_block = kWarps * kRowsPerWarp;
-    dim3 grid((unsigned)((N + rows_per_block - 1) / rows_per_block), (unsigned)H,
-              (unsigned)(B * S));
-    int staged = 0;
-    const size_t smem = evo_smem<T>(evo_fwd_kernel<T>, 1, N, D, &staged);
-    evo_fwd_kernel<T><<<grid, kWarps * 32, smem, (cudaStream_t)stream>>>(
-        (const T*)q, (const T*)k, (const T*)v, res_mask, pair_bias, (T*)o, lse, sh, staged);
-    return check_launch("evoattention_fwd");
+  return EVG_DISPATCH_DTYPE_16(dtype, [&] {
+    return launch_evo_fwd<T>(q, k, v, res_mask, pair_bias, o, lse, sh, (cudaStream_t)stream);
   });
 }
 
@@ -424,7 +536,10 @@ extern "C" int64_t evg_evoattention_bwd_workspace_bytes(int64_t B, int64_t S, in
                                                         int64_t H, int64_t D, int dtype) {
   (void)D; (void)dtype;
   if (B <= 0 || S <= 0 || N <= 0 || H <= 0) return 0;
-  return B * S * H * N * (int64_t)sizeof(float);
+  const int split = evo_split(B, S, N, H);
+  // delta [B,S,H,N] + (split > 1: one d_pair_bias slab per part)
+  return (B * S * H * N + (split > 1 ? (int64_t)split * B * H * N * N : 0)) *
+         (int64_t)sizeof(float);
 }
 
 extern "C" int evg_evoattention_bwd(const void* dout, const void* q, const void* k, const void* v,
@@ -442,23 +557,8 @@ extern "C" int evg_evoattention_bwd(const void* dout, const void* q, const void*
     return fail(EVG_EWORKSPACE, "evoattention_bwd: workspace %lld bytes, need %lld",
                 (long long)workspace_bytes, (long long)need);
   const EvoShape sh{(int)B, (int)S, (int)N, (int)H, (int)D, scale};
-  float* delta = (float*)workspace;
-  cudaStream_t st = (cudaStream_t)stream;
-  return EVG_DISPATCH_DTYPE(dtype, [&] {
-    const unsigned tiles = (unsigned)((N + kWarps - 1) / kWarps);
-    const int rows_per_block = kWarps * kRowsPerWarp;
-    const unsigned wide_tiles = (unsigned)((N + rows_per_block - 1) / rows_per_block);
-    evo_delta_kernel<T><<<dim3(tiles, (unsigned)H, (unsigned)(B * S)), kWarps * 32, 0, st>>>(
-        (const T*)dout, (const T*)o, delta, sh);
-    int staged = 0;
-    size_t smem = evo_smem<T>(evo_dq_dbias_kernel<T>, 2, N, D, &staged);
-    evo_dq_dbias_kernel<T><<<dim3(tiles, (unsigned)H, (unsigned)B), kWarps * 32, smem, st>>>(
-        (const T*)dout, (const T*)q, (const T*)k, (const T*)v, res_mask, pair_bias, lse, delta,
-        (T*)dq, d_pair_bias, sh, staged);
-    smem = evo_smem<T>(evo_dkdv_kernel<T>, 2, N, D, &staged);
-    evo_dkdv_kernel<T><<<dim3(wide_tiles, (unsigned)H, (unsigned)(B * S)), kWarps * 32, smem,
-                         st>>>((const T*)dout, (const T*)q, (const T*)k, (const T*)v, res_mask,
-                               pair_bias, lse, delta, (T*)dk, (T*)dv, sh, staged);
-    return check_launch("evoattention_bwd");
+  return EVG_DISPATCH_DTYPE_16(dtype, [&] {
+    return launch_evo_bwd<T>(dout, q, k, v, res_mask, pair_bias, o, lse, dq, dk, dv, d_pair_bias,
+                             (float*)workspace, sh, (cudaStream_t)stream);
   });
 }

@@ -175,8 +175,8 @@ def _declared_case(op_name, dims, dtype):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference/src",
-                    help="path to the reference's src/ directory")
+    ap.add_argument("--reference", required=True,
+                    help="path to the reference's src/ directory (akumdam2/evograd checkout)")
     ap.add_argument("--only", nargs="*", default=None,
                     help="regenerate only these operators (the index keeps the others)")
     args = ap.parse_args()
