@@ -669,7 +669,7 @@ def measure_e2e(wl, steps, warmup, world):
     device = torch.device("cuda", torch.cuda.current_device())
     dev_set = wl.make(device)
     host = {k: (v.cpu().pin_memory() if torch.is_tensor(v) else v) for k, v in dev_set.items()}
-    spec = wl.pipeline_spec() if world == 1 else None
+    spec = wl.pipeline_spec()
     if spec is not None:
         from evograd_b200.host_pipeline import pipeline_for
 
@@ -688,13 +688,19 @@ def measure_e2e(wl, steps, warmup, world):
         del dev_set
         live = [None]
 
+        def finish_all(total):
+            if world > 1:  # float32 partial sums of every rank's rows, then one rounding
+                torch.distributed.all_reduce(total, op=torch.distributed.ReduceOp.SUM)
+            return finish(total, dtype)
+
         def step(_i):
             for n in param_names:
                 params[n].copy_(host[n], non_blocking=True)
             live[0] = pipe.run(host_rows, params, host_out, host_grads,
-                               (lambda total: finish(total, dtype)) if finish else None)
+                               finish_all if finish else None)
 
         ms = time_steps(step, steps, warmup, barrier=_barrier_fn(world))
+        ms = _max_over_ranks(ms, world)
         del live, params, host_rows, host_out
         torch.cuda.empty_cache()
         return ms, h2d, d2h, (f"host_pipeline: {n_chunks} row chunks, copy-in / kernels / copy-out "
