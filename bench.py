@@ -201,7 +201,10 @@ class NormWL(Workload):
         if self.world > 1:
             from evograd_b200.sharded import ShardedNorm
 
-            self.sharded = ShardedNorm(self.kind, group)
+            # EVG_BENCH_OVERLAP=1 puts the 16-32 KB all-reduce and the rounding on a side
+            # stream, overlapping the next step's forward
+            self.sharded = ShardedNorm(self.kind, group,
+                                       overlap_comm=os.environ.get("EVG_BENCH_OVERLAP", "0") == "1")
         # fwd 1 kernel; bwd 2 (row kernel + column reduce); sharded adds the rounding kernel
         self.kernels_per_step = 3 + (1 if self.world > 1 else 0)
 
@@ -643,6 +646,8 @@ def measure_graphs(wl, steps, warmup, world):
         with torch.cuda.graph(g):
             for i in range(steps):
                 body(i)  # results are dropped: the graph's pool reuses their memory
+            if hasattr(wl, "finish"):
+                wl.finish()  # join a side stream (overlapped all-reduce) before capture ends
         return g
 
     bodies = (lambda i: wl.step(sets[i % n]),
