@@ -30,7 +30,10 @@
 extern "C" {
 #endif
 
-#define EVG_ABI_VERSION 1
+/* 2: added geglu, fused add + rmsnorm, grouped-query attention, evoattention,
+ *    the no-allocation rmsnorm backward and the bounded-wait self-test; every
+ *    version-1 entry point is unchanged. */
+#define EVG_ABI_VERSION 2
 
 enum evg_dtype { EVG_F32 = 0, EVG_F16 = 1, EVG_BF16 = 2 };
 

@@ -33,7 +33,7 @@ def test_binding_table_matches_header():
 def test_version_and_target():
     from evograd_b200 import _cabi
 
-    assert _cabi.lib.evg_abi_version() == 1
+    assert _cabi.lib.evg_abi_version() == 2
     assert _cabi.lib.evg_built_for_sm() == 100
 
 
