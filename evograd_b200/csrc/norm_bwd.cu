@@ -471,7 +471,13 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
                       aligned16(w) && hidden < (int64_t)1 << 31;
   RowCfg cfg;
   bool launched = false;
-  if (vec_ok && !tune("rows.force_generic") && !tune("norm_bwd.no_ring") && !tune(LN ? "layernorm_bwd.group" : "rmsnorm_bwd.group")) {
+  // Rows of fewer than 256 vectors (under 4 KB) would leave half of a ring block's
+  // threads idle and pay its per-row barriers for little data: they go to the
+  // group kernel below, several rows per block at a time (measured at
+  // [65536, 1024] bf16: RMSNorm backward 0.45 -> 0.84 of HBM peak).
+  const bool narrow_rows = vec_ok && hidden / N < 256;
+  if (vec_ok && !narrow_rows && !tune("rows.force_generic") && !tune("norm_bwd.no_ring") &&
+      !tune(LN ? "layernorm_bwd.group" : "rmsnorm_bwd.group")) {
     // Row ring: one group of 256 or 512 threads per block, VPT vectors per
     // thread, as many stages as fit (about 48 KB of rows in flight per block).
     const int64_t nvec = hidden / N;
@@ -503,7 +509,8 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
 #undef EVG_RING
     }
   }
-  if (!launched && vec_ok && !tune("rows.force_generic") && pick_rowcfg(op, hidden / N, cfg, 512, LN)) {
+  if (!launched && vec_ok && !tune("rows.force_generic") &&
+      pick_rowcfg(op, hidden / N, cfg, narrow_rows ? 256 : 512, LN)) {
     const int groups = cfg.threads / cfg.G;
     const size_t smem =
         ((size_t)groups * 2 * NV * (cfg.G / 32) + (size_t)(NV + 1) * hidden) * sizeof(float);
