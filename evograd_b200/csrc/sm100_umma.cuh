@@ -68,8 +68,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // ctx.limit_cycles; on timeout sets the abort word (code identifies the wait).
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
                                           int code) {
-  if (*ctx.abort_flag) return;
+  // Fast path first: a phase that has already completed costs one try_wait and no
+  // shared-memory load (the abort word only matters while actually waiting).
   if (mbar_try_wait(bar, parity)) return;
+  if (*ctx.abort_flag) return;
   const long long start = clock64();
   while (!mbar_try_wait(bar, parity)) {
     if (*ctx.abort_flag) return;
