@@ -332,6 +332,129 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   }
 }
 
+// Backward, group variant for NARROW rows (fewer than 256 vectors): a row is
+// handled by a group of G threads that keep it in registers, a block holds
+// several groups working on different rows, and the groups' column sums are
+// folded through shared memory in group order before the block writes its one
+// partial row. (The one-row-per-block ring above would leave most of its threads
+// idle on such rows.) Same arithmetic as the ring kernel.
+template <typename T, int G, int VPT>
+__global__ void __launch_bounds__(rowcfg_max_threads(G))
+add_rms_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ r,
+                   const T* __restrict__ w, const float* __restrict__ rstd, T* __restrict__ dx,
+                   float* __restrict__ partial, int64_t rows, int cols) {
+  constexpr int N = Vec<T>::N;
+  constexpr int Q = N / 4;
+  extern __shared__ float4 smem4[];
+  const int gid = threadIdx.x / G;
+  const int lig = threadIdx.x % G;
+  const int groups = blockDim.x / G;
+  const int nvec = cols / N;
+  // smem: float32 weight [Q][nvec] float4 | [cols] fold buffer | [groups][2][G/32] scratch
+  float4* w4 = smem4;
+  float* colbuf = reinterpret_cast<float*>(smem4 + (size_t)Q * nvec);
+  float* scratch = colbuf + cols + gid * (2 * (G / 32));
+  int phase = 0;
+  for (int idx = threadIdx.x; idx < nvec; idx += blockDim.x) {
+    float f[N];
+    unpack<T>(*reinterpret_cast<const uint4*>(w + (size_t)idx * N), f);
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+      w4[q * nvec + idx] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+  }
+  __syncthreads();
+  float acc_w[VPT][N];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k)
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc_w[k][j] = 0.f;
+  const float inv_cols = 1.0f / (float)cols;
+
+  for (int64_t row = (int64_t)blockIdx.x * groups + gid; row < rows;
+       row += (int64_t)gridDim.x * groups) {
+    const T* xr = x + row * cols;
+    const T* rr = r + row * cols;
+    const T* gr = dy + row * cols;
+    uint4 xv[VPT], rv[VPT], gv[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = lig + k * G;
+      xv[k] = rv[k] = gv[k] = make_uint4(0, 0, 0, 0);
+      if (idx < nvec) {
+        xv[k] = ld_vec(xr + (size_t)idx * N);
+        rv[k] = ld_vec(rr + (size_t)idx * N);
+        gv[k] = ld_vec(gr + (size_t)idx * N);
+      }
+    }
+    const float rs = rstd[row];
+    const float rb = round_to<T>(rs);
+    float sv[VPT][N], gy[VPT][N];
+    float c[1] = {0.f};
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = lig + k * G;
+      float rf[N];
+      unpack<T>(xv[k], sv[k]);
+      unpack<T>(rv[k], rf);
+      unpack<T>(gv[k], gy[k]);  // padded vectors have dout = 0 and add nothing
+      const int sidx = idx < nvec ? idx : 0;
+#pragma unroll
+      for (int qq = 0; qq < Q; ++qq) {
+        const float4 wv = w4[qq * nvec + sidx];
+        const float wj[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int e = 4 * qq + j;
+          sv[k][e] = round_to<T>(sv[k][e] + rf[e]);
+          c[0] = fmaf(gy[k][e] * wj[j], sv[k][e], c[0]);
+        }
+      }
+    }
+    group_allreduce<G, 1, SumOp>(c, scratch, phase, gid, lig);
+    const float a_s = -(rs * rs) * rs * (c[0] * inv_cols);
+    T* dr = dx + row * cols;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = lig + k * G;
+      if (idx < nvec) {
+        float o[N];
+#pragma unroll
+        for (int qq = 0; qq < Q; ++qq) {
+          const float4 wv = w4[qq * nvec + idx];
+          const float wj[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int e = 4 * qq + j;
+            const float g = gy[k][e] * wj[j];
+            o[e] = fmaf(sv[k][e], a_s, g * rb);
+            acc_w[k][e] = fmaf(gy[k][e], round_to<T>(sv[k][e] * rb), acc_w[k][e]);
+          }
+        }
+        st_vec(dr + (size_t)idx * N, pack<T>(o));
+      }
+    }
+  }
+  // Fold the groups of this block in group order, then write one partial row.
+  for (int g = 0; g < groups; ++g) {
+    if (gid == g) {
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int idx = lig + k * G;
+        if (idx < nvec) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) {
+            const int col = idx * N + j;
+            colbuf[col] = g == 0 ? acc_w[k][j] : colbuf[col] + acc_w[k][j];
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* pw = partial + (size_t)blockIdx.x * cols;
+  for (int col = threadIdx.x; col < cols; col += blockDim.x) pw[col] = colbuf[col];
+}
+
 // Any width / alignment. One block per row at a time; the block's partial row
 // in the workspace is private to it, so plain read-modify-write is race free.
 template <typename T>
@@ -411,7 +534,27 @@ int launch_add_rms_bwd(const void* dy, const void* x, const void* r, const void*
   bool launched = false;
   const bool vec_ok = hidden % N == 0 && aligned16(x) && aligned16(r) && aligned16(dy) &&
                       aligned16(dx) && aligned16(w) && hidden < (int64_t)1 << 31;
-  if (vec_ok && !tune("rows.force_generic") && !tune("norm_bwd.no_ring")) {
+  const bool narrow_rows = vec_ok && hidden / N < 256;
+  RowCfg cfg;
+  if (narrow_rows && !tune("rows.force_generic") &&
+      pick_rowcfg(op, hidden / N, cfg, 256, false)) {
+    const int groups = cfg.threads / cfg.G;
+    const size_t smem = ((size_t)groups * 2 * (cfg.G / 32) + (size_t)2 * hidden) * sizeof(float);
+#define EVG_X(g, v)                                                                            \
+  if (!launched && cfg.G == g && cfg.VPT == v) {                                               \
+    auto kern = add_rms_bwd_kernel<T, g, v>;                                                   \
+    if (smem > 48 * 1024)                                                                      \
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    blocks = persistent_grid(kern, cfg.threads, smem, rows, groups, cap);                      \
+    kern<<<blocks, cfg.threads, smem, stream>>>((const T*)dy, (const T*)x, (const T*)r,        \
+                                                (const T*)w, rstd, (T*)dx, partial, rows,      \
+                                                (int)hidden);                                  \
+    launched = true;                                                                           \
+  }
+    EVG_X(32, 1) EVG_X(32, 2) EVG_X(32, 4) EVG_X(64, 4)
+#undef EVG_X
+  }
+  if (!launched && vec_ok && !tune("rows.force_generic") && !tune("norm_bwd.no_ring")) {
     const int64_t nvec = hidden / N;
     constexpr int kThreads = 256;
     const size_t row_bytes = (size_t)hidden * sizeof(T);

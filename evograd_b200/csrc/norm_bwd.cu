@@ -509,6 +509,29 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
 #undef EVG_RING
     }
   }
+  if (LN && narrow_rows && hidden / N <= 128 && !tune("rows.force_generic") &&
+      !tune("layernorm_bwd.group")) {
+    // LayerNorm keeps two column sums per element, so rows of up to 128 vectors use two
+    // vectors per thread (32 accumulators) rather than four: groups of 32 / 64 threads
+    // ([65536, 1024] bf16: 0.55 -> 0.65 of HBM peak; wider rows measured better as they were).
+    const int nv = (int)(hidden / N);
+    const int G = nv <= 64 ? 32 : 64;
+    const int threads = 256, groups = threads / G;
+    const size_t smem =
+        ((size_t)groups * 2 * NV * (G / 32) + (size_t)(NV + 1) * hidden) * sizeof(float);
+#define EVG_XN(g)                                                                              \
+  if (!launched && G == g) {                                                                   \
+    auto kern = norm_bwd_kernel<T, g, 2, LN>;                                                  \
+    if (smem > 48 * 1024)                                                                      \
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    blocks = persistent_grid(kern, threads, smem, rows, groups, cap);                          \
+    kern<<<blocks, threads, smem, stream>>>((const T*)dy, (const T*)x, (const T*)w, mean,      \
+                                            rstd, (T*)dx, partial, rows, (int)hidden);         \
+    launched = true;                                                                           \
+  }
+    EVG_XN(32) EVG_XN(64)
+#undef EVG_XN
+  }
   if (!launched && vec_ok && !tune("rows.force_generic") &&
       pick_rowcfg(op, hidden / N, cfg, narrow_rows ? 256 : 512, LN)) {
     const int groups = cfg.threads / cfg.G;
