@@ -116,8 +116,10 @@ softmax_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restr
   }
 }
 
-// Rows of any width (for example vocabulary-sized logits) or alignment: one
-// block per row, online max/sum in the first pass, y written in the second.
+// Rows of any width or alignment (rows too wide for registers that the cluster
+// kernels of softmax_wide.cu do not take either): one block per row, three
+// passes (maximum, sum of exponentials, output); passes two and three re-read
+// the row from L2.
 // VEC selects 128-bit accesses when the row width and pointers allow them.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(1024, 1)

@@ -561,8 +561,8 @@ def evoattention_bwd(do, q, k, v, res_mask, pair_bias, o, lse, scale: float | No
 
 
 def device_status(reset: bool = True) -> None:
-    """Synchronise and raise :class:`EvgError` (EVG_ETIMEOUT) if a bounded wait inside
-    an attention kernel gave up since the last reset."""
+    """Synchronise and raise :class:`EvgError` (EVG_ETIMEOUT) if a bounded device-side
+    wait (attention, norm backward rings, wide softmax) gave up since the last reset."""
     call("evg_device_status", 1 if reset else 0)
 
 

@@ -336,8 +336,9 @@ int evg_evoattention_bwd(const void* dout, const void* q, const void* k,
 
 /*
  * Synchronises the current device (the one exception to "nothing synchronises")
- * and reports the sticky device-side status of the attention kernels: every
- * wait inside them is bounded, and a wait that gives up records its identity,
+ * and reports the sticky device-side status of the kernels that wait on
+ * mbarriers (attention, the norm backward rings, wide softmax): every wait
+ * inside them is bounded, and a wait that gives up records its identity,
  * lets the kernel finish and is reported here as EVG_ETIMEOUT (results of that
  * launch are then undefined). reset != 0 clears the status after reading it.
  */
