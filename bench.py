@@ -201,9 +201,6 @@ class NormWL(Workload):
         if self.world > 1:
             from evograd_b200.sharded import ShardedNorm
 
-            # The all-reduce stays on the main stream: putting it on a side stream inside the
-            # captured graph (ShardedNorm(overlap_comm=True)) stopped making progress in a
-            # two-GPU run, so that combination is not offered here.
             self.sharded = ShardedNorm(self.kind, group)
         # fwd 1 kernel; bwd 2 (row kernel + column reduce); sharded adds the rounding kernel
         self.kernels_per_step = 3 + (1 if self.world > 1 else 0)
@@ -234,10 +231,6 @@ class NormWL(Workload):
         if self.sharded is not None:
             return list(self.sharded.backward_from_saved(s["dy"], saved))
         return list(self.bwd(s["dy"], saved))
-
-    def finish(self):
-        if self.sharded is not None:
-            self.sharded.finish()
 
     def pipeline_spec(self):
         if self.kind == "layernorm":
@@ -600,8 +593,7 @@ def measure_device(wl, steps, warmup, world, sections=True):
     def step(i):
         live[0] = wl.step(sets[i % n_sets], timer if (timer and i >= warmup) else None)
 
-    ms = time_steps(step, steps, warmup, barrier=_barrier_fn(world),
-                    finalize=getattr(wl, "finish", None))
+    ms = time_steps(step, steps, warmup, barrier=_barrier_fn(world))
     ms = _max_over_ranks(ms, world)
     totals = timer.totals_ms() if timer else {}
     del sets, live
@@ -646,8 +638,6 @@ def measure_graphs(wl, steps, warmup, world):
         with torch.cuda.graph(g):
             for i in range(steps):
                 body(i)  # results are dropped: the graph's pool reuses their memory
-            if hasattr(wl, "finish"):
-                wl.finish()  # join a side stream (overlapped all-reduce) before capture ends
         return g
 
     bodies = (lambda i: wl.step(sets[i % n]),
@@ -721,8 +711,6 @@ def measure_e2e(wl, steps, warmup, world):
             if torch.is_tensor(v):
                 dev_set[k].copy_(v, non_blocking=True)
         results = wl.step(dev_set)
-        if hasattr(wl, "finish"):
-            wl.finish()  # an overlapped all-reduce must land before its result is copied out
         for dst, src in zip(host_out, results):
             dst.copy_(src, non_blocking=True)
 

@@ -216,8 +216,9 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
     bulk_load_1d(dst + row_bytes, r + row * cols, row_bytes, &full[s]);
     bulk_load_1d(dst + 2 * row_bytes, dy + row * cols, row_bytes, &full[s]);
   };
+  long long n_issued = 0;  // thread 0 only
   if (tid == 0)
-    for (int64_t i = 0; i < stages && i < n_mine; ++i) issue(i);
+    for (int64_t i = 0; i < stages && i < n_mine; ++i, ++n_issued) issue(i);
 
   f32x2 acc_w[VPT][P];
 #pragma unroll
@@ -283,7 +284,10 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       c[0] = lo + hi;
     }
     block_allreduce_sum_fixed<1, THREADS / 32>(c, scratch, phase);  // all done with stage s
-    if (tid == 0 && i + stages < n_mine) issue(i + stages);
+    if (tid == 0 && i + stages < n_mine && !*(volatile int*)abort_flag) {  // no new copies after a timeout
+      issue(i + stages);
+      ++n_issued;
+    }
     const f32x2 a_s = f2_splat(-(rs * rs) * rs * (c[0] * inv_cols));
     const f32x2 rb2 = f2_splat(rb);
 #pragma unroll
@@ -316,6 +320,7 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       parity ^= 1;
     }
   }
+  if (tid == 0 && *(volatile int*)abort_flag) ring_drain(full, stages, n_issued, wait_limit);
   float* pw = partial + (size_t)blockIdx.x * cols;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {

@@ -1,30 +1,17 @@
-// Causal attention forward / backward on the sm_100a tensor cores.
+// Causal attention: the C entry points and what the tensor-core kernels share
+// on the host side (argument checks, TMA descriptor encoding).
 //
-// All three main kernels share one structure per 128x128 score tile:
-//   1. TMA brings 128-row tiles of Q/K/V/dO (head_dim contiguous, 128-byte
-//      swizzle) into shared memory, completion counted on mbarriers;
-//   2. one thread issues tcgen05.mma with both operands in shared memory to form
-//      the 128x128 float32 score tile(s) in tensor memory (TMEM);
-//   3. the block's threads read their TMEM lane (one score row each), apply the
-//      element-wise step (softmax / dS) and write the 16-bit result back to TMEM;
-//   4. one thread issues tcgen05.mma with that TMEM tile as the A operand and a
-//      shared-memory tile read "MN-major" (contraction along the tile's rows)
-//      as B, accumulating O / dQ / dK / dV in TMEM.
-// The S x S matrix is never materialised. Work decomposition is deterministic:
-// forward and the dQ kernel own a query tile, the dK/dV kernel owns a key tile.
-//
-// Tensor-core work per 128x128 tile, head_dim D (FLOPs = 2*128*128*D each):
-//   forward 2 products; dK/dV kernel 4; dQ kernel 3.
+// The kernels live in attention_fwd2.cu / attention_bwd2.cu (tcgen05 + TMEM,
+// head sizes 64 / 128, 16-bit inputs) and attention_generic.cu (CUDA cores,
+// float32 and other head sizes). Work decomposition is deterministic: forward
+// and the dQ kernel own a query tile, the dK/dV kernel owns a key tile.
+#include <cmath>
 #include <cstdio>
 #include <mutex>
 
 #include "attention_common.cuh"
 
 namespace evg {
-
-// Sticky device-side status shared by the attention kernels (0 = fine,
-// otherwise the identifying code of the first bounded wait that gave up).
-__device__ int g_attn_device_status = 0;
 
 namespace umma {
 
@@ -65,502 +52,18 @@ using namespace umma;
 using namespace attn;
 
 
-// ------------------------------------------------------------------ forward
-// grid = (query tiles, B*H), 128 threads, two blocks per SM so that one block's
-// softmax overlaps the other's tensor-core phases.
-// TMEM (256 columns): [0,128) S, reused as P (64 columns of packed 16-bit);
-//                     [128,128+HD) O.
-template <int HD, int FMT>
-__global__ void __launch_bounds__(128, 2)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                const __grid_constant__ CUtensorMap map_v, void* __restrict__ o_ptr,
-                float* __restrict__ lse_ptr, int S, float scale_log2, long long wait_limit) {
-  extern __shared__ uint8_t smem_raw[];
-  constexpr uint32_t TB = tile_bytes<HD>();
-  BlockSetup bs = carve(smem_raw, 3 * TB);
-  uint8_t* sQ = bs.smem;
-  uint8_t* sK = sQ + TB;
-  uint8_t* sV = sK + TB;
-  uint64_t* bar_q = bs.bars + 0;
-  uint64_t* bar_k = bs.bars + 1;
-  uint64_t* bar_v = bs.bars + 2;
-  uint64_t* bar_s = bs.bars + 3;
-  uint64_t* bar_o = bs.bars + 4;
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int qtile = gridDim.x - 1 - blockIdx.x;  // heaviest tiles first
-  const int bh = blockIdx.y;
-  const int q0 = qtile * kTile;
-  const int n_kv = qtile + 1;
-
-  if (tid == 0) {
-    *bs.abort_flag = 0;
-    mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
-    mbar_init(bar_s, 1); mbar_init(bar_o, 1);
-    fence_mbar_init();
-    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v);
-  }
-  __syncthreads();
-  if (warp == 0) { tmem_alloc(bs.tmem_slot, 256); tmem_relinquish(); }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = *bs.tmem_slot;
-  const WaitCtx ctx{bs.abort_flag, &g_attn_device_status, wait_limit};
-
-  constexpr uint32_t idesc_s = instr_desc_f16(FMT, 128, 128, 0, 0);
-  constexpr uint32_t idesc_o = instr_desc_f16(FMT, 128, HD, 0, 1);
-  const uint32_t tS = tmem, tP = tmem, tO = tmem + 128;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-
-  if (tid == 0) {
-    mbar_expect_tx(bar_q, TB); load_tile<HD>(sQ, &map_q, q0, bh, bar_q);
-    mbar_expect_tx(bar_k, TB); load_tile<HD>(sK, &map_k, 0, bh, bar_k);
-    mbar_expect_tx(bar_v, TB); load_tile<HD>(sV, &map_v, 0, bh, bar_v);
-  }
-
-  const int q_glob = q0 + tid;
-  float m_run = -INFINITY, l_run = 0.f;
-
-  for (int j = 0; j < n_kv; ++j) {
-    const uint32_t ph = j & 1;
-    if (tid == 0) {
-      if (j == 0) mbar_wait(bar_q, 0, ctx, 101);
-      mbar_wait(bar_k, ph, ctx, 102);
-      tc_fence_after_sync();
-      issue_scores<HD>(tS, smem_u32(sQ), smem_u32(sK), idesc_s);
-      mma_commit(bar_s);
-    }
-    mbar_wait(bar_s, ph, ctx, 103);
-    __syncwarp();
-    tc_fence_after_sync();
-    if (tid == 0 && j + 1 < n_kv) {  // K tile is free once the scores exist
-      mbar_expect_tx(bar_k, TB);
-      load_tile<HD>(sK, &map_k, (j + 1) * kTile, bh, bar_k);
-    }
-    __syncwarp();
-    // ---- this thread's score row
-    uint32_t sr[128];
-#pragma unroll
-    for (int c = 0; c < 4; ++c)
-      tmem_ld32(tS + lane_base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
-    tmem_wait_ld();
-    const bool diag = (j == qtile);
-    const int kv0 = j * kTile;
-    float mx = -INFINITY;
-#pragma unroll
-    for (int c = 0; c < 128; ++c) {
-      float t = __uint_as_float(sr[c]) * scale_log2;
-      if (diag && kv0 + c > q_glob) t = -INFINITY;
-      sr[c] = __float_as_uint(t);
-      mx = fmaxf(mx, t);
-    }
-    const bool grow = mx > m_run + kRescaleThreshold;  // always true on the first tile
-    const float m_new = grow ? mx : m_run;
-    if (j > 0 && __any_sync(0xffffffffu, grow)) {
-      // Rescale this warp's rows of O (rows that did not grow use alpha = 1).
-      const float alpha = grow ? exp2f(m_run - m_new) : 1.0f;
-      l_run *= alpha;
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t orow[32];
-        tmem_ld32(tO + lane_base + c * 32, orow);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
-        tmem_st32(tO + lane_base + c * 32, orow);
-      }
-    }
-    m_run = m_new;
-    float lsum = 0.f;
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t pr[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float p0 = exp2f(__uint_as_float(sr[c * 64 + 2 * i]) - m_run);
-        const float p1 = exp2f(__uint_as_float(sr[c * 64 + 2 * i + 1]) - m_run);
-        lsum += p0 + p1;
-        pr[i] = pack2<FMT>(p0, p1);
-      }
-      tmem_st32(tP + lane_base + c * 32, pr);
-    }
-    l_run += lsum;
-    tmem_wait_st();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-      mbar_wait(bar_v, ph, ctx, 104);
-      issue_accumulate(tO, tP, smem_u32(sV), idesc_o, j > 0);
-      mma_commit(bar_o);
-      // P (aliasing S) and the V tile are busy until these MMAs finish.
-      mbar_wait(bar_o, ph, ctx, 105);
-      if (j + 1 < n_kv) {
-        mbar_expect_tx(bar_v, TB);
-        load_tile<HD>(sV, &map_v, (j + 1) * kTile, bh, bar_v);
-      }
-    }
-  }
-  // ---- epilogue: O / l, log-sum-exp
-  mbar_wait(bar_o, (n_kv - 1) & 1, ctx, 106);
-  __syncwarp();
-  tc_fence_after_sync();
-  const float inv_l = 1.0f / l_run;
-  const bool row_ok = q_glob < S;
-  uint8_t* orow_g = reinterpret_cast<uint8_t*>(o_ptr) + ((size_t)bh * S + (row_ok ? q_glob : 0)) * HD * 2;
-#pragma unroll
-  for (int c = 0; c < HD / 32; ++c) {
-    uint32_t orow[32];
-    tmem_ld32(tO + lane_base + c * 32, orow);
-    tmem_wait_ld();
-    if (row_ok) {
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint4 pk;
-        pk.x = pack2<FMT>(__uint_as_float(orow[8 * v + 0]) * inv_l, __uint_as_float(orow[8 * v + 1]) * inv_l);
-        pk.y = pack2<FMT>(__uint_as_float(orow[8 * v + 2]) * inv_l, __uint_as_float(orow[8 * v + 3]) * inv_l);
-        pk.z = pack2<FMT>(__uint_as_float(orow[8 * v + 4]) * inv_l, __uint_as_float(orow[8 * v + 5]) * inv_l);
-        pk.w = pack2<FMT>(__uint_as_float(orow[8 * v + 6]) * inv_l, __uint_as_float(orow[8 * v + 7]) * inv_l);
-        *reinterpret_cast<uint4*>(orow_g + (c * 32 + v * 8) * 2) = pk;
-      }
-    }
-  }
-  if (row_ok) lse_ptr[(size_t)bh * S + q_glob] = (m_run + log2f(l_run)) * kLn2;
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 256);
+// The kernels take the row maximum on raw scores and scale afterwards, which is
+// only the same thing for a positive, finite scale.
+int check_scale(const char* what, float scale) {
+  if (!(scale > 0.f) || !std::isfinite(scale))
+    return fail(EVG_EUNSUPPORTED, "%s: scale %g (must be positive and finite)", what,
+                (double)scale);
+  return EVG_OK;
 }
 
-// ----------------------------------------------------------- backward: delta
-// delta[row] = sum_d dO[row,d] * O[row,d]; HD/8 threads per row.
-template <int HD, int FMT>
-__global__ void __launch_bounds__(256)
-attn_delta_kernel(const void* __restrict__ do_ptr, const void* __restrict__ o_ptr,
-                  float* __restrict__ delta, int64_t rows) {
-  constexpr int TPR = HD / 8;
-  const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / TPR;
-  const int part = threadIdx.x % TPR;
-  float s = 0.f;
-  if (row < rows) {
-    const uint4 a = ld_vec(reinterpret_cast<const uint8_t*>(do_ptr) + (row * HD + part * 8) * 2);
-    const uint4 b = ld_vec(reinterpret_cast<const uint8_t*>(o_ptr) + (row * HD + part * 8) * 2);
-    float af[8], bf[8];
-    if constexpr (FMT == 1) { unpack<__nv_bfloat16>(a, af); unpack<__nv_bfloat16>(b, bf); }
-    else { unpack<__half>(a, af); unpack<__half>(b, bf); }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s += af[i] * bf[i];
-  }
-#pragma unroll
-  for (int off = TPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (row < rows && part == 0) delta[row] = s;
-}
-
-// Shared by the two backward kernels: store a [128 x HD] float32 TMEM
-// accumulator, scaled, as 16-bit rows of a [B*H, S, HD] tensor. 256 threads:
-// warp w owns TMEM lanes 32*(w%4).. and column half w/4.
-template <int HD, int FMT>
-__device__ __forceinline__ void store_accumulator(uint32_t t_acc, void* out, int bh, int row0,
-                                                  int S, float scale, int warp, int lane) {
-  const int r = (warp & 3) * 32 + lane;
-  const int half = warp >> 2;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  const int row = row0 + r;
-  const bool ok = row < S;
-  uint8_t* dst = reinterpret_cast<uint8_t*>(out) + ((size_t)bh * S + (ok ? row : 0)) * HD * 2;
-#pragma unroll
-  for (int c = 0; c < HD / 64; ++c) {
-    const int col = half * (HD / 2) + c * 32;
-    uint32_t acc[32];
-    tmem_ld32(t_acc + lane_base + col, acc);
-    tmem_wait_ld();
-    if (ok) {
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint4 pk;
-        pk.x = pack2<FMT>(__uint_as_float(acc[8 * v + 0]) * scale, __uint_as_float(acc[8 * v + 1]) * scale);
-        pk.y = pack2<FMT>(__uint_as_float(acc[8 * v + 2]) * scale, __uint_as_float(acc[8 * v + 3]) * scale);
-        pk.z = pack2<FMT>(__uint_as_float(acc[8 * v + 4]) * scale, __uint_as_float(acc[8 * v + 5]) * scale);
-        pk.w = pack2<FMT>(__uint_as_float(acc[8 * v + 6]) * scale, __uint_as_float(acc[8 * v + 7]) * scale);
-        *reinterpret_cast<uint4*>(dst + (col + v * 8) * 2) = pk;
-      }
-    }
-  }
-}
-
-// ---------------------------------------------------------- backward: dK, dV
-// grid = (key tiles, B*H), 256 threads, one block per SM (TMEM: all 512 columns).
-// The block owns key tile `kvt` and walks query tiles i >= kvt:
-//   S^T = K Q_i^T, dP^T = V dO_i^T              (lanes = keys, columns = queries)
-//   P^T = exp2(S^T*c - lse_i), dS^T = P^T*(dP^T - delta_i)
-//   dV += P^T dO_i, dK += dS^T Q_i              (A from TMEM, B MN-major)
-// TMEM: [0,128) S^T -> P^T; [128,256) dP^T -> dS^T; [256,256+HD) dV; [384,384+HD) dK.
-template <int HD, int FMT>
-__global__ void __launch_bounds__(256, 1)
-attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                     const float* __restrict__ lse_ptr, const float* __restrict__ delta_ptr,
-                     void* __restrict__ dk_ptr, void* __restrict__ dv_ptr, int S, float scale,
-                     long long wait_limit) {
-  extern __shared__ uint8_t smem_raw[];
-  constexpr uint32_t TB = tile_bytes<HD>();
-  BlockSetup bs = carve(smem_raw, 6 * TB + 1024);
-  uint8_t* sK = bs.smem;
-  uint8_t* sV = sK + TB;
-  uint8_t* sQ[2] = {sV + TB, sV + 2 * TB};
-  uint8_t* sDO[2] = {sV + 3 * TB, sV + 4 * TB};
-  float* s_lse = reinterpret_cast<float*>(sV + 5 * TB);  // [128] scaled to log2 units
-  float* s_delta = s_lse + 128;
-  uint64_t* bar_kv = bs.bars + 0;
-  uint64_t* bar_q[2] = {bs.bars + 1, bs.bars + 2};
-  uint64_t* bar_1 = bs.bars + 3;  // S^T and dP^T ready
-  uint64_t* bar_2 = bs.bars + 4;  // dV and dK accumulated
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kvt = blockIdx.x;  // key tile 0 has the most query tiles: heaviest first
-  const int bh = blockIdx.y;
-  const int kv0 = kvt * kTile;
-  const int n_q = (S + kTile - 1) / kTile;
-  const int n_it = n_q - kvt;
-  const float scale_log2 = scale * kLog2e;
-
-  if (tid == 0) {
-    *bs.abort_flag = 0;
-    mbar_init(bar_kv, 1); mbar_init(bar_q[0], 1); mbar_init(bar_q[1], 1);
-    mbar_init(bar_1, 1); mbar_init(bar_2, 1);
-    fence_mbar_init();
-    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k);
-    prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
-  }
-  __syncthreads();
-  if (warp == 0) { tmem_alloc(bs.tmem_slot, 512); tmem_relinquish(); }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = *bs.tmem_slot;
-  const WaitCtx ctx{bs.abort_flag, &g_attn_device_status, wait_limit};
-  constexpr uint32_t idesc_s = instr_desc_f16(FMT, 128, 128, 0, 0);
-  constexpr uint32_t idesc_d = instr_desc_f16(FMT, 128, HD, 0, 1);
-  const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 384;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  const int half = warp >> 2;               // which 64 query columns this warp handles
-  const int r = (warp & 3) * 32 + lane;     // key row inside the tile
-  const int kv_glob = kv0 + r;
-
-  if (tid == 0) {
-    mbar_expect_tx(bar_kv, 2 * TB);
-    load_tile<HD>(sK, &map_k, kv0, bh, bar_kv);
-    load_tile<HD>(sV, &map_v, kv0, bh, bar_kv);
-    for (int s = 0; s < 2 && s < n_it; ++s) {
-      mbar_expect_tx(bar_q[s], 2 * TB);
-      load_tile<HD>(sQ[s], &map_q, (kvt + s) * kTile, bh, bar_q[s]);
-      load_tile<HD>(sDO[s], &map_do, (kvt + s) * kTile, bh, bar_q[s]);
-    }
-  }
-
-  for (int it = 0; it < n_it; ++it) {
-    const int st = it & 1;
-    const uint32_t ph_stage = (it >> 1) & 1, ph = it & 1;
-    const int q0 = (kvt + it) * kTile;
-    if (tid == 0) {
-      if (it == 0) mbar_wait(bar_kv, 0, ctx, 201);
-      mbar_wait(bar_q[st], ph_stage, ctx, 202);
-      tc_fence_after_sync();
-      issue_scores<HD>(tS, smem_u32(sK), smem_u32(sQ[st]), idesc_s);
-      issue_scores<HD>(tDP, smem_u32(sV), smem_u32(sDO[st]), idesc_s);
-      mma_commit(bar_1);
-    }
-    if (tid < 128) {
-      const int q = q0 + tid;
-      s_lse[tid] = q < S ? lse_ptr[(size_t)bh * S + q] * kLog2e : INFINITY;
-      s_delta[tid] = q < S ? delta_ptr[(size_t)bh * S + q] : 0.f;
-    }
-    mbar_wait(bar_1, ph, ctx, 203);
-    __syncwarp();
-    tc_fence_after_sync();
-    uint32_t sr[64], dr[64];
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      tmem_ld32(tS + lane_base + half * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
-      tmem_ld32(tDP + lane_base + half * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&dr[c * 32]));
-    }
-    tmem_wait_ld();
-    tc_fence_before_sync();
-    __syncthreads();  // every warp has read its scores; s_lse/s_delta are visible
-    const bool diag = (it == 0);
-    uint32_t pp[32], dd[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      float p[2], d[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int c = half * 64 + 2 * i + e;  // query column inside the tile
-        float pe = exp2f(__uint_as_float(sr[2 * i + e]) * scale_log2 - s_lse[c]);
-        if (diag && q0 + c < kv_glob) pe = 0.f;
-        p[e] = pe;
-        d[e] = pe * (__uint_as_float(dr[2 * i + e]) - s_delta[c]);
-      }
-      pp[i] = pack2<FMT>(p[0], p[1]);
-      dd[i] = pack2<FMT>(d[0], d[1]);
-    }
-    tmem_st32(tS + lane_base + half * 32, pp);
-    tmem_st32(tDP + lane_base + half * 32, dd);
-    tmem_wait_st();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-      issue_accumulate(tDV, tS, smem_u32(sDO[st]), idesc_d, it > 0);
-      issue_accumulate(tDK, tDP, smem_u32(sQ[st]), idesc_d, it > 0);
-      mma_commit(bar_2);
-    }
-    mbar_wait(bar_2, ph, ctx, 204);
-    tc_fence_after_sync();
-    if (tid == 0 && it + 2 < n_it) {
-      mbar_expect_tx(bar_q[st], 2 * TB);
-      load_tile<HD>(sQ[st], &map_q, (kvt + it + 2) * kTile, bh, bar_q[st]);
-      load_tile<HD>(sDO[st], &map_do, (kvt + it + 2) * kTile, bh, bar_q[st]);
-    }
-  }
-  __syncwarp();
-  store_accumulator<HD, FMT>(tDV, dv_ptr, bh, kv0, S, 1.0f, warp, lane);
-  store_accumulator<HD, FMT>(tDK, dk_ptr, bh, kv0, S, scale, warp, lane);
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
-}
-
-// --------------------------------------------------------------- backward: dQ
-// grid = (query tiles, B*H), 256 threads, one block per SM.
-//   S = Q K_j^T, dP = dO V_j^T; dS = exp2(S*c - lse)*(dP - delta); dQ += dS K_j
-// TMEM: [0,128) S -> dS; [128,256) dP; [256,256+HD) dQ.
-template <int HD, int FMT>
-__global__ void __launch_bounds__(256, 1)
-attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                   const float* __restrict__ lse_ptr, const float* __restrict__ delta_ptr,
-                   void* __restrict__ dq_ptr, int S, float scale, long long wait_limit) {
-  extern __shared__ uint8_t smem_raw[];
-  constexpr uint32_t TB = tile_bytes<HD>();
-  BlockSetup bs = carve(smem_raw, 6 * TB);
-  uint8_t* sQ = bs.smem;
-  uint8_t* sDO = sQ + TB;
-  uint8_t* sK[2] = {sDO + TB, sDO + 2 * TB};
-  uint8_t* sV[2] = {sDO + 3 * TB, sDO + 4 * TB};
-  uint64_t* bar_qdo = bs.bars + 0;
-  uint64_t* bar_kv[2] = {bs.bars + 1, bs.bars + 2};
-  uint64_t* bar_1 = bs.bars + 3;
-  uint64_t* bar_2 = bs.bars + 4;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qtile = gridDim.x - 1 - blockIdx.x;
-  const int bh = blockIdx.y;
-  const int q0 = qtile * kTile;
-  const int n_it = qtile + 1;
-  const float scale_log2 = scale * kLog2e;
-
-  if (tid == 0) {
-    *bs.abort_flag = 0;
-    mbar_init(bar_qdo, 1); mbar_init(bar_kv[0], 1); mbar_init(bar_kv[1], 1);
-    mbar_init(bar_1, 1); mbar_init(bar_2, 1);
-    fence_mbar_init();
-    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k);
-    prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
-  }
-  __syncthreads();
-  if (warp == 0) { tmem_alloc(bs.tmem_slot, 512); tmem_relinquish(); }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = *bs.tmem_slot;
-  const WaitCtx ctx{bs.abort_flag, &g_attn_device_status, wait_limit};
-  constexpr uint32_t idesc_s = instr_desc_f16(FMT, 128, 128, 0, 0);
-  constexpr uint32_t idesc_d = instr_desc_f16(FMT, 128, HD, 0, 1);
-  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  const int half = warp >> 2;            // which 64 key columns this warp handles
-  const int r = (warp & 3) * 32 + lane;  // query row inside the tile
-  const int q_glob = q0 + r;
-  const float lse2 = q_glob < S ? lse_ptr[(size_t)bh * S + q_glob] * kLog2e : INFINITY;
-  const float delta = q_glob < S ? delta_ptr[(size_t)bh * S + q_glob] : 0.f;
-
-  if (tid == 0) {
-    mbar_expect_tx(bar_qdo, 2 * TB);
-    load_tile<HD>(sQ, &map_q, q0, bh, bar_qdo);
-    load_tile<HD>(sDO, &map_do, q0, bh, bar_qdo);
-    for (int s = 0; s < 2 && s < n_it; ++s) {
-      mbar_expect_tx(bar_kv[s], 2 * TB);
-      load_tile<HD>(sK[s], &map_k, s * kTile, bh, bar_kv[s]);
-      load_tile<HD>(sV[s], &map_v, s * kTile, bh, bar_kv[s]);
-    }
-  }
-
-  for (int it = 0; it < n_it; ++it) {
-    const int st = it & 1;
-    const uint32_t ph_stage = (it >> 1) & 1, ph = it & 1;
-    const int kv0 = it * kTile;
-    if (tid == 0) {
-      if (it == 0) mbar_wait(bar_qdo, 0, ctx, 301);
-      mbar_wait(bar_kv[st], ph_stage, ctx, 302);
-      tc_fence_after_sync();
-      issue_scores<HD>(tS, smem_u32(sQ), smem_u32(sK[st]), idesc_s);
-      issue_scores<HD>(tDP, smem_u32(sDO), smem_u32(sV[st]), idesc_s);
-      mma_commit(bar_1);
-    }
-    mbar_wait(bar_1, ph, ctx, 303);
-    __syncwarp();
-    tc_fence_after_sync();
-    uint32_t sr[64], dr[64];
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      tmem_ld32(tS + lane_base + half * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
-      tmem_ld32(tDP + lane_base + half * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&dr[c * 32]));
-    }
-    tmem_wait_ld();
-    tc_fence_before_sync();
-    __syncthreads();  // all score reads done before dS overwrites the S columns
-    const bool diag = (it == qtile);
-    uint32_t dd[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      float d[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int c = half * 64 + 2 * i + e;  // key column inside the tile
-        float pe = exp2f(__uint_as_float(sr[2 * i + e]) * scale_log2 - lse2);
-        if (diag && kv0 + c > q_glob) pe = 0.f;
-        d[e] = pe * (__uint_as_float(dr[2 * i + e]) - delta);
-      }
-      dd[i] = pack2<FMT>(d[0], d[1]);
-    }
-    tmem_st32(tS + lane_base + half * 32, dd);
-    tmem_wait_st();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-      issue_accumulate(tDQ, tS, smem_u32(sK[st]), idesc_d, it > 0);
-      mma_commit(bar_2);
-    }
-    mbar_wait(bar_2, ph, ctx, 304);
-    tc_fence_after_sync();
-    if (tid == 0 && it + 2 < n_it) {
-      mbar_expect_tx(bar_kv[st], 2 * TB);
-      load_tile<HD>(sK[st], &map_k, (it + 2) * kTile, bh, bar_kv[st]);
-      load_tile<HD>(sV[st], &map_v, (it + 2) * kTile, bh, bar_kv[st]);
-    }
-  }
-  __syncwarp();
-  store_accumulator<HD, FMT>(tDQ, dq_ptr, bh, q0, S, scale, warp, lane);
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
-}
-
-// ---------------------------------------------------------------- host side
-long long wait_limit_cycles() {
-  const int t = tune("attention.wait_limit");  // in millions of cycles
-  return t > 0 ? (long long)t * 1000000ll : 2000000000ll;  // ~1 s at 2 GHz
-}
-
-int check_attention_args(const char* what, int64_t B, int64_t H, int64_t S, int64_t D, int dtype) {
+int check_attention_args(const char* what, int64_t B, int64_t H, int64_t S, int64_t D, int dtype,
+                         float scale) {
+  if (int rc = check_scale(what, scale)) return rc;
   if (B <= 0 || H <= 0 || S <= 0)
     return fail(EVG_EBADSHAPE, "%s: B=%lld H=%lld S=%lld must be positive", what, (long long)B,
                 (long long)H, (long long)S);
@@ -574,85 +77,6 @@ int check_attention_args(const char* what, int64_t B, int64_t H, int64_t S, int6
   return EVG_OK;
 }
 
-template <typename Kernel>
-int set_smem(Kernel kernel, size_t bytes) {
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) !=
-      cudaSuccess) {
-    cudaGetLastError();
-    return fail(EVG_ELAUNCH, "attention: cannot reserve %zu bytes of shared memory", bytes);
-  }
-  return EVG_OK;
-}
-
-template <int HD, int FMT>
-int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int64_t B,
-               int64_t H, int64_t S, float scale, cudaStream_t stream) {
-  CUtensorMap mq, mk, mv;
-  if (!encode_tile_map_16bit(&mq, q, FMT, HD, S, B * H, kTile) ||
-      !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * H, kTile) ||
-      !encode_tile_map_16bit(&mv, v, FMT, HD, S, B * H, kTile))
-    return fail(EVG_ELAUNCH, "causal_attention_fwd: cuTensorMapEncodeTiled failed");
-  const size_t smem = 3 * tile_bytes<HD>() + kControlBytes + 1024;
-  auto kern = attn_fwd_kernel<HD, FMT>;
-  if (int rc = set_smem(kern, smem)) return rc;
-  dim3 grid((unsigned)((S + kTile - 1) / kTile), (unsigned)(B * H));
-  kern<<<grid, 128, smem, stream>>>(mq, mk, mv, o, lse, (int)S, scale * kLog2e,
-                                    wait_limit_cycles());
-  return check_launch("causal_attention_fwd");
-}
-
-template <int HD, int FMT>
-int launch_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
-               const float* lse, void* dq, void* dk, void* dv, float* delta, int64_t B, int64_t H,
-               int64_t S, float scale, cudaStream_t stream) {
-  CUtensorMap mq, mk, mv, mdo;
-  if (!encode_tile_map_16bit(&mq, q, FMT, HD, S, B * H, kTile) ||
-      !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * H, kTile) ||
-      !encode_tile_map_16bit(&mv, v, FMT, HD, S, B * H, kTile) ||
-      !encode_tile_map_16bit(&mdo, dout, FMT, HD, S, B * H, kTile))
-    return fail(EVG_ELAUNCH, "causal_attention_bwd: cuTensorMapEncodeTiled failed");
-  const int64_t rows = B * H * S;
-  {
-    constexpr int TPR = HD / 8;
-    const int64_t threads = rows * TPR;
-    attn_delta_kernel<HD, FMT><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(dout, o, delta,
-                                                                                     rows);
-    if (int rc = check_launch("causal_attention_bwd delta")) return rc;
-  }
-  dim3 grid((unsigned)((S + kTile - 1) / kTile), (unsigned)(B * H));
-  {
-    const size_t smem = 6 * tile_bytes<HD>() + 1024 + kControlBytes + 1024;
-    auto kern = attn_bwd_dkdv_kernel<HD, FMT>;
-    if (int rc = set_smem(kern, smem)) return rc;
-    kern<<<grid, 256, smem, stream>>>(mq, mk, mv, mdo, lse, delta, dk, dv, (int)S, scale,
-                                      wait_limit_cycles());
-    if (int rc = check_launch("causal_attention_bwd dkdv")) return rc;
-  }
-  {
-    const size_t smem = 6 * tile_bytes<HD>() + kControlBytes + 1024;
-    auto kern = attn_bwd_dq_kernel<HD, FMT>;
-    if (int rc = set_smem(kern, smem)) return rc;
-    kern<<<grid, 256, smem, stream>>>(mq, mk, mv, mdo, lse, delta, dq, (int)S, scale,
-                                      wait_limit_cycles());
-    if (int rc = check_launch("causal_attention_bwd dq")) return rc;
-  }
-  return EVG_OK;
-}
-
-int read_attention_status(int reset) {
-  int code = 0;
-  if (cudaMemcpyFromSymbol(&code, g_attn_device_status, sizeof(int)) != cudaSuccess) {
-    cudaGetLastError();
-    return -1;
-  }
-  if (reset && code != 0) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_attn_device_status, &zero, sizeof(int));
-  }
-  return code;
-}
-const bool g_attention_status_registered = (register_device_status(read_attention_status), true);
-
 }  // namespace
 }  // namespace evg
 
@@ -662,26 +86,19 @@ extern "C" int evg_causal_attention_fwd(const void* q, const void* k, const void
                                         float* lse, int64_t B, int64_t H, int64_t S, int64_t D,
                                         float scale, int dtype, void* stream) {
   if (!q || !k || !v || !o || !lse) return fail(EVG_ENULL, "causal_attention_fwd: null pointer argument");
-  if (int rc = check_attention_args("causal_attention_fwd", B, H, S, D, dtype)) return rc;
+  if (int rc = check_attention_args("causal_attention_fwd", B, H, S, D, dtype, scale)) return rc;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
     return fail(EVG_EALIGN, "causal_attention_fwd: q/k/v/o must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
-  if (tune("attention.variant") != 1)  // default: two query tiles per block, warp-specialised
-    return attn::launch_fwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, q, k, v, o, lse, B, H, H, S,
-                                 scale, st);
-  if (D == 128) {
-    return dtype == EVG_BF16 ? launch_fwd<128, 1>(q, k, v, o, lse, B, H, S, scale, st)
-                             : launch_fwd<128, 0>(q, k, v, o, lse, B, H, S, scale, st);
-  }
-  return dtype == EVG_BF16 ? launch_fwd<64, 1>(q, k, v, o, lse, B, H, S, scale, st)
-                           : launch_fwd<64, 0>(q, k, v, o, lse, B, H, S, scale, st);
+  return attn::launch_fwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, q, k, v, o, lse, B, H, H, S,
+                               scale, st);
 }
 
 extern "C" int64_t evg_causal_attention_bwd_workspace_bytes(int64_t B, int64_t H, int64_t S,
                                                             int64_t D, int dtype) {
   (void)D; (void)dtype;
   if (B <= 0 || H <= 0 || S <= 0) return 0;
-  return attn::bwd2_workspace_bytes(B, H, S);  // covers the first version's B*H*S floats too
+  return attn::bwd2_workspace_bytes(B, H, S);
 }
 
 extern "C" int evg_causal_attention_bwd(const void* dout, const void* q, const void* k,
@@ -691,7 +108,7 @@ extern "C" int evg_causal_attention_bwd(const void* dout, const void* q, const v
                                         int64_t D, float scale, int dtype, void* stream) {
   if (!dout || !q || !k || !v || !o || !lse || !dq || !dk || !dv)
     return fail(EVG_ENULL, "causal_attention_bwd: null pointer argument");
-  if (int rc = check_attention_args("causal_attention_bwd", B, H, S, D, dtype)) return rc;
+  if (int rc = check_attention_args("causal_attention_bwd", B, H, S, D, dtype, scale)) return rc;
   const int64_t need = evg_causal_attention_bwd_workspace_bytes(B, H, S, D, dtype);
   if (!workspace || workspace_bytes < need)
     return fail(EVG_EWORKSPACE, "causal_attention_bwd: workspace %lld bytes, need %lld",
@@ -699,18 +116,8 @@ extern "C" int evg_causal_attention_bwd(const void* dout, const void* q, const v
   for (const void* p : {dout, q, k, v, o, (const void*)dq, (const void*)dk, (const void*)dv, (const void*)workspace})
     if (!aligned16(p)) return fail(EVG_EALIGN, "causal_attention_bwd: tensors must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
-  float* delta = (float*)workspace;
-  if (tune("attention.variant") != 1)  // default: warp-specialised, pipelined kernels
-    return attn::launch_bwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, dout, q, k, v, o, lse, dq, dk,
-                                 dv, delta, B, H, H, S, scale, st);
-  if (D == 128) {
-    return dtype == EVG_BF16
-               ? launch_bwd<128, 1>(dout, q, k, v, o, lse, dq, dk, dv, delta, B, H, S, scale, st)
-               : launch_bwd<128, 0>(dout, q, k, v, o, lse, dq, dk, dv, delta, B, H, S, scale, st);
-  }
-  return dtype == EVG_BF16
-             ? launch_bwd<64, 1>(dout, q, k, v, o, lse, dq, dk, dv, delta, B, H, S, scale, st)
-             : launch_bwd<64, 0>(dout, q, k, v, o, lse, dq, dk, dv, delta, B, H, S, scale, st);
+  return attn::launch_bwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, dout, q, k, v, o, lse, dq, dk,
+                               dv, (float*)workspace, B, H, H, S, scale, st);
 }
 
 
@@ -720,7 +127,8 @@ bool tensor_core_shape(int64_t D, int dtype) {
   return (D == 64 || D == 128) && (dtype == EVG_BF16 || dtype == EVG_F16);
 }
 int check_gqa_args(const char* what, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
-                   int dtype) {
+                   int dtype, float scale) {
+  if (int rc = check_scale(what, scale)) return rc;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || D <= 0)
     return fail(EVG_EBADSHAPE, "%s: B=%lld Hq=%lld Hkv=%lld S=%lld D=%lld must be positive", what,
                 (long long)B, (long long)Hq, (long long)Hkv, (long long)S, (long long)D);
@@ -743,7 +151,7 @@ extern "C" int evg_causal_gqa_attention_fwd(const void* q, const void* k, const 
                                             void* stream) {
   if (!q || !k || !v || !o || !lse)
     return fail(EVG_ENULL, "causal_gqa_attention_fwd: null pointer argument");
-  if (int rc = check_gqa_args("causal_gqa_attention_fwd", B, Hq, Hkv, S, D, dtype)) return rc;
+  if (int rc = check_gqa_args("causal_gqa_attention_fwd", B, Hq, Hkv, S, D, dtype, scale)) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if (tensor_core_shape(D, dtype) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o))
     return attn::launch_fwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, q, k, v, o, lse, B, Hq, Hkv, S,
@@ -769,7 +177,7 @@ extern "C" int evg_causal_gqa_attention_bwd(const void* dout, const void* q, con
                                             int dtype, void* stream) {
   if (!dout || !q || !k || !v || !o || !lse || !dq || !dk || !dv)
     return fail(EVG_ENULL, "causal_gqa_attention_bwd: null pointer argument");
-  if (int rc = check_gqa_args("causal_gqa_attention_bwd", B, Hq, Hkv, S, D, dtype)) return rc;
+  if (int rc = check_gqa_args("causal_gqa_attention_bwd", B, Hq, Hkv, S, D, dtype, scale)) return rc;
   const int64_t need = evg_causal_gqa_attention_bwd_workspace_bytes(B, Hq, Hkv, S, D, dtype);
   if (!workspace || workspace_bytes < need)
     return fail(EVG_EWORKSPACE, "causal_gqa_attention_bwd: workspace %lld bytes, need %lld",

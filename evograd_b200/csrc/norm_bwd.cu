@@ -224,8 +224,9 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
     bulk_load_1d(dst, x + row * cols, row_bytes, &full[s]);
     bulk_load_1d(dst + row_bytes, dy + row * cols, row_bytes, &full[s]);
   };
+  long long n_issued = 0;  // thread 0 only
   if (tid == 0)
-    for (int64_t i = 0; i < stages && i < n_mine; ++i) issue(i);
+    for (int64_t i = 0; i < stages && i < n_mine; ++i, ++n_issued) issue(i);
 
   // Element-wise float32 work is done on packed pairs (f32x2): element 2p and
   // 2p+1 of a vector share one instruction.
@@ -313,7 +314,10 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
       }
     }
     block_allreduce_sum_fixed<NV, THREADS / 32>(c, scratch, phase);  // all done with stage s
-    if (tid == 0 && i + stages < n_mine) issue(i + stages);
+    if (tid == 0 && i + stages < n_mine && !*(volatile int*)abort_flag) {  // no new copies after a timeout
+      issue(i + stages);
+      ++n_issued;
+    }
     // dx = rs*g - rs*mean(g) - rs*mean(g*xh)*xh
     const f32x2 a_x = f2_splat(-rs * (c[0] * inv_cols));
     const f32x2 a_0 = f2_splat(LN ? -rs * (c[1] * inv_cols) : 0.f);
@@ -345,6 +349,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
       parity ^= 1;
     }
   }
+  if (tid == 0 && *(volatile int*)abort_flag) ring_drain(full, stages, n_issued, wait_limit);
   // One group per block: the partial row goes out straight from registers.
   float* pw = partial + (size_t)blockIdx.x * cols;
   float* pb = partial + ((size_t)gridDim.x + blockIdx.x) * cols;

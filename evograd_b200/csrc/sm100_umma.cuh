@@ -83,6 +83,25 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const 
   }
 }
 
+// After an abort the producer stops issuing copies; the ones already issued
+// still write into this block's shared memory, which the next block resident on
+// the SM may reuse. The issuing thread therefore lets them land (a bounded wait
+// that ignores the abort word and records nothing) before the block returns.
+__device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity, long long limit_cycles) {
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity))
+    if (clock64() - start > limit_cycles) return;
+}
+// Drains the last `stages` issues of a ring whose issue number i uses barrier
+// full[i % stages] with parity (i / stages) & 1.
+__device__ __forceinline__ void ring_drain(uint64_t* full, int stages, long long n_issued,
+                                           long long limit_cycles) {
+  long long i = n_issued - stages;
+  if (i < 0) i = 0;
+  for (; i < n_issued; ++i)
+    mbar_drain(&full[i % stages], (uint32_t)((i / stages) & 1), limit_cycles);
+}
+
 // TMA: global -> shared tile load, completion counted on an mbarrier.
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int c0, int c1,
                                             int c2, uint64_t* bar) {

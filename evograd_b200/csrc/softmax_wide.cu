@@ -90,8 +90,9 @@ softmax_wide_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restr
                          off, n, &sm->full[s]);
     }
   };
+  long long n_issued = 0;  // thread 0 only
   if (tid == 0)
-    for (int64_t i = 0; i < stages && i < n_mine; ++i) issue(i);
+    for (int64_t i = 0; i < stages && i < n_mine; ++i, ++n_issued) issue(i);
 
   int s = 0;
   uint32_t parity = 0;
@@ -164,12 +165,17 @@ softmax_wide_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restr
       }
     }
     __syncthreads();  // every thread has finished reading stage s
-    if (tid == 0 && i + stages < n_mine) issue(i + stages);
+    if (tid == 0 && i + stages < n_mine && !*(volatile int*)&sm->abort_flag) {
+      issue(i + stages);  // no new copies after a timeout
+      ++n_issued;
+    }
     if (++s == stages) {
       s = 0;
       parity ^= 1;
     }
   }
+  if (tid == 0 && my_nvec > 0 && *(volatile int*)&sm->abort_flag)
+    ring_drain(sm->full, stages, n_issued, wait_limit);
   // No block may leave while a peer can still write into its slots: the last
   // write to this block happens before the last cluster barrier it passed.
 }

@@ -71,21 +71,13 @@ class ShardedNorm:
     "fused_add_rms_norm" (whose forward also takes ``residual`` and whose backward
     returns ``(dx, dr, dweight)`` with ``dr is dx``)."""
 
-    def __init__(self, kind: str, group=None, kernels: NormKernels | None = None,
-                 overlap_comm: bool = False):
-        """``overlap_comm`` (CUDA only) issues the all-reduce and the rounding on a
-        side stream, so the next kernels on the caller's stream (for example the
-        next step's forward) run while the 16-32 KB exchange is in flight. The
-        returned parameter gradients are then only valid after :meth:`finish`."""
+    def __init__(self, kind: str, group=None, kernels: NormKernels | None = None):
         if kind not in ("layernorm", "rmsnorm", "fused_add_rms_norm"):
             raise ValueError(f"kind must be layernorm, rmsnorm or fused_add_rms_norm, got {kind!r}")
         self.kind = kind
         self.group = group
         self.k = kernels or NormKernels.cuda()
         self.collectives = 0  # all_reduce calls issued so far
-        self.overlap_comm = overlap_comm
-        self._comm_stream = None
-        self._pending = None
 
     def forward_with_saved(self, x_shard, weight, bias=None, eps: float = 1e-5, residual=None):
         if self.kind == "fused_add_rms_norm":
@@ -116,39 +108,15 @@ class ShardedNorm:
             dx, partial = self.k.rmsnorm_bwd(dy_shard, x, weight, rstd, partials_f32=True)
         if partial.dtype != torch.float32:
             raise TypeError("local backward must return float32 partial sums")
-        if world > 1 and self.overlap_comm and partial.is_cuda:
-            if self._comm_stream is None:
-                self._comm_stream = torch.cuda.Stream(device=partial.device)
-            main = torch.cuda.current_stream(partial.device)
-            self._comm_stream.wait_stream(main)
-            with torch.cuda.stream(self._comm_stream):
-                dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
-                rounded = self.k.cast_from_f32(partial, weight.dtype)
-                self._pending = torch.cuda.Event()
-                self._pending.record(self._comm_stream)
-            partial.record_stream(self._comm_stream)
-            rounded.record_stream(main)
+        if world > 1:
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
             self.collectives += 1
-        else:
-            if world > 1:
-                dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
-                self.collectives += 1
-            rounded = self.k.cast_from_f32(partial, weight.dtype)
+        rounded = self.k.cast_from_f32(partial, weight.dtype)
         if self.kind == "layernorm":
             return dx, rounded[0], rounded[1]
         if self.kind == "fused_add_rms_norm":
             return dx, dx, rounded
         return dx, rounded
-
-
-def _finish(self):
-    """Make the caller's current stream wait for an overlapped exchange."""
-    if self._pending is not None:
-        torch.cuda.current_stream().wait_event(self._pending)
-        self._pending = None
-
-
-ShardedNorm.finish = _finish
 
 
 def shard_rows(t: torch.Tensor, group=None) -> torch.Tensor:

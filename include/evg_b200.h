@@ -339,8 +339,10 @@ int evg_evoattention_bwd(const void* dout, const void* q, const void* k,
  * and reports the sticky device-side status of the kernels that wait on
  * mbarriers (attention, the norm backward rings, wide softmax): every wait
  * inside them is bounded, and a wait that gives up records its identity,
- * lets the kernel finish and is reported here as EVG_ETIMEOUT (results of that
- * launch are then undefined). reset != 0 clears the status after reading it.
+ * lets the kernel finish and is reported here as EVG_ETIMEOUT. Results of that
+ * launch are then undefined, and so is everything enqueued on the device
+ * between that launch and this call (it may have consumed the bad results).
+ * reset != 0 clears the status after reading it.
  */
 int evg_device_status(int reset);
 

@@ -135,23 +135,6 @@ def test_full_size_heads_against_oracle_slices():
         assert_checks(_strict_checks(got, {"o": o_ref, **g_ref}), f"full size slice {(b, h)}")
 
 
-def test_first_version_backward_kernels_still_agree():
-    """attention.variant = 1 selects the unpipelined backward kernels."""
-    from evograd_b200 import _cabi
-
-    dims = dict(B=1, H=2, S=700, D=128)
-    inputs = ao.make_inputs("causal_attention", dims, "bfloat16")
-    o_ref, g_ref = ao.oracle("causal_attention", inputs, reference_dtype=torch.float32,
-                             forward=ao.causal_attention_forward_sdpa)
-    _cabi.tune_set("attention.variant", 1)
-    try:
-        o, grads, _ = run_pair("causal_attention", to_device(inputs))
-    finally:
-        _cabi.tune_set("attention.variant", 0)
-    got = {"o": o, **dict(zip(("dq", "dk", "dv"), grads))}
-    assert_checks(_strict_checks(got, {"o": o_ref, **g_ref}), "variant 1")
-
-
 def test_bad_arguments_raise():
     from evograd_b200 import ops
     from evograd_b200._cabi import EvgError

@@ -33,8 +33,18 @@ def test_binding_table_matches_header():
 def test_version_and_target():
     from evograd_b200 import _cabi
 
-    assert _cabi.lib.evg_abi_version() == 2
+    import __graft_entry__ as entry
+
+    assert _cabi.lib.evg_abi_version() == entry.header_abi_version() >= 2
     assert _cabi.lib.evg_built_for_sm() == 100
+
+
+def test_build_entry_point_runs_clean():
+    """``__graft_entry__.build()`` compiles (or finds up to date) the library,
+    imports the package and checks version and target without raising."""
+    import __graft_entry__ as entry
+
+    entry.build()
 
 
 def test_argument_validation_needs_no_gpu():
@@ -49,6 +59,23 @@ def test_argument_validation_needs_no_gpu():
     assert lib.evg_tune_get(b"rows.force_generic") == 1
     assert lib.evg_tune_set(b"rows.force_generic", 0) == 0
     assert lib.evg_tune_get(b"rows.force_generic") == 0
+
+
+def test_attention_scale_must_be_positive_and_finite():
+    """The tensor-core kernels scale after taking the row maximum, so a scale that
+    is zero, negative or not finite is refused before anything is enqueued."""
+    import ctypes as C
+
+    from evograd_b200 import _cabi
+
+    buf = (C.c_char * 64)()
+    p = C.cast(buf, C.c_void_p)
+    for bad in (0.0, -0.125, float("inf"), float("nan")):
+        rc = _cabi.lib.evg_causal_attention_fwd(p, p, p, p, p, 1, 1, 128, 128, bad, 2, None)
+        assert rc == -8, (bad, rc)
+        assert "scale" in _cabi.last_error()
+        rc = _cabi.lib.evg_causal_gqa_attention_fwd(p, p, p, p, p, 1, 2, 1, 128, 128, bad, 2, None)
+        assert rc == -8, (bad, rc)
 
 
 def test_cpu_tensors_are_refused():
