@@ -506,6 +506,281 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   if (r.warp == 1) tmem_dealloc(tmem, 512);
 }
 
+// ------------------------------------------------- dK, dV (128-query tiles)
+// grid = (key tiles, B*Hkv). The block owns key tile `kvt` and walks whole
+// 128-row query tiles i >= kvt:
+//   S^T = K Q_i^T                                 [128 keys x 128 queries]
+//   dP^T = V dO_i^T                               two chunks of 64 queries
+//   P^T = exp2(S^T*c - lse2_q), dS^T = P^T*(dP^T - delta_q)
+//   dV += P^T dO_i, dK += dS^T Q_i                (A from TMEM, k-steps of 16 queries)
+// TMEM: X [0,128) S^T; Y0 [128,192), Y1 [192,256) dP^T of query chunk 0 / 1,
+// replaced in place by the 16-bit P^T / dS^T; [256,256+HD) dV; [384,384+HD) dK.
+// The S^T product has N = 128, so its two shared-memory operands stay within the
+// SM's 128 bytes per clock. Program of the MMA warp for tile i:
+//     S^T(i+1) -> X       as soon as the compute warps have pulled S^T(i) into registers
+//     dV, dK (i, chunk 0) -> dP^T(i+1, chunk 0) -> Y0
+//     dV, dK (i, chunk 1) -> dP^T(i+1, chunk 1) -> Y1
+// The tensor pipe runs its instructions in order, so dP^T(i+1, ch) lands in Y_ch
+// right behind the products that read it. The exponentials of tile i+1 run under
+// the products of tile i, and the dS step of one chunk runs under the products of
+// the other chunk, so no step of the chain  dP^T -> dS^T -> dV/dK -> dP^T  waits
+// for the compute warps as long as they keep up.
+// Q tiles sit in a ring of QST stages and dO tiles (with the row statistics) in
+// a ring of two, each with its own full/empty barriers: Q(i+1) is wanted soon
+// after dK(i-1) has released a stage, so with QST = 3 its load is already a tile
+// ahead; dO(i+1) is only wanted after dV/dK(i, chunk 0).
+// A compute warp (TMEM lane quarter q, column half h) handles 32 query columns
+// of each chunk and writes 16 columns of P^T followed by 16 of dS^T into the same
+// 32 columns of Y_ch: it only ever overwrites what it has read itself.
+template <int HD, int FMT, int QST>
+__global__ void __launch_bounds__(kThreads2, 1)
+attn_bwd3_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                      const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
+                      void* __restrict__ dk_ptr, void* __restrict__ dv_ptr, int S, int S_pad,
+                      int group, float scale, long long wait_limit, uint32_t smem_bytes) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr uint32_t TB = tile_bytes<HD>();
+  constexpr uint32_t kTiles = 4 + QST;
+  BlockSetup bs = carve(smem_raw, kTiles * TB + 2048);
+  // The launch reserves little more than the tiles themselves: if the dynamic
+  // shared memory did not start on a 1024-byte boundary the carve-up would not
+  // fit, which is reported instead of run.
+  if ((uint32_t)(bs.smem - smem_raw) + kTiles * TB + 2048 + (uint32_t)kControlBytes > smem_bytes) {
+    if (threadIdx.x == 0) atomicCAS(&g_attn2_device_status, 0, 699);
+    return;
+  }
+  uint8_t* sK = bs.smem;
+  uint8_t* sV = sK + TB;
+  uint8_t* sDO0 = sV + TB;        // 2 stages
+  uint8_t* sQ0 = sDO0 + 2 * TB;   // QST stages
+  float* s_stat = reinterpret_cast<float*>(sQ0 + QST * TB);  // [stage][lse2 | delta][128]
+  uint64_t* kv_full = bs.bars + 0;
+  uint64_t* q_full = bs.bars + 1;    // [QST]
+  uint64_t* q_empty = bs.bars + 4;   // [QST]
+  uint64_t* do_full = bs.bars + 7;   // [2]
+  uint64_t* do_empty = bs.bars + 9;  // [2]
+  uint64_t* s_full = bs.bars + 11;
+  uint64_t* x_free = bs.bars + 12;
+  uint64_t* dp_full = bs.bars + 13;   // [2] per query chunk
+  uint64_t* pds_full = bs.bars + 15;  // [2]
+  uint64_t* done = bs.bars + 17;
+  const Roles r = roles();
+  const int kvt = blockIdx.x;  // key tile 0 meets the most query tiles: heaviest first
+  const int bh = blockIdx.y;
+  const int kv0 = kvt * kTile;
+  const int n_it = S_pad / kTile - kvt;
+  // Grouped-query attention: the query tiles of each of the `group` query heads
+  // bh*group + hh in turn (iteration git = hh * n_it + it), accumulating in TMEM.
+  const int n_git = group * n_it;
+  const float scale_log2 = scale * kLog2e;
+
+  if (threadIdx.x == 0) {
+    *bs.abort_flag = 0;
+    mbar_init(kv_full, 1); mbar_init(done, 1);
+    for (int i = 0; i < QST; ++i) { mbar_init(q_full + i, 1); mbar_init(q_empty + i, 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(do_full + i, 1); mbar_init(do_empty + i, 1);
+      mbar_init(dp_full + i, 1); mbar_init(pds_full + i, 8);
+    }
+    mbar_init(s_full, 1); mbar_init(x_free, 8);
+    fence_mbar_init();
+    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
+  }
+  __syncthreads();
+  if (r.warp == 1) { tmem_alloc(bs.tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *bs.tmem_slot;
+  const WaitCtx ctx{bs.abort_flag, &g_attn2_device_status, wait_limit};
+  constexpr uint32_t idesc_s = instr_desc_f16(FMT, 128, 128, 0, 0);
+  constexpr uint32_t idesc_p = instr_desc_f16(FMT, 128, 64, 0, 0);
+  constexpr uint32_t idesc_d = instr_desc_f16(FMT, 128, HD, 0, 1);
+  const uint32_t tX = tmem;
+  const uint32_t tY[2] = {tmem + 128, tmem + 192};
+  const uint32_t tDV = tmem + 256, tDK = tmem + 384;
+
+  if (r.is_tma && r.lane == 0) {
+    mbar_expect_tx(kv_full, 2 * TB);
+    load_tile<HD>(sK, &map_k, kv0, bh, kv_full);
+    load_tile<HD>(sV, &map_v, kv0, bh, kv_full);
+    int it = 0, bhq = bh * group, git = 0;
+    int qs = 0, q_round = 0;  // Q stage of tile git and how often the ring has wrapped
+    for (; git < n_git; ++git) {
+      const int ds = git & 1;
+      const int q0 = (kvt + it) * kTile;
+      if (q_round > 0) mbar_wait(q_empty + qs, (q_round - 1) & 1, ctx, 621);
+      if (*ctx.abort_flag) break;  // no new copies after a timeout
+      mbar_expect_tx(q_full + qs, TB);
+      load_tile<HD>(sQ0 + qs * TB, &map_q, q0, bhq, q_full + qs);
+      if (git >= 2) mbar_wait(do_empty + ds, ((git >> 1) - 1) & 1, ctx, 631);
+      if (!*ctx.abort_flag) {
+        mbar_expect_tx(do_full + ds, TB + 1024);
+        load_tile<HD>(sDO0 + ds * TB, &map_do, q0, bhq, do_full + ds);
+        bulk_load_1d(s_stat + ds * 256, lse2_pad + (size_t)bhq * S_pad + q0, 512, do_full + ds);
+        bulk_load_1d(s_stat + ds * 256 + 128, delta_pad + (size_t)bhq * S_pad + q0, 512,
+                     do_full + ds);
+      }
+      if (++qs == QST) { qs = 0; ++q_round; }
+      if (++it == n_it) { it = 0; ++bhq; }
+    }
+    if (*ctx.abort_flag) {
+      // Let the copies still in flight land before the block returns: each of
+      // these waits gives up after the same cycle budget.
+      mbar_drain(kv_full, 0, wait_limit);
+      for (int g = git > QST ? git - QST : 0; g < git; ++g)
+        mbar_drain(q_full + g % QST, (uint32_t)((g / QST) & 1), wait_limit);
+      for (int g = git > 2 ? git - 2 : 0; g < git; ++g)
+        mbar_drain(do_full + (g & 1), (uint32_t)((g >> 1) & 1), wait_limit);
+    }
+  } else if (r.is_mma) {
+    const bool lead = elect_one();
+    const DescBase v_base = desc_base_kmajor(smem_u32(sV));
+    // dP^T of query chunk ch: B operand = rows [64 ch, 64 ch + 64) of a dO tile.
+    auto issue_dp = [&](int ch, uint32_t do_saddr) {
+      const DescBase da = desc_base_kmajor(do_saddr + ch * 64 * 128);
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        if (lead)
+          mma_ss(tY[ch], desc_at(v_base, kstep_kmajor(kTile, ks)),
+                 desc_at(da, kstep_kmajor(kTile, ks)), idesc_p, ks > 0 ? 1u : 0u);
+      if (lead) mma_commit(dp_full + ch);
+    };
+    mbar_wait(kv_full, 0, ctx, 622);
+    mbar_wait(q_full + 0, 0, ctx, 623);
+    tc_fence_after_sync();
+    issue_scores<HD>(lead, tX, smem_u32(sK), smem_u32(sQ0), idesc_s);
+    if (lead) mma_commit(s_full);
+    mbar_wait(do_full + 0, 0, ctx, 632);
+    tc_fence_after_sync();
+    issue_dp(0, smem_u32(sDO0));
+    issue_dp(1, smem_u32(sDO0));
+    int qs = 0, q_par = 0;  // Q stage of tile c and the parity of its full barrier
+    for (int c = 0; c < n_git; ++c) {
+      const int ds = c & 1, ds1 = ds ^ 1;
+      const bool more = c + 1 < n_git;
+      int qs1 = qs + 1, q_par1 = q_par;
+      if (qs1 == QST) { qs1 = 0; q_par1 ^= 1; }
+      if (more) {
+        mbar_wait(q_full + qs1, q_par1, ctx, 624);
+        mbar_wait(x_free, c & 1, ctx, 625);
+        tc_fence_after_sync();
+        issue_scores<HD>(lead, tX, smem_u32(sK), smem_u32(sQ0 + qs1 * TB), idesc_s);
+        if (lead) mma_commit(s_full);
+      }
+      const uint32_t do_saddr = smem_u32(sDO0 + ds * TB), q_saddr = smem_u32(sQ0 + qs * TB);
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        mbar_wait(pds_full + ch, c & 1, ctx, 626);
+        tc_fence_after_sync();
+        // Query k-step kk of the chunk (16 queries): 32-column group kk/2, 8 packed
+        // columns (kk%2) inside it; dS^T sits 16 columns after P^T.
+        const DescBase dob = desc_base_mnmajor(do_saddr + ch * 64 * 128, kTile);
+        const DescBase qb = desc_base_mnmajor(q_saddr + ch * 64 * 128, kTile);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          if (lead)
+            mma_ts(tDV, tY[ch] + (kk >> 1) * 32 + (kk & 1) * 8, desc_at(dob, kstep_mnmajor(kk)),
+                   idesc_d, (c > 0 || ch > 0 || kk > 0) ? 1u : 0u);
+        if (lead && ch == 1) mma_commit(do_empty + ds);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          if (lead)
+            mma_ts(tDK, tY[ch] + (kk >> 1) * 32 + 16 + (kk & 1) * 8,
+                   desc_at(qb, kstep_mnmajor(kk)), idesc_d, (c > 0 || ch > 0 || kk > 0) ? 1u : 0u);
+        if (lead && ch == 1) mma_commit(q_empty + qs);
+        if (more) {
+          if (ch == 0) {
+            mbar_wait(do_full + ds1, ((c + 1) >> 1) & 1, ctx, 633);
+            tc_fence_after_sync();
+          }
+          issue_dp(ch, smem_u32(sDO0 + ds1 * TB));
+        }
+      }
+      qs = qs1;
+      q_par = q_par1;
+      __syncwarp();
+    }
+    if (lead) mma_commit(done);
+  } else if (r.is_compute) {
+    const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
+    const int kv_glob = kv0 + r.row;
+    const int col0 = r.half * 32;  // first query column inside a chunk of this warp
+    int it = 0;                    // query-tile index within the current query head
+    for (int c = 0; c < n_git; ++c) {
+      const int ds = c & 1;
+      mbar_wait(do_full + ds, (c >> 1) & 1, ctx, 627);  // row statistics landed
+      mbar_wait(s_full, c & 1, ctx, 628);
+      __syncwarp();
+      tc_fence_after_sync();
+      uint32_t sr[64];  // [chunk][32 columns]
+      tmem_ld32(tX + lane_base + col0, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+      tmem_ld32(tX + lane_base + 64 + col0, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+      tmem_wait_ld();
+      warp_arrive(x_free, r.lane);
+      const float* stat = s_stat + ds * 256;
+      float p[64];
+      uint32_t pp[32];
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        const float4* lse4 = reinterpret_cast<const float4*>(stat + ch * 64 + col0);
+        const int q_first = kvt * kTile + ch * 64 + col0;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 l4 = lse4[g];
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float pe = fast_exp2(fmaf(__uint_as_float(sr[ch * 32 + 4 * g + e]), scale_log2, -lv[e]));
+            // diagonal tile: queries before the key are masked
+            if (it == 0 && q_first + 4 * g + e < kv_glob) pe = 0.f;
+            p[ch * 32 + 4 * g + e] = pe;
+          }
+          pp[ch * 16 + 2 * g] = pack2<FMT>(p[ch * 32 + 4 * g], p[ch * 32 + 4 * g + 1]);
+          pp[ch * 16 + 2 * g + 1] = pack2<FMT>(p[ch * 32 + 4 * g + 2], p[ch * 32 + 4 * g + 3]);
+        }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        mbar_wait(dp_full + ch, c & 1, ctx, 629);
+        __syncwarp();
+        tc_fence_after_sync();
+        uint32_t dr[32];
+        tmem_ld32(tY[ch] + lane_base + col0, dr);
+        tmem_wait_ld();
+        const float4* del4 = reinterpret_cast<const float4*>(stat + 128 + ch * 64 + col0);
+        uint32_t dd[16];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 d4 = del4[g];
+          const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          float d[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            d[e] = p[ch * 32 + 4 * g + e] * (__uint_as_float(dr[4 * g + e]) - dv[e]);
+          dd[2 * g] = pack2<FMT>(d[0], d[1]);
+          dd[2 * g + 1] = pack2<FMT>(d[2], d[3]);
+        }
+        tmem_st16(tY[ch] + lane_base + col0, *reinterpret_cast<uint32_t(*)[16]>(&pp[ch * 16]));
+        tmem_st16(tY[ch] + lane_base + col0 + 16, dd);
+        tmem_wait_st();
+        warp_arrive(pds_full + ch, r.lane);
+      }
+      if (++it == n_it) it = 0;
+    }
+    mbar_wait(done, 0, ctx, 630);
+    __syncwarp();
+    tc_fence_after_sync();
+    store_rows<HD, FMT>(tDV, dv_ptr, bh, kv0, S, 1.0f, r);
+    store_rows<HD, FMT>(tDK, dk_ptr, bh, kv0, S, scale, r);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (r.warp == 1) tmem_dealloc(tmem, 512);
+}
+
 // ---------------------------------------------------------------- host side
 long long wait_limit_cycles2() {
   const int t = tune("attention.wait_limit");  // in millions of cycles
@@ -548,12 +823,34 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
   dim3 grid((unsigned)n_q, (unsigned)(B * H));
   const long long limit = wait_limit_cycles2();
   {
-    const size_t smem = 6 * tile_bytes<HD>() + 2048 + kControlBytes + 1024;
-    auto kern = attn_bwd2_dkdv_kernel<HD, FMT>;
-    if (int rc = reserve_smem(kern, smem)) return rc;
+    // attention.dkdv: 0 (default) whole 128-query tiles with a three-stage Q ring,
+    // 2 the same with two stages, 1 the kernel that walks 64-query chunks.
+    const int variant = tune("attention.dkdv");
     dim3 grid_kv((unsigned)n_q, (unsigned)(B * Hkv));
-    kern<<<grid_kv, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
-                                               (int)S, (int)S_pad, group, scale, limit);
+    if (variant == 1) {
+      const size_t smem = 6 * tile_bytes<HD>() + 2048 + kControlBytes + 1024;
+      auto kern = attn_bwd2_dkdv_kernel<HD, FMT>;
+      if (int rc = reserve_smem(kern, smem)) return rc;
+      kern<<<grid_kv, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
+                                                 (int)S, (int)S_pad, group, scale, limit);
+    } else if (variant == 2) {
+      const size_t smem = 6 * tile_bytes<HD>() + 2048 + kControlBytes + 1024;
+      auto kern = attn_bwd3_dkdv_kernel<HD, FMT, 2>;
+      if (int rc = reserve_smem(kern, smem)) return rc;
+      kern<<<grid_kv, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
+                                                 (int)S, (int)S_pad, group, scale, limit,
+                                                 (uint32_t)smem);
+    } else {
+      // 7 tiles of 32 KB at head size 128 leave 768 bytes of the 227 KB for alignment.
+      size_t smem = 7 * tile_bytes<HD>() + 2048 + kControlBytes + 1024;
+      const size_t most = (size_t)device_info().max_smem_optin;
+      if (smem > most) smem = most;
+      auto kern = attn_bwd3_dkdv_kernel<HD, FMT, 3>;
+      if (int rc = reserve_smem(kern, smem)) return rc;
+      kern<<<grid_kv, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
+                                                 (int)S, (int)S_pad, group, scale, limit,
+                                                 (uint32_t)smem);
+    }
     if (int rc = check_launch("causal_attention_bwd dkdv")) return rc;
   }
   {
