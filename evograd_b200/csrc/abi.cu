@@ -26,7 +26,7 @@ const char* const kTuneKeys[] = {
     "layernorm_fwd.threads",    "layernorm_bwd.group",    "layernorm_bwd.vpt",
     "layernorm_bwd.threads",    "rmsnorm_fwd.group",      "rmsnorm_fwd.vpt",
     "rmsnorm_fwd.threads",      "rmsnorm_bwd.group",      "rmsnorm_bwd.vpt",
-    "rmsnorm_bwd.threads",      "attention.dkdv",         "rope.generic",           "norm_bwd.no_ring",
+    "rmsnorm_bwd.threads",      "rope.generic",           "norm_bwd.no_ring",
     "norm_bwd.stages",         "norm_bwd.ring_threads",      "attention.wait_limit",
     "softmax.no_cluster",       "softmax.cluster",        "softmax.cluster_stages", "softmax.cluster_threads", "evoattention.no_stage",
 };

@@ -1,22 +1,27 @@
 // Causal attention backward, warp-specialised and pipelined (sm_100a).
 //
-// Roles inside a block of 320 threads:
-//   warp 0, lane 0   TMA producer: tiles of Q/K/V/dO (+ row statistics) into a
-//                    shared-memory ring, completion on "full" mbarriers, refills
+// Roles inside a block:
+//   warp 0, lane 0   TMA producer: tiles of Q/K/V/dO (+ row statistics) into
+//                    shared-memory rings, completion on "full" mbarriers, refills
 //                    gated by "empty" mbarriers that the MMA thread commits;
-//   warp 1, lane 0   tcgen05.mma issuer: every product of the kernel, in an
+//   warp 1           tcgen05.mma issuer: every product of the kernel, in an
 //                    order that keeps the tensor pipe fed while the compute
 //                    warps work on the previous tile;
-//   warps 2..9       256 compute threads: thread = one TMEM lane (score row)
-//                    and one half of the tile's columns.
-// The score buffers are double-buffered in TMEM, so the scores of tile j+1 are
-// formed while tile j is being turned into dS. A compute warp writes its 16-bit
-// results only into TMEM columns it read itself, so no block-wide barrier is
-// needed between reading scores and writing dS: the A operand of the following
-// product is addressed k-step by k-step and need not be contiguous.
+//   warps 2..        compute threads: thread = one TMEM lane (score row) and one
+//                    group of the tile's columns (8 warps in the dQ kernel,
+//                    16 in the dK/dV kernel).
+// A compute warp writes its 16-bit results only into TMEM columns it read
+// itself, so no block-wide barrier is needed between reading scores and writing
+// dS: the A operand of the following product is addressed k-step by k-step and
+// need not be contiguous.
 //
-// As in the first version, dK/dV belong to the block that owns a key tile and dQ
-// to the block that owns a query tile: deterministic, no atomics.
+// dK/dV belong to the block that owns a key tile and dQ to the block that owns
+// a query tile: deterministic, no atomics, at the price of 7 tile products
+// where a fused backward with a float32 dQ reduction needs 5. On a B200 both
+// kernels run into the board's power limit (sw_power_cap active, SM clock near
+// 1.55 GHz); their time per tile product is within a few percent of what a
+// library bf16 GEMM sustains under the same limit, so the number of tile
+// products, not idle cycles between them, is what sets the time.
 #include "attention_common.cuh"
 
 namespace evg {
@@ -58,22 +63,25 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
 }
 
 // Rows of a [128 x HD] float32 TMEM accumulator -> 16-bit rows of [B*H, S, HD].
-template <int HD, int FMT>
+// The CG column groups of compute warps take HD / CG columns each.
+template <int HD, int FMT, int CG = 2>
 __device__ __forceinline__ void store_rows(uint32_t t_acc, void* out, int bh, int row0, int S,
                                            float scale, const Roles& r) {
+  constexpr int CW = HD / CG;             // columns per warp
+  constexpr int PIECE = CW >= 32 ? 32 : 16;  // columns per TMEM read
   const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
   const int row = row0 + r.row;
   const bool ok = row < S;
   uint8_t* dst = reinterpret_cast<uint8_t*>(out) + ((size_t)bh * S + (ok ? row : 0)) * HD * 2;
 #pragma unroll
-  for (int c = 0; c < HD / 64; ++c) {
-    const int col = r.half * (HD / 2) + c * 32;
-    uint32_t acc[32];
-    tmem_ld32(t_acc + lane_base + col, acc);
+  for (int c = 0; c < CW / PIECE; ++c) {
+    const int col = r.half * CW + c * PIECE;
+    uint32_t acc[PIECE];
+    tmem_ld(t_acc + lane_base + col, acc);
     tmem_wait_ld();
     if (ok) {
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
+      for (int v = 0; v < PIECE / 8; ++v) {
         uint4 pk;
         pk.x = pack2<FMT>(__uint_as_float(acc[8 * v + 0]) * scale, __uint_as_float(acc[8 * v + 1]) * scale);
         pk.y = pack2<FMT>(__uint_as_float(acc[8 * v + 2]) * scale, __uint_as_float(acc[8 * v + 3]) * scale);
@@ -298,215 +306,6 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 }
 
 // -------------------------------------------------------------------- dK, dV
-// grid = (key tiles, B*H). The block owns key tile `kvt` and walks the query
-// tiles i >= kvt in CHUNKS of 64 query rows (two chunks per 128-row tile), so
-// that the float32 score/dP buffers take 64 TMEM columns each and can be
-// double-buffered next to the two 128-column accumulators:
-//   S^T = K Q_c^T, dP^T = V dO_c^T           [128 keys x 64 queries]
-//   P^T = exp2(S^T*c - lse2_q), dS^T = P^T*(dP^T - delta_q)
-//   dV += P^T dO_c, dK += dS^T Q_c           (A from TMEM, 4 k-steps of 16 queries)
-// TMEM: [0,64) [64,128) score buffers, [128,192) [192,256) dP buffers,
-//       [256,256+HD) dV, [384,384+HD) dK.
-// A compute warp handles 32 of a chunk's 64 query columns; its packed P^T / dS^T
-// (16 columns) go to the start of the 32 columns it read.
-template <int HD, int FMT>
-__global__ void __launch_bounds__(kThreads2, 1)
-attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                      const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
-                      void* __restrict__ dk_ptr, void* __restrict__ dv_ptr, int S, int S_pad,
-                      int group, float scale, long long wait_limit) {
-  extern __shared__ uint8_t smem_raw[];
-  constexpr uint32_t TB = tile_bytes<HD>();
-  BlockSetup bs = carve(smem_raw, 6 * TB + 2048);
-  uint8_t* sK = bs.smem;
-  uint8_t* sV = sK + TB;
-  uint8_t* sQ[2] = {sV + TB, sV + 2 * TB};
-  uint8_t* sDO[2] = {sV + 3 * TB, sV + 4 * TB};
-  float* s_stat = reinterpret_cast<float*>(sV + 5 * TB);  // [stage][lse2 | delta][128]
-  uint64_t* kv_full = bs.bars + 0;
-  uint64_t* q_full = bs.bars + 1;     // [2]
-  uint64_t* q_empty = bs.bars + 3;    // [2]
-  uint64_t* sdp_full = bs.bars + 5;   // [2]
-  uint64_t* pds_full = bs.bars + 7;   // [2]
-  uint64_t* done = bs.bars + 9;
-  const Roles r = roles();
-  const int kvt = blockIdx.x;  // key tile 0 meets the most query tiles: heaviest first
-  const int bh = blockIdx.y;
-  const int kv0 = kvt * kTile;
-  const int n_q = S_pad / kTile;
-  const int n_it = n_q - kvt;
-  // Grouped-query attention: the block owns key tile `kvt` of k/v head `bh` and
-  // walks the query tiles of each of the `group` query heads bh*group + hh in
-  // turn (iteration git = hh * n_it + it), accumulating dK/dV in TMEM across them.
-  const int n_git = group * n_it;
-  const int n_chunks = 2 * n_git;
-  const float scale_log2 = scale * kLog2e;
-
-  if (threadIdx.x == 0) {
-    *bs.abort_flag = 0;
-    mbar_init(kv_full, 1); mbar_init(done, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(q_full + i, 1); mbar_init(q_empty + i, 1);
-      mbar_init(sdp_full + i, 1); mbar_init(pds_full + i, 8);
-    }
-    fence_mbar_init();
-    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k);
-    prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
-  }
-  __syncthreads();
-  if (r.warp == 1) { tmem_alloc(bs.tmem_slot, 512); tmem_relinquish(); }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = *bs.tmem_slot;
-  const WaitCtx ctx{bs.abort_flag, &g_attn2_device_status, wait_limit};
-  constexpr uint32_t idesc_s = instr_desc_f16(FMT, 128, 64, 0, 0);
-  constexpr uint32_t idesc_d = instr_desc_f16(FMT, 128, HD, 0, 1);
-  const uint32_t tSb[2] = {tmem, tmem + 64};
-  const uint32_t tPb[2] = {tmem + 128, tmem + 192};
-  const uint32_t tDV = tmem + 256, tDK = tmem + 384;
-
-  if (r.is_tma && r.lane == 0) {
-    mbar_expect_tx(kv_full, 2 * TB);
-    load_tile<HD>(sK, &map_k, kv0, bh, kv_full);
-    load_tile<HD>(sV, &map_v, kv0, bh, kv_full);
-    int it = 0, bhq = bh * group;
-    for (int git = 0; git < n_git; ++git) {
-      const int st = git & 1;
-      const int q0 = (kvt + it) * kTile;
-      if (git >= 2) mbar_wait(q_empty + st, ((git - 2) >> 1) & 1, ctx, 601);
-      mbar_expect_tx(q_full + st, 2 * TB + 1024);
-      load_tile<HD>(sQ[st], &map_q, q0, bhq, q_full + st);
-      load_tile<HD>(sDO[st], &map_do, q0, bhq, q_full + st);
-      bulk_load_1d(s_stat + st * 256, lse2_pad + (size_t)bhq * S_pad + q0, 512, q_full + st);
-      bulk_load_1d(s_stat + st * 256 + 128, delta_pad + (size_t)bhq * S_pad + q0, 512, q_full + st);
-      if (++it == n_it) {
-        it = 0;
-        ++bhq;
-      }
-    }
-  } else if (r.is_mma) {
-    const bool lead = elect_one();
-    const DescBase k_base = desc_base_kmajor(smem_u32(sK)), v_base = desc_base_kmajor(smem_u32(sV));
-    // Scores of chunk c: B operand = 64 rows of the Q / dO tile starting at row 64*(c&1).
-    auto issue_chunk_scores = [&](int c) {
-      const int st = (c >> 1) & 1, hq = c & 1, b = c & 1;
-      const DescBase qa = desc_base_kmajor(smem_u32(sQ[st]) + hq * 64 * 128);
-      const DescBase da = desc_base_kmajor(smem_u32(sDO[st]) + hq * 64 * 128);
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks)
-        if (lead)
-          mma_ss(tSb[b], desc_at(k_base, kstep_kmajor(kTile, ks)),
-                 desc_at(qa, kstep_kmajor(kTile, ks)), idesc_s, ks > 0 ? 1u : 0u);
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks)
-        if (lead)
-          mma_ss(tPb[b], desc_at(v_base, kstep_kmajor(kTile, ks)),
-                 desc_at(da, kstep_kmajor(kTile, ks)), idesc_s, ks > 0 ? 1u : 0u);
-      if (lead) mma_commit(sdp_full + b);
-    };
-    mbar_wait(kv_full, 0, ctx, 602);
-    mbar_wait(q_full + 0, 0, ctx, 603);
-    tc_fence_after_sync();
-    issue_chunk_scores(0);
-    for (int c = 0; c < n_chunks; ++c) {
-      const int b = c & 1, it = c >> 1, st = it & 1, hq = c & 1;
-      if (c + 1 < n_chunks) {
-        const int it1 = (c + 1) >> 1;
-        if (((c + 1) & 1) == 0) {
-          mbar_wait(q_full + (it1 & 1), (it1 >> 1) & 1, ctx, 604);
-          tc_fence_after_sync();
-        }
-        issue_chunk_scores(c + 1);
-      }
-      mbar_wait(pds_full + b, (c >> 1) & 1, ctx, 605);
-      tc_fence_after_sync();
-      // 4 k-steps of 16 queries; packed halves sit at buffer columns 0 and 32.
-      const DescBase dob = desc_base_mnmajor(smem_u32(sDO[st]) + hq * 64 * 128, kTile);
-      const DescBase qb = desc_base_mnmajor(smem_u32(sQ[st]) + hq * 64 * 128, kTile);
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        if (lead)
-          mma_ts(tDV, tSb[b] + (ks >> 1) * 32 + (ks & 1) * 8, desc_at(dob, kstep_mnmajor(ks)),
-                 idesc_d, (c > 0 || ks > 0) ? 1u : 0u);
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        if (lead)
-          mma_ts(tDK, tPb[b] + (ks >> 1) * 32 + (ks & 1) * 8, desc_at(qb, kstep_mnmajor(ks)),
-                 idesc_d, (c > 0 || ks > 0) ? 1u : 0u);
-      if (lead && hq == 1) mma_commit(q_empty + st);
-      __syncwarp();
-    }
-    if (lead) mma_commit(done);
-  } else if (r.is_compute) {
-    const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
-    const int kv_glob = kv0 + r.row;
-    int it = 0;  // query-tile index within the current query head
-    for (int c = 0; c < n_chunks; ++c) {
-      const int b = c & 1, git = c >> 1, st = git & 1, hq = c & 1;
-      if (hq == 0) mbar_wait(q_full + st, (git >> 1) & 1, ctx, 606);  // row statistics landed
-      mbar_wait(sdp_full + b, (c >> 1) & 1, ctx, 607);
-      __syncwarp();
-      tc_fence_after_sync();
-      uint32_t sr[32], dr[32];
-      tmem_ld32(tSb[b] + lane_base + r.half * 32, sr);
-      tmem_ld32(tPb[b] + lane_base + r.half * 32, dr);
-      tmem_wait_ld();
-      const int col0 = hq * 64 + r.half * 32;  // first query column (inside the tile) of this warp
-      const float4* lse4 = reinterpret_cast<const float4*>(s_stat + st * 256 + col0);
-      const float4* del4 = reinterpret_cast<const float4*>(s_stat + st * 256 + 128 + col0);
-      const int q_first = (kvt + it) * kTile + col0;
-      uint32_t pp[16], dd[16];
-      if (it == 0) {  // diagonal tile: queries before the key are masked
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 l4 = lse4[g], d4 = del4[g];
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-          float p[4], d[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float pe = fast_exp2(fmaf(__uint_as_float(sr[4 * g + e]), scale_log2, -lv[e]));
-            if (q_first + 4 * g + e < kv_glob) pe = 0.f;
-            p[e] = pe;
-            d[e] = pe * (__uint_as_float(dr[4 * g + e]) - dv[e]);
-          }
-          pp[2 * g] = pack2<FMT>(p[0], p[1]); pp[2 * g + 1] = pack2<FMT>(p[2], p[3]);
-          dd[2 * g] = pack2<FMT>(d[0], d[1]); dd[2 * g + 1] = pack2<FMT>(d[2], d[3]);
-        }
-      } else {
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 l4 = lse4[g], d4 = del4[g];
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-          float p[4], d[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            p[e] = fast_exp2(fmaf(__uint_as_float(sr[4 * g + e]), scale_log2, -lv[e]));
-            d[e] = p[e] * (__uint_as_float(dr[4 * g + e]) - dv[e]);
-          }
-          pp[2 * g] = pack2<FMT>(p[0], p[1]); pp[2 * g + 1] = pack2<FMT>(p[2], p[3]);
-          dd[2 * g] = pack2<FMT>(d[0], d[1]); dd[2 * g + 1] = pack2<FMT>(d[2], d[3]);
-        }
-      }
-      tmem_st16(tSb[b] + lane_base + r.half * 32, pp);
-      tmem_st16(tPb[b] + lane_base + r.half * 32, dd);
-      tmem_wait_st();
-      warp_arrive(pds_full + b, r.lane);
-      if (hq == 1 && ++it == n_it) it = 0;
-    }
-    mbar_wait(done, 0, ctx, 608);
-    __syncwarp();
-    tc_fence_after_sync();
-    store_rows<HD, FMT>(tDV, dv_ptr, bh, kv0, S, 1.0f, r);
-    store_rows<HD, FMT>(tDK, dk_ptr, bh, kv0, S, scale, r);
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (r.warp == 1) tmem_dealloc(tmem, 512);
-}
-
-// ------------------------------------------------- dK, dV (128-query tiles)
 // grid = (key tiles, B*Hkv). The block owns key tile `kvt` and walks whole
 // 128-row query tiles i >= kvt:
 //   S^T = K Q_i^T                                 [128 keys x 128 queries]
@@ -516,7 +315,8 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 // TMEM: X [0,128) S^T; Y0 [128,192), Y1 [192,256) dP^T of query chunk 0 / 1,
 // replaced in place by the 16-bit P^T / dS^T; [256,256+HD) dV; [384,384+HD) dK.
 // The S^T product has N = 128, so its two shared-memory operands stay within the
-// SM's 128 bytes per clock. Program of the MMA warp for tile i:
+// SM's 128 bytes per clock (a 64-column product needs 192). Program of the MMA
+// warp for tile i:
 //     S^T(i+1) -> X       as soon as the compute warps have pulled S^T(i) into registers
 //     dV, dK (i, chunk 0) -> dP^T(i+1, chunk 0) -> Y0
 //     dV, dK (i, chunk 1) -> dP^T(i+1, chunk 1) -> Y1
@@ -529,12 +329,15 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 // a ring of two, each with its own full/empty barriers: Q(i+1) is wanted soon
 // after dK(i-1) has released a stage, so with QST = 3 its load is already a tile
 // ahead; dO(i+1) is only wanted after dV/dK(i, chunk 0).
-// A compute warp (TMEM lane quarter q, column half h) handles 32 query columns
-// of each chunk and writes 16 columns of P^T followed by 16 of dS^T into the same
-// 32 columns of Y_ch: it only ever overwrites what it has read itself.
-template <int HD, int FMT, int QST>
-__global__ void __launch_bounds__(kThreads2, 1)
-attn_bwd3_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+// 4 * CG compute warps: warp (TMEM lane quarter q, column group g) handles
+// CPW = 64 / CG query columns of each chunk and writes CPW/2 columns of P^T
+// followed by CPW/2 of dS^T into the same CPW columns of Y_ch: it only ever
+// overwrites what it has read itself. CG = 4 (16 warps, 32 elements per thread
+// and tile) keeps the SM's issue slots and its special-function unit busier than
+// CG = 2 does, with half the registers per thread.
+template <int HD, int FMT, int QST, int CG>
+__global__ void __launch_bounds__(64 + 128 * CG, 1)
+attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                       const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
                       void* __restrict__ dk_ptr, void* __restrict__ dv_ptr, int S, int S_pad,
@@ -565,7 +368,10 @@ attn_bwd3_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   uint64_t* dp_full = bs.bars + 13;   // [2] per query chunk
   uint64_t* pds_full = bs.bars + 15;  // [2]
   uint64_t* done = bs.bars + 17;
-  const Roles r = roles();
+  constexpr int CPW = 64 / CG;  // query columns of a chunk per compute warp
+  // First packed P^T column (inside Y_ch) of the chunk's query k-step kk.
+  auto p_col = [](int kk) { return (kk * 16 / CPW) * CPW + (kk * 16 % CPW) / 2; };
+  const Roles r = roles();  // r.half is the warp's column group, 0 .. CG-1
   const int kvt = blockIdx.x;  // key tile 0 meets the most query tiles: heaviest first
   const int bh = blockIdx.y;
   const int kv0 = kvt * kTile;
@@ -581,9 +387,9 @@ attn_bwd3_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     for (int i = 0; i < QST; ++i) { mbar_init(q_full + i, 1); mbar_init(q_empty + i, 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(do_full + i, 1); mbar_init(do_empty + i, 1);
-      mbar_init(dp_full + i, 1); mbar_init(pds_full + i, 8);
+      mbar_init(dp_full + i, 1); mbar_init(pds_full + i, 4 * CG);
     }
-    mbar_init(s_full, 1); mbar_init(x_free, 8);
+    mbar_init(s_full, 1); mbar_init(x_free, 4 * CG);
     fence_mbar_init();
     prefetch_tensormap(&map_q); prefetch_tensormap(&map_k);
     prefetch_tensormap(&map_v); prefetch_tensormap(&map_do);
@@ -675,21 +481,21 @@ attn_bwd3_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       for (int ch = 0; ch < 2; ++ch) {
         mbar_wait(pds_full + ch, c & 1, ctx, 626);
         tc_fence_after_sync();
-        // Query k-step kk of the chunk (16 queries): 32-column group kk/2, 8 packed
-        // columns (kk%2) inside it; dS^T sits 16 columns after P^T.
+        // Query k-step kk of the chunk (16 queries = 8 packed columns): its P^T
+        // columns start at p_col(kk), dS^T sits CPW/2 columns after P^T.
         const DescBase dob = desc_base_mnmajor(do_saddr + ch * 64 * 128, kTile);
         const DescBase qb = desc_base_mnmajor(q_saddr + ch * 64 * 128, kTile);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           if (lead)
-            mma_ts(tDV, tY[ch] + (kk >> 1) * 32 + (kk & 1) * 8, desc_at(dob, kstep_mnmajor(kk)),
-                   idesc_d, (c > 0 || ch > 0 || kk > 0) ? 1u : 0u);
+            mma_ts(tDV, tY[ch] + p_col(kk), desc_at(dob, kstep_mnmajor(kk)), idesc_d,
+                   (c > 0 || ch > 0 || kk > 0) ? 1u : 0u);
         if (lead && ch == 1) mma_commit(do_empty + ds);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           if (lead)
-            mma_ts(tDK, tY[ch] + (kk >> 1) * 32 + 16 + (kk & 1) * 8,
-                   desc_at(qb, kstep_mnmajor(kk)), idesc_d, (c > 0 || ch > 0 || kk > 0) ? 1u : 0u);
+            mma_ts(tDK, tY[ch] + p_col(kk) + CPW / 2, desc_at(qb, kstep_mnmajor(kk)), idesc_d,
+                   (c > 0 || ch > 0 || kk > 0) ? 1u : 0u);
         if (lead && ch == 1) mma_commit(q_empty + qs);
         if (more) {
           if (ch == 0) {
@@ -707,64 +513,81 @@ attn_bwd3_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   } else if (r.is_compute) {
     const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
     const int kv_glob = kv0 + r.row;
-    const int col0 = r.half * 32;  // first query column inside a chunk of this warp
-    int it = 0;                    // query-tile index within the current query head
+    const int col0 = r.half * CPW;  // first query column inside a chunk of this warp
+    int it = 0;                     // query-tile index within the current query head
     for (int c = 0; c < n_git; ++c) {
       const int ds = c & 1;
       mbar_wait(do_full + ds, (c >> 1) & 1, ctx, 627);  // row statistics landed
       mbar_wait(s_full, c & 1, ctx, 628);
       __syncwarp();
       tc_fence_after_sync();
-      uint32_t sr[64];  // [chunk][32 columns]
-      tmem_ld32(tX + lane_base + col0, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
-      tmem_ld32(tX + lane_base + 64 + col0, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+      uint32_t sr[2][CPW];  // [chunk][columns]
+      tmem_ld(tX + lane_base + col0, sr[0]);
+      tmem_ld(tX + lane_base + 64 + col0, sr[1]);
       tmem_wait_ld();
       warp_arrive(x_free, r.lane);
       const float* stat = s_stat + ds * 256;
-      float p[64];
-      uint32_t pp[32];
+      float p[2][CPW];
+      uint32_t pp[2][CPW / 2];
+      if (it == 0) {  // diagonal tile: queries before the key are masked
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        const float4* lse4 = reinterpret_cast<const float4*>(stat + ch * 64 + col0);
-        const int q_first = kvt * kTile + ch * 64 + col0;
+        for (int ch = 0; ch < 2; ++ch) {
+          const float4* lse4 = reinterpret_cast<const float4*>(stat + ch * 64 + col0);
+          const int q_first = kvt * kTile + ch * 64 + col0;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 l4 = lse4[g];
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+          for (int g = 0; g < CPW / 4; ++g) {
+            const float4 l4 = lse4[g];
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float pe = fast_exp2(fmaf(__uint_as_float(sr[ch * 32 + 4 * g + e]), scale_log2, -lv[e]));
-            // diagonal tile: queries before the key are masked
-            if (it == 0 && q_first + 4 * g + e < kv_glob) pe = 0.f;
-            p[ch * 32 + 4 * g + e] = pe;
+            for (int e = 0; e < 4; ++e) {
+              const float pe =
+                  fast_exp2(fmaf(__uint_as_float(sr[ch][4 * g + e]), scale_log2, -lv[e]));
+              p[ch][4 * g + e] = (q_first + 4 * g + e < kv_glob) ? 0.f : pe;
+            }
           }
-          pp[ch * 16 + 2 * g] = pack2<FMT>(p[ch * 32 + 4 * g], p[ch * 32 + 4 * g + 1]);
-          pp[ch * 16 + 2 * g + 1] = pack2<FMT>(p[ch * 32 + 4 * g + 2], p[ch * 32 + 4 * g + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          const float4* lse4 = reinterpret_cast<const float4*>(stat + ch * 64 + col0);
+#pragma unroll
+          for (int g = 0; g < CPW / 4; ++g) {
+            const float4 l4 = lse4[g];
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              p[ch][4 * g + e] =
+                  fast_exp2(fmaf(__uint_as_float(sr[ch][4 * g + e]), scale_log2, -lv[e]));
+          }
         }
       }
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+        for (int g = 0; g < CPW / 2; ++g) pp[ch][g] = pack2<FMT>(p[ch][2 * g], p[ch][2 * g + 1]);
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         mbar_wait(dp_full + ch, c & 1, ctx, 629);
         __syncwarp();
         tc_fence_after_sync();
-        uint32_t dr[32];
-        tmem_ld32(tY[ch] + lane_base + col0, dr);
+        uint32_t dr[CPW];
+        tmem_ld(tY[ch] + lane_base + col0, dr);
         tmem_wait_ld();
         const float4* del4 = reinterpret_cast<const float4*>(stat + 128 + ch * 64 + col0);
-        uint32_t dd[16];
+        uint32_t dd[CPW / 2];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
+        for (int g = 0; g < CPW / 4; ++g) {
           const float4 d4 = del4[g];
           const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
           float d[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            d[e] = p[ch * 32 + 4 * g + e] * (__uint_as_float(dr[4 * g + e]) - dv[e]);
+            d[e] = p[ch][4 * g + e] * (__uint_as_float(dr[4 * g + e]) - dv[e]);
           dd[2 * g] = pack2<FMT>(d[0], d[1]);
           dd[2 * g + 1] = pack2<FMT>(d[2], d[3]);
         }
-        tmem_st16(tY[ch] + lane_base + col0, *reinterpret_cast<uint32_t(*)[16]>(&pp[ch * 16]));
-        tmem_st16(tY[ch] + lane_base + col0 + 16, dd);
+        tmem_st(tY[ch] + lane_base + col0, pp[ch]);
+        tmem_st(tY[ch] + lane_base + col0 + CPW / 2, dd);
         tmem_wait_st();
         warp_arrive(pds_full + ch, r.lane);
       }
@@ -773,8 +596,8 @@ attn_bwd3_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     mbar_wait(done, 0, ctx, 630);
     __syncwarp();
     tc_fence_after_sync();
-    store_rows<HD, FMT>(tDV, dv_ptr, bh, kv0, S, 1.0f, r);
-    store_rows<HD, FMT>(tDK, dk_ptr, bh, kv0, S, scale, r);
+    store_rows<HD, FMT, CG>(tDV, dv_ptr, bh, kv0, S, 1.0f, r);
+    store_rows<HD, FMT, CG>(tDK, dk_ptr, bh, kv0, S, scale, r);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -823,34 +646,17 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
   dim3 grid((unsigned)n_q, (unsigned)(B * H));
   const long long limit = wait_limit_cycles2();
   {
-    // attention.dkdv: 0 (default) whole 128-query tiles with a three-stage Q ring,
-    // 2 the same with two stages, 1 the kernel that walks 64-query chunks.
-    const int variant = tune("attention.dkdv");
+    // 7 tiles of 32 KB at head size 128 leave 768 bytes of the 227 KB for alignment.
+    size_t smem = 7 * tile_bytes<HD>() + 2048 + kControlBytes + 1024;
+    const size_t most = (size_t)device_info().max_smem_optin;
+    if (smem > most) smem = most;
+    constexpr int CG = 4;  // 16 compute warps
+    auto kern = attn_bwd2_dkdv_kernel<HD, FMT, 3, CG>;
+    if (int rc = reserve_smem(kern, smem)) return rc;
     dim3 grid_kv((unsigned)n_q, (unsigned)(B * Hkv));
-    if (variant == 1) {
-      const size_t smem = 6 * tile_bytes<HD>() + 2048 + kControlBytes + 1024;
-      auto kern = attn_bwd2_dkdv_kernel<HD, FMT>;
-      if (int rc = reserve_smem(kern, smem)) return rc;
-      kern<<<grid_kv, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
-                                                 (int)S, (int)S_pad, group, scale, limit);
-    } else if (variant == 2) {
-      const size_t smem = 6 * tile_bytes<HD>() + 2048 + kControlBytes + 1024;
-      auto kern = attn_bwd3_dkdv_kernel<HD, FMT, 2>;
-      if (int rc = reserve_smem(kern, smem)) return rc;
-      kern<<<grid_kv, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
-                                                 (int)S, (int)S_pad, group, scale, limit,
-                                                 (uint32_t)smem);
-    } else {
-      // 7 tiles of 32 KB at head size 128 leave 768 bytes of the 227 KB for alignment.
-      size_t smem = 7 * tile_bytes<HD>() + 2048 + kControlBytes + 1024;
-      const size_t most = (size_t)device_info().max_smem_optin;
-      if (smem > most) smem = most;
-      auto kern = attn_bwd3_dkdv_kernel<HD, FMT, 3>;
-      if (int rc = reserve_smem(kern, smem)) return rc;
-      kern<<<grid_kv, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
-                                                 (int)S, (int)S_pad, group, scale, limit,
-                                                 (uint32_t)smem);
-    }
+    kern<<<grid_kv, 64 + 128 * CG, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
+                                                   (int)S, (int)S_pad, group, scale, limit,
+                                                   (uint32_t)smem);
     if (int rc = check_launch("causal_attention_bwd dkdv")) return rc;
   }
   {

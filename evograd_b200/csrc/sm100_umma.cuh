@@ -207,6 +207,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+// The same accesses chosen by the width of the register array.
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[8]) { tmem_st8(taddr, r); }
+
 // Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
 // Field layout: start address [0,14), leading byte offset [16,30), stride byte
 // offset [32,46) (all in 16-byte units), version [46,48), layout type [61,64).
