@@ -114,5 +114,22 @@ int launch_generic_bwd(int dtype, const void* dout, const void* q, const void* k
                        void* workspace, int64_t workspace_bytes, int64_t B, int64_t Hq,
                        int64_t Hkv, int64_t S, int64_t D, float scale, cudaStream_t stream);
 
+
+// EvoformerAttention on the tensor cores (attention_evo_tc.cu): head sizes 32 and
+// 64, 16-bit inputs, residue counts that are a multiple of 4.
+bool evo_tc_shape(int64_t B, int64_t S, int64_t N, int64_t H, int64_t D, int dtype);
+int launch_evo_tc_fwd(int head_dim, int fmt, const void* q, const void* k, const void* v,
+                      const float* res_mask, const float* pair_bias, void* o, float* lse,
+                      int64_t B, int64_t S, int64_t N, int64_t H, float scale,
+                      cudaStream_t stream);
+// delta = rowsum(do * o) as float32 [B, S, H, N] comes from the caller; dbias_out
+// receives `split` partial d_pair_bias arrays [split][B][H][N][N] (MSA rows cut
+// into `split` parts), which the caller adds up when split > 1.
+int launch_evo_tc_bwd(int head_dim, int fmt, const void* dout, const void* q, const void* k,
+                      const void* v, const float* res_mask, const float* pair_bias,
+                      const float* lse, const float* delta, void* dq, void* dk, void* dv,
+                      float* dbias_out, int split, int64_t B, int64_t S, int64_t N, int64_t H,
+                      float scale, cudaStream_t stream);
+
 }  // namespace attn
 }  // namespace evg

@@ -19,7 +19,10 @@
 // (batch, head, query) row, without atomics. Saved state: o and the float32
 // log-sum-exp [B, S, H, N].
 #include <algorithm>
+#include <initializer_list>
+#include <type_traits>
 
+#include "attention_common.cuh"
 #include "evg_common.cuh"
 
 // 16-bit element types only (the reference declares float16 | bfloat16).
@@ -412,6 +415,25 @@ int evo_split(int64_t B, int64_t S, int64_t N, int64_t H) {
   return split < 1 ? 1 : (int)split;
 }
 
+// The same for the tensor-core d_pair_bias kernel, whose blocks own a
+// [128 x 64] tile of the gradient: about four blocks per SM, at most 32 parts.
+int evo_tc_split(int64_t B, int64_t S, int64_t N, int64_t H) {
+  const int64_t blocks = ((N + 127) / 128) * ((N + 63) / 64) * H * B;
+  int64_t split = (4 * (int64_t)device_info().sm_count + blocks - 1) / blocks;
+  if (split > 32) split = 32;
+  if (split > S) split = S;
+  while (split > 1 && B * H * split > 65535) --split;
+  return split < 1 ? 1 : (int)split;
+}
+
+bool evo_use_tc(int64_t B, int64_t S, int64_t N, int64_t H, int64_t D, int dtype,
+                std::initializer_list<const void*> ptrs) {
+  if (!attn::evo_tc_shape(B, S, N, H, D, dtype)) return false;
+  for (const void* p : ptrs)
+    if (!aligned16(p)) return false;
+  return true;
+}
+
 // Dynamic shared memory of a kernel with `bufs` float32 row buffers per warp
 // and (when it fits) two staged [N, D] matrices of T; *staged says which.
 template <typename T, typename Kernel>
@@ -471,10 +493,10 @@ template <typename T>
 int launch_evo_bwd(const void* dout, const void* q, const void* k, const void* v,
                    const float* res_mask, const float* pair_bias, const void* o,
                    const float* lse, void* dq, void* dk, void* dv, float* d_pair_bias,
-                   float* workspace, const EvoShape& sh, cudaStream_t st) {
+                   float* workspace, const EvoShape& sh, bool use_tc, cudaStream_t st) {
   const int64_t B = sh.B, S = sh.S, N = sh.N, H = sh.H, D = sh.D;
   float* delta = workspace;
-  const int split = evo_split(B, S, N, H);
+  const int split = use_tc ? evo_tc_split(B, S, N, H) : evo_split(B, S, N, H);
   float* slabs = split > 1 ? delta + B * S * H * N : d_pair_bias;
   const int dt = evo_dt((int)D);
   const bool few_chunks = N <= 384;
@@ -483,6 +505,19 @@ int launch_evo_bwd(const void* dout, const void* q, const void* k, const void* v
   const unsigned wide_tiles = (unsigned)((N + rows_per_block - 1) / rows_per_block);
   evo_delta_kernel<T><<<dim3(tiles, (unsigned)H, (unsigned)(B * S)), kWarps * 32, 0, st>>>(
       (const T*)dout, (const T*)o, delta, sh);
+  if (use_tc) {
+    if (int rc = check_launch("evoattention_bwd delta")) return rc;
+    if (int rc = attn::launch_evo_tc_bwd((int)D, sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0,
+                                         dout, q, k, v, res_mask, pair_bias, lse, delta, dq, dk,
+                                         dv, slabs, split, B, S, N, H, sh.scale, st))
+      return rc;
+    if (split > 1) {
+      const int64_t n = B * H * N * N;
+      evo_dbias_reduce_kernel<<<(unsigned)std::min<int64_t>((n + 255) / 256, 4096), 256, 0, st>>>(
+          slabs, d_pair_bias, n, split);
+    }
+    return check_launch("evoattention_bwd");
+  }
 #define EVG_EVO_DQ(DT_, MAXC_)                                                                   \
   if (dt == DT_ && few_chunks == (MAXC_ == 12)) {                                                \
     int staged = 0;                                                                              \
@@ -527,6 +562,9 @@ extern "C" int evg_evoattention_fwd(const void* q, const void* k, const void* v,
     return fail(EVG_ENULL, "evoattention_fwd: null pointer argument");
   if (int rc = check_evo("evoattention_fwd", B, S, N, H, D, dtype)) return rc;
   const EvoShape sh{(int)B, (int)S, (int)N, (int)H, (int)D, scale};
+  if (evo_use_tc(B, S, N, H, D, dtype, {q, k, v, res_mask, pair_bias, o, lse}))
+    return attn::launch_evo_tc_fwd((int)D, dtype == EVG_BF16 ? 1 : 0, q, k, v, res_mask, pair_bias,
+                                   o, lse, B, S, N, H, scale, (cudaStream_t)stream);
   return EVG_DISPATCH_DTYPE_16(dtype, [&] {
     return launch_evo_fwd<T>(q, k, v, res_mask, pair_bias, o, lse, sh, (cudaStream_t)stream);
   });
@@ -536,8 +574,9 @@ extern "C" int64_t evg_evoattention_bwd_workspace_bytes(int64_t B, int64_t S, in
                                                         int64_t H, int64_t D, int dtype) {
   (void)D; (void)dtype;
   if (B <= 0 || S <= 0 || N <= 0 || H <= 0) return 0;
-  const int split = evo_split(B, S, N, H);
-  // delta [B,S,H,N] + (split > 1: one d_pair_bias slab per part)
+  // delta [B,S,H,N] + (split > 1: one d_pair_bias slab per part); enough for
+  // whichever of the two kernel families the call ends up on
+  const int split = std::max(evo_split(B, S, N, H), evo_tc_split(B, S, N, H));
   return (B * S * H * N + (split > 1 ? (int64_t)split * B * H * N * N : 0)) *
          (int64_t)sizeof(float);
 }
@@ -557,8 +596,12 @@ extern "C" int evg_evoattention_bwd(const void* dout, const void* q, const void*
     return fail(EVG_EWORKSPACE, "evoattention_bwd: workspace %lld bytes, need %lld",
                 (long long)workspace_bytes, (long long)need);
   const EvoShape sh{(int)B, (int)S, (int)N, (int)H, (int)D, scale};
+  const bool use_tc = evo_use_tc(B, S, N, H, D, dtype,
+                                 {dout, q, k, v, res_mask, pair_bias, o, lse, (const void*)dq,
+                                  (const void*)dk, (const void*)dv, (const void*)d_pair_bias,
+                                  (const void*)workspace});
   return EVG_DISPATCH_DTYPE_16(dtype, [&] {
     return launch_evo_bwd<T>(dout, q, k, v, res_mask, pair_bias, o, lse, dq, dk, dv, d_pair_bias,
-                             (float*)workspace, sh, (cudaStream_t)stream);
+                             (float*)workspace, sh, use_tc, (cudaStream_t)stream);
   });
 }

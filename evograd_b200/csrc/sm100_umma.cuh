@@ -22,6 +22,11 @@ namespace umma {
 bool encode_tile_map_16bit(CUtensorMap* map, const void* base, int fmt, uint64_t cols,
                            uint64_t rows, uint64_t outer, uint32_t box_rows);
 
+// The same for a dense float32 [outer, rows, cols] tensor with tiles of
+// [box_rows x box_cols]; swizzle128 needs box_cols == 32 (128 bytes per row).
+bool encode_tile_map_f32(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                         uint64_t outer, uint32_t box_cols, uint32_t box_rows, bool swizzle128);
+
 #ifdef __CUDACC__
 // ---------------------------------------------------------------- device side
 
