@@ -167,8 +167,12 @@ __device__ __forceinline__ void store_head_rows(uint32_t t_acc, void* out, int b
 
 // ------------------------------------------------------------------ forward
 // grid = (query tiles of 128, H, B*S), 128 threads: thread = query row, key
-// chunks of 64. TMEM (128 columns): [0,64) scores, P packed into [0,32);
-// [64,128) O. Online softmax with a lazily moved running maximum.
+// chunks of 64. TMEM (256 columns): two score buffers [0,64), [64,128) (chunk c
+// uses buffer c % 2; its P is packed into the buffer's first 32 columns) and
+// O [128,192). After the block barrier that ends chunk c, warp 0 first issues the
+// scores of chunk c+1 into the other buffer and only then O += P V of chunk c,
+// so the other warps wait for two small products, not for the whole issue
+// sequence. Online softmax with a lazily moved running maximum.
 template <int HD, int FMT>
 __global__ void __launch_bounds__(128, 2)
 evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -176,9 +180,9 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   const float* __restrict__ res_mask, void* __restrict__ o_ptr,
                   float* __restrict__ lse_ptr, EvoDims d, float scale_log2, long long wait_limit) {
   extern __shared__ uint8_t smem_raw[];
-  Setup su = block_setup(smem_raw, kRowTileBytes + 4 * kColTileBytes + kBiasTileBytes + 256, 128,
+  Setup su = block_setup(smem_raw, kRowTileBytes + 4 * kColTileBytes + kBiasTileBytes + 256, 256,
                          [](uint64_t* bars) {
-                           for (int i = 0; i < 5; ++i) mbar_init(bars + i, 1);
+                           for (int i = 0; i < 6; ++i) mbar_init(bars + i, 1);
                          });
   uint8_t* sQ = su.bs.smem;
   uint8_t* sK = sQ + kRowTileBytes;       // 2 stages
@@ -189,13 +193,14 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   uint64_t* kv_full = su.bs.bars + 1;  // [2]
   uint64_t* s_done = su.bs.bars + 3;
   uint64_t* bias_full = su.bs.bars + 4;
+  uint64_t* pv_done = su.bs.bars + 5;
   const WaitCtx ctx{su.bs.abort_flag, &g_evo_tc_device_status, wait_limit};
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = blockIdx.x, h = blockIdx.y, bs = blockIdx.z, b = bs / d.S;
   const int N = d.N;
   const int n_kc = (N + 63) / 64;
   const int x0 = tile_x0<HD>(h), ks0 = tile_ks0<HD>(h), oc0 = tile_c0<HD>(h);
-  const uint32_t tS = su.tmem, tO = su.tmem + 64;
+  const uint32_t tO = su.tmem + 128;
   constexpr uint32_t idesc_s = instr_desc_f16(FMT, 128, 64, 0, 0);
   constexpr uint32_t idesc_o = instr_desc_f16(FMT, 128, 64, 0, 1);
 
@@ -210,7 +215,8 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int st = c & 1;
     mbar_wait(kv_full + st, (c >> 1) & 1, ctx, 801);
     tc_fence_after_sync();
-    issue_head_scores<HD>(lead, tS, smem_u32(sQ), smem_u32(sK + st * kColTileBytes), idesc_s, ks0);
+    issue_head_scores<HD>(lead, su.tmem + st * 64, smem_u32(sQ), smem_u32(sK + st * kColTileBytes),
+                          idesc_s, ks0);
     if (lead) mma_commit(s_done);
   };
   if (threadIdx.x == 0) {
@@ -221,6 +227,7 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     load_kv(0);
     load_bias_rows(sB, sM, &map_bias, res_mask + (size_t)bs * N, qt * 128, 0, b * d.H + h, N,
                    bias_full);
+    if (n_kc > 1) load_kv(1);
   }
   __syncwarp();
   if (warp == 0) {
@@ -236,15 +243,19 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   for (int c = 0; c < n_kc; ++c) {
     const int st = c & 1;
+    const uint32_t tS = su.tmem + st * 64;
     mbar_wait(s_done, c & 1, ctx, 803);
     __syncwarp();
     tc_fence_after_sync();
-    // The products of chunk c-1 are complete, so its K/V stage can take chunk c+1.
-    if (threadIdx.x == 0 && c + 1 < n_kc) load_kv(c + 1);
     uint32_t sr[64];
     tmem_ld32(tS + lane_base, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
     tmem_ld32(tS + lane_base + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
     tmem_wait_ld();
+    if (threadIdx.x == 0 && c >= 1 && c + 1 < n_kc) {
+      // chunk c+1 takes the K/V stage of chunk c-1 once O += P V (c-1) has read V
+      mbar_wait(pv_done, (c - 1) & 1, ctx, 807);
+      load_kv(c + 1);
+    }
     mbar_wait(bias_full, c & 1, ctx, 805);
     const int k0 = c * 64;
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -269,8 +280,11 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const bool grow = mx > m_run + kRescaleThreshold;  // always true for the first chunk
     const float m_new = grow ? mx : m_run;
     if (c > 0 && __any_sync(0xffffffffu, grow)) {
-      // O += P V of the previous chunk has completed (the scores just read were
-      // issued behind it); rows that did not grow use alpha = 1.
+      // Rows that did not grow use alpha = 1. O += P V of the previous chunk must
+      // have completed before O is touched.
+      mbar_wait(pv_done, (c - 1) & 1, ctx, 806);
+      __syncwarp();
+      tc_fence_after_sync();
       const float alpha = grow ? fast_exp2(m_run - m_new) : 1.0f;
       l_run *= alpha;
 #pragma unroll
@@ -297,24 +311,21 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     tmem_st32(tS + lane_base, pr);
     tmem_wait_st();
     tc_fence_before_sync();
-    __syncthreads();
-    // every thread is past its bias / mask reads of this chunk
-    if (threadIdx.x == 0 && c + 1 < n_kc)
-      load_bias_rows(sB, sM, &map_bias, res_mask + (size_t)bs * N, qt * 128, (c + 1) * 64,
-                     b * d.H + h, N, bias_full);
+    __syncthreads();  // P is in TMEM; every thread is past its bias / mask reads
     if (warp == 0) {
       tc_fence_after_sync();
+      if (c + 1 < n_kc) issue_s(c + 1);  // into the other score buffer
       issue_head_accumulate(lead, tO, tS, [](int kk) { return (uint32_t)kk * 8u; },
                             smem_u32(sV + st * kColTileBytes), idesc_o, c > 0);
-      if (c + 1 < n_kc) {
-        issue_s(c + 1);  // overwrites the P columns behind the product that reads them
-      } else if (lead) {
-        mma_commit(s_done);
-      }
+      if (lead) mma_commit(pv_done);
+      __syncwarp();
+      if (lane == 0 && c + 1 < n_kc)
+        load_bias_rows(sB, sM, &map_bias, res_mask + (size_t)bs * N, qt * 128, (c + 1) * 64,
+                       b * d.H + h, N, bias_full);
       __syncwarp();
     }
   }
-  mbar_wait(s_done, n_kc & 1, ctx, 804);
+  mbar_wait(pv_done, (n_kc - 1) & 1, ctx, 804);
   __syncwarp();
   tc_fence_after_sync();
   {
@@ -333,7 +344,7 @@ evo_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x < 32) tmem_dealloc(su.tmem, 128);
+  if (threadIdx.x < 32) tmem_dealloc(su.tmem, 256);
 }
 
 // ------------------------------------------------- backward: shared pieces
