@@ -15,7 +15,11 @@ What is timed
     value     device-resident inputs, K steps between two CUDA events on the
               launching stream, barrier + synchronise on both sides, max over
               ranks. Inputs rotate through enough buffer sets that nothing a
-              step reads is still in L2 from the previous use.
+              step reads is still in L2 from the previous use. The K steps are
+              one CUDA graph; the graph is replayed at least five times (enough
+              to cover 100 ms, as the reference's timing loops are sized,
+              bench/fair.py:28-35) and the median replay is reported with its
+              20 % / 80 % quantiles.
     e2e       the same step through the public pair API starting from pinned HOST
               buffers: host->device copies of the inputs and device->host copies
               of every result are inside the timed region.
@@ -25,9 +29,13 @@ What is timed
     cpu_baseline / --impl reference
               the oracle port of the reference's CPU autograd path (the same
               forward under torch.autograd.grad) on the host cores.
-Multi-GPU: weak scaling. Every rank processes a full-size shard (global rows =
-N x 16384); LayerNorm/RMSNorm all-reduce their float32 dweight/dbias partial
-sums over NCCL, everything else exchanges nothing.
+Multi-GPU: the headline is weak scaling. Every rank processes a full-size shard
+(global rows = N x 16384); LayerNorm/RMSNorm exchange their float32
+dweight/dbias partial sums, everything else exchanges nothing. At N > 1 the line
+also carries ``strong`` (the baseline shapes cut N ways: rows, batch or (batch,
+head) units per rank, step time max over ranks, speed-up over the whole shape on
+one GPU) and ``parity_n`` (each rank's dx rows and the exchanged dweight/dbias
+checked against a float32 computation over all ranks' rows, untimed).
 """
 
 from __future__ import annotations
@@ -123,6 +131,26 @@ class Workload:
         evograd_b200.host_pipeline, or None when the workload has no row pipeline."""
         return None
 
+    def memory_inputs(self, s):
+        """Tensors the saved state is measured against: the declaration's
+        ``memory_input_names()`` (opdecl/activity.py:530-535), by default every
+        tensor argument of the forward."""
+        return [t for t in self.inputs_of(s) if torch.is_tensor(t)]
+
+    @classmethod
+    def shard_of(cls, world):
+        """The class of one rank's share when the baseline shape is cut ``world``
+        ways (strong scaling), or None if the shape does not divide."""
+        return None
+
+
+def _shard_class(cls, world, **attrs):
+    for k, v in attrs.items():
+        if v <= 0:
+            return None
+    name = getattr(cls, "name", "") or cls.__name__
+    return type(f"{cls.__name__}Shard{world}", (cls,), dict(attrs, name=f"{name}/{world}"))
+
 
 def _load_pair(op):
     path = os.path.join(ROOT, "evograd_b200", "pairs", f"{op}.py")
@@ -148,6 +176,13 @@ class SoftmaxWL(Workload):
 
     def inputs_of(self, s):
         return [s["x"], s["dy"]]
+
+    def memory_inputs(self, s):
+        return [s["x"]]
+
+    @classmethod
+    def shard_of(cls, world):
+        return _shard_class(cls, world, rows=cls.rows // world) if cls.rows % world == 0 else None
 
     def forward(self, s):
         y, saved = self.fwd(s["x"])
@@ -218,6 +253,13 @@ class NormWL(Workload):
     def inputs_of(self, s):
         return [s[k] for k in ("x", "weight", "bias", "dy") if k in s]
 
+    def memory_inputs(self, s):
+        return [s[k] for k in ("x", "weight", "bias") if k in s]
+
+    @classmethod
+    def shard_of(cls, world):
+        return _shard_class(cls, world, rows=cls.rows // world) if cls.rows % world == 0 else None
+
     def forward(self, s):
         if self.sharded is not None:
             y, saved = self.sharded.forward_with_saved(s["x"], s["weight"], s.get("bias"), self.eps)
@@ -270,6 +312,13 @@ class SwiGLUWL(Workload):
     def inputs_of(self, s):
         return [s["a"], s["b"], s["dc"]]
 
+    def memory_inputs(self, s):
+        return [s["a"], s["b"]]
+
+    @classmethod
+    def shard_of(cls, world):
+        return _shard_class(cls, world, rows=cls.rows // world) if cls.rows % world == 0 else None
+
     def forward(self, s):
         c, saved = self.fwd(s["a"], s["b"])
         return [c], saved
@@ -317,6 +366,9 @@ class FusedAddRMSNormWL(Workload):
     def inputs_of(self, s):
         return [s["x"], s["r"], s["weight"], s["dout"]]
 
+    def memory_inputs(self, s):
+        return [s["x"], s["r"], s["weight"]]
+
     def forward(self, s):
         out, saved = self.fwd(s["x"], s["r"], s["weight"], self.eps)
         return [out], saved
@@ -357,6 +409,13 @@ class RopeWL(Workload):
 
     def inputs_of(self, s):
         return [s["q"], s["k"], s["dq_out"], s["dk_out"], s["cos"], s["sin"]]
+
+    def memory_inputs(self, s):
+        return [s["q"], s["k"]]  # the declaration counts x only (ops/level1/rope/__init__.py:157)
+
+    @classmethod
+    def shard_of(cls, world):
+        return _shard_class(cls, world, B=cls.B // world) if cls.B % world == 0 else None
 
     def forward(self, s):
         from evograd_b200 import ops
@@ -399,6 +458,14 @@ class AttentionWL(Workload):
     def inputs_of(self, s):
         return [s["q"], s["k"], s["v"], s["do"]]
 
+    def memory_inputs(self, s):
+        return [s["q"], s["k"], s["v"]]
+
+    @classmethod
+    def shard_of(cls, world):
+        units = cls.B * cls.H  # independent (batch, head) units
+        return _shard_class(cls, world, B=1, H=units // world) if units % world == 0 else None
+
     def forward(self, s):
         o, saved = self.fwd(s["q"], s["k"], s["v"])
         return [o], saved
@@ -423,7 +490,7 @@ class AttentionWL(Workload):
 class EvoAttentionWL(Workload):
     """AlphaFold-3 triangle attention (S == N == 256, 4 heads of 32): the largest
     family of the reference's evoattention grid
-    (ops/level1/evoattention/__init__.py:44-56). Runs on the CUDA-core kernels."""
+    (ops/level1/evoattention/__init__.py:44-56). Runs on the tcgen05 kernels."""
     name, bound, kernels_per_step, pair = "evoattention_bf16_1x256x4x256x32", "tensor", 4, \
         "evoattention"
     B, S, H, N, D = 1, 256, 4, 256, 32
@@ -446,6 +513,9 @@ class EvoAttentionWL(Workload):
     def inputs_of(self, s):
         return [s[k] for k in ("q", "k", "v", "res_mask", "pair_bias", "do")]
 
+    def memory_inputs(self, s):
+        return [s[k] for k in ("q", "k", "v", "res_mask", "pair_bias")]
+
     def forward(self, s):
         o, saved = self.fwd(s["q"], s["k"], s["v"], s["res_mask"], s["pair_bias"])
         return [o], saved
@@ -459,7 +529,14 @@ class EvoAttentionWL(Workload):
 
     def config(self):
         return {"workload": self.name, "shape": [self.B, self.S, self.N, self.H, self.D],
-                "saved": "o, lse f32", "kernels": "CUDA cores (one warp per row), untuned"}
+                "saved": "o, lse f32", "kernels": "tcgen05, 128 x 64 score tiles"}
+
+
+class EvoAttentionPairBiasWL(EvoAttentionWL):
+    """Pair-bias attention at 384 residues (S == 1, 16 heads of 64): the largest
+    case of the reference grid's pair_bias family."""
+    name = "evoattention_bf16_1x1x16x384x64"
+    B, S, H, N, D = 1, 1, 16, 384, 64
 
 
 class DecoderLayerWL(Workload):
@@ -511,6 +588,9 @@ class DecoderLayerWL(Workload):
     def inputs_of(self, s):
         return [s[k] for k in self._ARGS] + [s["dout"]]
 
+    def memory_inputs(self, s):
+        return [s[k] for k in self._ARGS]
+
     def forward(self, s):
         out, saved = self.fwd(*[s[k] for k in self._ARGS], s["eps"])
         return [out], saved
@@ -544,7 +624,7 @@ WORKLOADS = {"softmax": SoftmaxWL, "layernorm": LayerNormWL, "rmsnorm": RMSNormW
              "swiglu": SwiGLUWL, "rope": RopeWL, "attention": AttentionWL,
              "geglu": GeGLUWL, "fused_add_rms_norm": FusedAddRMSNormWL,
              "softmax_vocab": SoftmaxVocabWL, "decoder_layer": DecoderLayerWL,
-             "evoattention": EvoAttentionWL}
+             "evoattention": EvoAttentionWL, "evoattention_n384": EvoAttentionPairBiasWL}
 
 
 # --------------------------------------------------------------------------
@@ -612,16 +692,68 @@ def _make_sets(wl):
     return [probe] + [wl.make(device, salt=i) for i in range(1, n_sets)]
 
 
+REP_BUDGET_MS = 100.0  # per timed leg, as the reference sizes its loops (bench/fair.py:28-35)
+MIN_REPS, MAX_REPS = 5, 60
+
+
+def _quantile(sorted_vals, q):
+    if len(sorted_vals) == 1:
+        return sorted_vals[0]
+    pos = q * (len(sorted_vals) - 1)
+    lo = int(pos)
+    hi = min(lo + 1, len(sorted_vals) - 1)
+    return sorted_vals[lo] + (sorted_vals[hi] - sorted_vals[lo]) * (pos - lo)
+
+
+def _replay_stats(graph, steps, world):
+    """Replays a graph holding `steps` steps: one untimed replay, then at least
+    MIN_REPS timed ones (enough to cover REP_BUDGET_MS), each between its own
+    CUDA event pair with barrier + synchronise on both sides and the maximum
+    over ranks taken per replay. Returns per-step milliseconds."""
+    from evograd_b200.timing import time_steps
+
+    barrier = _barrier_fn(world)
+    first = _max_over_ranks(time_steps(lambda _i: graph.replay(), 1, 1, barrier=barrier), world)
+    reps = max(MIN_REPS, min(MAX_REPS, int(REP_BUDGET_MS / max(first, 1e-3))))
+    if world > 1:  # every rank must run the same number of replays
+        t = torch.tensor([reps], device="cuda", dtype=torch.int64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
+        reps = int(t.item())
+    samples = [first]
+    for _ in range(reps - 1):
+        samples.append(_max_over_ranks(time_steps(lambda _i: graph.replay(), 1, 0, barrier=barrier),
+                                       world))
+    per_step = sorted(v / steps for v in samples)
+    return {"median": _quantile(per_step, 0.5), "q20": _quantile(per_step, 0.2),
+            "q80": _quantile(per_step, 0.8), "reps": len(per_step)}
+
+
+def _saved_accounting(wl, s, saved):
+    """saved_bytes / input_bytes / saved_memory_ratio as bench/harness.py:128-131 and
+    321-346 compute them (every tensor of the saved state counts, also those that
+    are the inputs themselves), plus the split the reference's final report makes
+    between inputs kept by reference and newly written state (bench/fair.py:297-322)."""
+    tensors = [t for t in (saved if isinstance(saved, (tuple, list)) else (saved,))
+               if torch.is_tensor(t)]
+    inputs = wl.memory_inputs(s)
+    input_ptrs = {t.untyped_storage().data_ptr() for t in wl.inputs_of(s) if torch.is_tensor(t)}
+    total = sum(t.numel() * t.element_size() for t in tensors)
+    retained = sum(t.numel() * t.element_size() for t in tensors
+                   if t.untyped_storage().data_ptr() in input_ptrs)
+    in_bytes = sum(t.numel() * t.element_size() for t in inputs)
+    return {"saved_bytes": int(total), "input_bytes": int(in_bytes),
+            "saved_memory_ratio": round(total / max(in_bytes, 1), 6),
+            "retained_input_bytes": int(retained), "new_saved_bytes": int(total - retained)}
+
+
 def measure_graphs(wl, steps, warmup, world):
     """Device leg with the host launch path removed: the K timed steps (cycling
     through the rotating input sets) are captured into ONE CUDA graph, for the
-    full step, the forward alone and the backward alone, and one replay of each
-    is timed between a CUDA event pair. W eager steps plus one untimed replay
-    come first. (One graph per step would put a graph-launch gap of several
-    microseconds between steps, which is a third of the float32 softmax step.)
-    Returns (step_ms, fwd_ms, bwd_ms, n_sets) per step."""
-    from evograd_b200.timing import time_steps
-
+    full step, the forward alone and the backward alone, and each graph is
+    replayed several times (see _replay_stats). W eager steps come first. (One
+    graph per step would put a graph-launch gap of several microseconds between
+    steps, which is a third of the float32 softmax step.)
+    Returns (step, fwd, bwd statistics, n_sets, saved-state accounting)."""
     sets = _make_sets(wl)
     n = len(sets)
     side = torch.cuda.Stream()
@@ -632,6 +764,7 @@ def measure_graphs(wl, steps, warmup, world):
         saved = [wl.forward(s_)[1] for s_ in sets]  # state the backward-only graph consumes
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
+    accounting = _saved_accounting(wl, sets[0], saved[0])
 
     def capture(body):
         g = torch.cuda.CUDAGraph()
@@ -646,12 +779,11 @@ def measure_graphs(wl, steps, warmup, world):
     res = []
     for body in bodies:
         g = capture(body)
-        ms = time_steps(lambda _i: g.replay(), 1, 1, barrier=_barrier_fn(world))
-        res.append(_max_over_ranks(ms, world) / steps)
+        res.append(_replay_stats(g, steps, world))
         del g
     del saved, sets
     torch.cuda.empty_cache()
-    return res[0], res[1], res[2], n
+    return res[0], res[1], res[2], n, accounting
 
 
 def measure_e2e(wl, steps, warmup, world):
@@ -745,19 +877,33 @@ def _rate(work, ms):
     return work / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
 
 
+def _stat_keys(prefix, st):
+    return {f"{prefix}_ms": round(st["median"], 5), f"{prefix}_ms_q20": round(st["q20"], 5),
+            f"{prefix}_ms_q80": round(st["q80"], 5)}
+
+
 def per_op_entry(wl, steps, warmup, world, peaks):
     launch = "cuda graph replay"
+    accounting = {}
     try:
-        step_ms, fwd_ms, bwd_ms, n_sets = measure_graphs(wl, steps, warmup, world)
+        st, sf, sb, n_sets, accounting = measure_graphs(wl, steps, warmup, world)
+        reps = st["reps"]
     except Exception as exc:  # capture refused: time the same calls eagerly
         launch = f"eager ({type(exc).__name__})"
         torch.cuda.synchronize()
         ms, totals, _launches, n_sets = measure_device(wl, steps, warmup, world)
-        step_ms = ms / steps
-        fwd_ms = totals["fwd"][0] / totals["fwd"][1]
-        bwd_ms = totals["bwd"][0] / totals["bwd"][1]
-    e = {"step_ms": round(step_ms, 5), "fwd_ms": round(fwd_ms, 5), "bwd_ms": round(bwd_ms, 5),
-         "buffer_sets": n_sets, "launch": launch}
+        one = lambda v: {"median": v, "q20": v, "q80": v}  # noqa: E731
+        st = one(ms / steps)
+        sf = one(totals["fwd"][0] / totals["fwd"][1])
+        sb = one(totals["bwd"][0] / totals["bwd"][1])
+        reps = 1
+    step_ms, fwd_ms, bwd_ms = st["median"], sf["median"], sb["median"]
+    e = {**_stat_keys("step", st), **_stat_keys("fwd", sf), **_stat_keys("bwd", sb),
+         # the reference's report keys for the same three timings (bench/harness.py:328-331)
+         "forward_ms": round(fwd_ms, 5), "backward_from_saved_ms": round(bwd_ms, 5),
+         "forward_backward_full_step_ms": round(step_ms, 5),
+         "reps": reps, "steps_per_rep": steps, "buffer_sets": n_sets, "launch": launch,
+         **accounting}
     if wl.bound == "hbm":
         peak = peaks["hbm_gbs"]
         e.update({"algorithmic_MB": round(wl.step_work / 1e6, 1),
@@ -766,12 +912,126 @@ def per_op_entry(wl, steps, warmup, world, peaks):
                   "bwd_gbs": round(_rate(wl.bwd_work, bwd_ms), 1),
                   "frac_of_hbm_peak": round(_rate(wl.step_work, step_ms) / peak, 4)})
     else:
-        peak = peaks["bf16_tflops_sustained"]
+        bwd_tf = wl.bwd_work / (bwd_ms * 1e-3) / 1e12
         e.update({"fwd_tflops": round(wl.fwd_work / (fwd_ms * 1e-3) / 1e12, 1),
-                  "bwd_tflops": round(wl.bwd_work / (bwd_ms * 1e-3) / 1e12, 1),
+                  "bwd_tflops": round(bwd_tf, 1),
                   "tflops": round(wl.step_work / (step_ms * 1e-3) / 1e12 * world, 1),
-                  "bwd_frac_of_bf16_peak": round(wl.bwd_work / (bwd_ms * 1e-3) / 1e12 / peak, 4)})
+                  "bwd_frac_of_burst": round(bwd_tf / peaks["bf16_tflops"], 4),
+                  "bwd_frac_of_sustained": round(bwd_tf / peaks["bf16_tflops_sustained"], 4)})
     return e
+
+
+def strong_scaling(world, steps, warmup, peaks):
+    """The baseline shapes cut `world` ways (rows, batch or (batch, head) units per
+    rank; LayerNorm/RMSNorm with the cross-rank dweight/dbias exchange): step
+    time of the shard (max over ranks) against the whole shape on one GPU with no
+    exchange, both as graph replays in this run."""
+    device = torch.device("cuda", torch.cuda.current_device())
+    out = {}
+    for name in ("softmax", "layernorm", "rmsnorm", "swiglu", "rope", "attention"):
+        cls = WORKLOADS[name]
+        shard_cls = cls.shard_of(world)
+        if shard_cls is None:
+            out[name] = None
+            continue
+        whole = cls(device)
+        if getattr(whole, "sharded", None) is not None:
+            whole.sharded = None  # the one-GPU reference point exchanges nothing
+        t1 = measure_graphs(whole, steps, warmup, 1)[0]["median"]
+        del whole
+        torch.cuda.empty_cache()
+        t1 = _max_over_ranks(t1, world)
+        shard = shard_cls(device)
+        tn = measure_graphs(shard, steps, warmup, world)[0]
+        out[name] = {"shard": shard.config().get("shape"), "whole_shape_1gpu_ms": round(t1, 5),
+                     "shard_step_ms": round(tn["median"], 5), "shard_step_ms_q20": round(tn["q20"], 5),
+                     "shard_step_ms_q80": round(tn["q80"], 5),
+                     "speedup": round(t1 / tn["median"], 3),
+                     "efficiency": round(t1 / tn["median"] / world, 4),
+                     "exchange": "float32 dweight/dbias partial sums" if cls.collective else "none"}
+        del shard
+        torch.cuda.empty_cache()
+    return out
+
+
+def parity_n(world, rank):
+    """Untimed check of the N > 1 path on the baseline LayerNorm / RMSNorm shapes cut
+    by rows: this rank's y and dx against a float32 computation of the same rows,
+    the exchanged dweight/dbias against the float32 column sums over ALL ranks'
+    rows (per-rank float32 sums, added across ranks). Raises on a mismatch."""
+    from evograd_b200.sharded import ShardedNorm
+
+    device = torch.device("cuda", torch.cuda.current_device())
+    report = {}
+    for kind, cls in (("layernorm", LayerNormWL), ("rmsnorm", RMSNormWL)):
+        rows, hidden, eps = cls.rows // world, cls.hidden, cls.eps
+        g = _gen(device, cls.rows * 100000 + hidden)
+        w = _randn((hidden,), BF16, device, g, 0.1, 1.0)  # same seed: identical on every rank
+        b = _randn((hidden,), BF16, device, g, 0.1, 0.0) if kind == "layernorm" else None
+        g = _gen(device, cls.rows * 100000 + hidden + 7919 * (rank + 1))
+        x = _randn((rows, hidden), BF16, device, g)
+        dy = _randn((rows, hidden), BF16, device, g)
+        sn = ShardedNorm(kind)
+        y, saved = sn.forward_with_saved(x, w, b, eps)
+        grads = sn.backward_from_saved(dy, saved)
+        xf, dyf, wf = x.float(), dy.float(), w.float()
+        if kind == "layernorm":
+            mu = xf.mean(-1, keepdim=True)
+            xh = (xf - mu) * torch.rsqrt(((xf - mu) ** 2).mean(-1, keepdim=True) + eps)
+            y_ref = xh * wf + b.float()
+            gg = dyf * wf
+            dx_ref = torch.rsqrt(((xf - mu) ** 2).mean(-1, keepdim=True) + eps) * (
+                gg - gg.mean(-1, keepdim=True) - xh * (gg * xh).mean(-1, keepdim=True))
+            sums = torch.stack(((dyf * xh).sum(0), dyf.sum(0)))
+            mags = torch.stack(((dyf * xh).abs().sum(0), dyf.abs().sum(0)))
+        else:
+            rs = torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps)
+            xh = xf * rs
+            y_ref = xh * wf
+            gg = dyf * wf
+            dx_ref = (gg - xh * (gg * xh).mean(-1, keepdim=True)) * rs
+            sums = (dyf * xh).sum(0)[None]
+            mags = (dyf * xh).abs().sum(0)[None]
+        torch.distributed.all_reduce(sums)
+        torch.distributed.all_reduce(mags)
+        errs = {}
+        for nm, got, ref in (("y", y, y_ref), ("dx", grads[0], dx_ref)):
+            err = (got.float() - ref).abs()
+            ok = bool((err <= 1e-2 + 1.6e-2 * ref.abs()).all())
+            errs[nm] = float(err.max())
+            if not ok:
+                raise AssertionError(f"parity at N={world}: {kind} {nm} max-abs {errs[nm]:.3e}")
+        for i, nm in enumerate(("dweight", "dbias")[: sums.shape[0]]):
+            got = grads[1 + i].float()
+            # one rounding to bf16 (half an ulp = 2^-9 relative; two ulps allowed) on top of
+            # float32 summation noise proportional to the summed magnitudes
+            bound = 2.0 ** -7 * sums[i].abs() + 1e-5 * mags[i] + 1e-3
+            err = (got - sums[i]).abs()
+            errs[nm] = float(err.max())
+            if not bool((err <= bound).all()):
+                raise AssertionError(f"parity at N={world}: {kind} {nm} max-abs {errs[nm]:.3e}")
+            # and every rank holds the same bits
+            lo, hi = grads[1 + i].clone().view(torch.int16), grads[1 + i].clone().view(torch.int16)
+            torch.distributed.all_reduce(lo, op=torch.distributed.ReduceOp.MIN)
+            torch.distributed.all_reduce(hi, op=torch.distributed.ReduceOp.MAX)
+            if not torch.equal(lo, hi):
+                raise AssertionError(f"parity at N={world}: {kind} {nm} differs between ranks")
+        report[kind] = {"rows_per_rank": rows, "max_abs_err": {k: round(v, 6) for k, v in errs.items()},
+                        "exchange": sn.exchange_name()}
+        del x, dy, y, saved, grads, xf, dyf
+        torch.cuda.empty_cache()
+    return {"status": "ok", **report}
+
+
+def _common_config(wl, world):
+    """The workload description both arms print (what is computed, on what)."""
+    return {**wl.config(), "parallelism": f"rows x{world}" if world > 1 else "1 gpu"}
+
+
+def _metric_of(wl):
+    if wl.bound == "hbm":
+        return f"fwd+bwd achieved HBM GB/s ({wl.name})", "GB/s"
+    return f"fwd+bwd TFLOP/s ({wl.name}; attention bwd TFLOP/s under per_op)", "TFLOP/s"
 
 
 def run_ours(args):
@@ -783,17 +1043,27 @@ def run_ours(args):
     peaks, peak_source = measured_peaks()
     wl = WORKLOADS[args.workload](device)
 
+    parity = None
+    if world > 1 and not args.no_parity:
+        parity = parity_n(world, rank)  # raises if the N > 1 results are wrong
+
     # Leg 1 (value): K steps between one event pair, captured as one CUDA graph of
-    # the public pair calls (forward, backward, and at N > 1 the NCCL
-    # all-reduce), so the host's launch path is not what is being timed.
+    # the public pair calls (forward, backward, and at N > 1 the cross-rank
+    # exchange), so the host's launch path is not what is being timed; the graph
+    # is replayed several times and the median replay is the value.
     # Leg 2 (roofline): K backward launches alone (row kernel and column reduce),
-    # again one graph between one event pair; if capture is refused, the same K
-    # steps launched eagerly with an event pair around forward and backward.
+    # timed the same way; if capture is refused, the same K steps launched
+    # eagerly with an event pair around forward and backward.
     launch_mode = "cuda graph replay (the K steps captured in one graph)"
-    roofline_loop = "one replay of a graph holding K backward launches, between one CUDA event pair"
+    roofline_loop = ("replays of a graph holding K backward launches, each between one CUDA "
+                     "event pair; median")
+    spread = None
     with ClockSampler(local) as clocks:
         try:
-            step_ms, _f, bwd_ms, n_sets = measure_graphs(wl, args.steps, args.warmup, world)
+            st, _sf, sb, n_sets, _acc = measure_graphs(wl, args.steps, args.warmup, world)
+            step_ms, bwd_ms = st["median"], sb["median"]
+            spread = {"reps": st["reps"], "ms_per_step_q20": round(st["q20"], 5),
+                      "ms_per_step_q80": round(st["q80"], 5)}
             launches = wl.kernels_per_step * args.steps
         except Exception as exc:  # capture refused: the same calls, launched eagerly
             launch_mode = f"eager, current stream ({type(exc).__name__})"
@@ -806,22 +1076,27 @@ def run_ours(args):
                                                     sections=True)
             bwd_total, bwd_n = totals["bwd"]
             bwd_ms = bwd_total / bwd_n
+    metric, unit = _metric_of(wl)
     if wl.bound == "hbm":
-        metric = f"fwd+bwd achieved HBM GB/s ({wl.name})"
-        unit, value = "GB/s", _rate(wl.step_work, step_ms) * world
+        value = _rate(wl.step_work, step_ms) * world
     else:
-        metric = f"fwd+bwd TFLOP/s ({wl.name}; attention bwd TFLOP/s under per_op)"
-        unit, value = "TFLOP/s", wl.step_work / (step_ms * 1e-3) / 1e12 * world
+        value = wl.step_work / (step_ms * 1e-3) / 1e12 * world
 
     # roofline of the dominant launch: the backward (largest share of the step)
+    traffic, traffic_source = ncu_traffic(args.workload)
     if wl.bound == "hbm":
         achieved, peak, runit = _rate(wl.bwd_work, bwd_ms), peaks["hbm_gbs"], "GB/s"
+        peak_note = f"of {peak_source} (copy bandwidth)"
     else:
-        achieved, peak, runit = wl.bwd_work / (bwd_ms * 1e-3) / 1e12, peaks["bf16_tflops_sustained"], "TFLOP/s"
+        achieved, peak, runit = (wl.bwd_work / (bwd_ms * 1e-3) / 1e12,
+                                 peaks["bf16_tflops_sustained"], "TFLOP/s")
+        peak_note = f"of {peak_source} (sustained bf16 GEMM rate; the kernel runs under the power cap)"
     roofline = {"kernel": f"{args.workload} backward", "bound": wl.bound, "achieved": round(achieved, 1),
                 "peak": peak, "unit": runit, "frac": round(achieved / peak, 4),
-                "peak_source": f"of {peak_source}", "per_launch_ms": round(bwd_ms, 4),
-                "traffic": TRAFFIC_NCU.get(args.workload)}
+                "peak_source": peak_note, "per_launch_ms": round(bwd_ms, 4),
+                "traffic": traffic, "traffic_source": traffic_source}
+    if wl.bound != "hbm":
+        roofline["frac_of_burst"] = round(achieved / peaks["bf16_tflops"], 4)
 
     e2e = None
     if not args.no_e2e:
@@ -839,15 +1114,17 @@ def run_ours(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(step_ms, 5),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": wl.dtype, "data": "synthetic",
-        "config": {**wl.config(), "l2": f"{n_sets} rotating input set(s), each pass reads data not in L2",
-                   "parallelism": f"rows x{world}" if world > 1 else "1 gpu",
-                   "launch": launch_mode,
-                   "roofline_loop": roofline_loop},
+        "config": _common_config(wl, world),
+        "run": {"l2": f"{n_sets} rotating input set(s), each pass reads data not in L2",
+                "launch": launch_mode, "roofline_loop": roofline_loop, "spread": spread,
+                "exchange": (wl.sharded.exchange_name() if getattr(wl, "sharded", None) else None)},
         "e2e": e2e,
         "gpu_launches": launches,
         "roofline": roofline,
         "clocks": clocks.summary(),
     }
+    if parity is not None:
+        line["parity_n"] = parity
 
     if not args.no_per_op:
         per_op = {}
@@ -858,13 +1135,20 @@ def run_ours(args):
             torch.cuda.empty_cache()
         line["per_op"] = per_op
 
+    if world > 1 and not args.no_strong:
+        line["strong"] = strong_scaling(world, max(3, args.steps // 2), max(3, args.warmup), peaks)
+
     if rank == 0 and world == 1 and not args.no_cpu:
         sec, reps, cores = measure_cpu(wl)
         work, sample = wl.cpu_sample()
-        cpu_val = (work / sec / 1e9) if wl.bound == "hbm" else work / sec / 1e12
-        sample = f"{sample} x{reps} (median)"
-        line["cpu_baseline"] = {"value": round(cpu_val, 3), "unit": unit, "cores": cores,
-                                "kind": "port", "sample": sample, "s_per_step": round(sec, 4)}
+        div = 1e9 if wl.bound == "hbm" else 1e12
+        line["cpu_baseline"] = {"value": round(work / sec / div, 3), "unit": unit, "cores": cores,
+                                "kind": "port", "sample": f"{sample} x{reps} (median)",
+                                "s_per_step": round(sec, 4)}
+        sec1, reps1, _ = measure_cpu(wl, budget_s=6.0, max_reps=3, threads=1)
+        line["cpu_baseline"]["one_thread"] = {"value": round(work / sec1 / div, 4), "unit": unit,
+                                              "cores": 1, "sample": f"{sample} x{reps1} (median)",
+                                              "s_per_step": round(sec1, 4)}
 
     from evograd_b200 import ops
     ops.device_status()
@@ -875,27 +1159,48 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per backward launch from the ncu
-# captures summarised under profiles/ (None until a capture exists).
-TRAFFIC_NCU = {
-    # norm_bwd_ring_kernel + colreduce_kernel, profiles/layernorm_bf16_16384x4096.md
-    "layernorm": 375.9e6 + 9.7e6,
-    # captured at a quarter / an eighth of the rows and scaled by the row count:
-    # profiles/rmsnorm_and_fused_add_bf16_8192x4096.md
-    "rmsnorm": 4 * (134.3e6 + 37.4e6) + 4.9e6,
-    "fused_add_rms_norm": 4 * (201.4e6 + 44.5e6) + 4.9e6,
-    # profiles/softmax_bf16_512x128256.md, profiles/geglu_bf16_4096x14336.md
-    "softmax_vocab": 8 * 360.7e6,
-    "geglu": 8 * 541.9e6,
-}
+# dram__bytes_read.sum + dram__bytes_write.sum per backward launch from ncu
+# captures: bytes (already scaled to the bench's row count where the capture ran
+# on fewer rows), the file the summary of the capture is in, the kernel sources
+# the capture belongs to and the digest of those sources when it was taken.
+TRAFFIC_NCU = {}
+
+
+def _source_digest(files):
+    import hashlib
+
+    h = hashlib.sha256()
+    for f in files:
+        with open(os.path.join(ROOT, "evograd_b200", "csrc", f), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:12]
+
+
+def ncu_traffic(workload):
+    """(bytes per launch, where they come from); bytes are None when no capture
+    exists or the kernel sources changed after it was taken."""
+    entry = TRAFFIC_NCU.get(workload)
+    if entry is None:
+        return None, "no ncu capture for this workload"
+    try:
+        now = _source_digest(entry["sources"])
+    except OSError:
+        now = "unreadable"
+    where = f"{entry['profile']} @ csrc digest {entry['digest']}"
+    if now != entry["digest"]:
+        return None, f"stale: {where}, sources now {now}"
+    return entry["bytes"], where
 
 
 def run_reference(args):
     """The reference's own implementation of the path: its CPU autograd oracle
     (restated in oracle/), all host threads, on the same workload."""
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
+    # a launcher sets OMP_NUM_THREADS=1 for its ranks; only this rank computes
+    torch.set_num_threads(os.cpu_count() or 1)
     wl = WORKLOADS[args.workload](torch.device("cpu"))
     s = wl.make(torch.device("cpu"))
     for _ in range(min(args.warmup, 1)):
@@ -911,18 +1216,18 @@ def run_reference(args):
         wl.cpu_step(s)
     sec = (time.perf_counter() - t0) / steps
     hbm = wl.bound == "hbm"
-    unit = "GB/s" if hbm else "TFLOP/s"
+    metric, unit = _metric_of(wl)
     work, sample = wl.cpu_sample()
     value = work / sec / (1e9 if hbm else 1e12)
     cores = torch.get_num_threads()
     line = {
         "impl": "reference",
-        "metric": (f"fwd+bwd achieved HBM GB/s ({wl.name})" if hbm
-                   else f"fwd+bwd TFLOP/s ({wl.name}; attention bwd TFLOP/s under per_op)"),
+        "metric": metric,
         "value": round(value, 4), "unit": unit, "n_gpus": args.gpus, "steps": steps,
         "warmup": min(args.warmup, 1) + 1, "ms_per_step": round(sec * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
-        "data": "synthetic", "config": {**wl.config(), "device": "host CPU"},
+        "data": "synthetic", "config": _common_config(wl, max(world, args.gpus)),
+        "run": {"device": "host CPU", "threads": cores},
         "cpu_baseline": {"value": round(value, 4), "unit": unit, "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": round(value, 4), "unit": unit, "h2d_bytes_per_step": 0,
@@ -942,6 +1247,8 @@ def main():
     ap.add_argument("--no-per-op", action="store_true", help="skip the per-operator table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-strong", action="store_true", help="N > 1: skip the strong-scaling table")
+    ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the untimed result check")
     ap.add_argument("--attention-shape", default=None, metavar="B,H,S",
                     help="smaller causal-attention case (profiling captures only; head_dim stays 128)")
     ap.add_argument("--rows", type=int, default=None,

@@ -151,6 +151,14 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
          c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_void_p],
     ),
+    "evg_exchange_create": (c_int, [c_int64, c_int, c_int, ctypes.POINTER(c_void_p), c_void_p]),
+    "evg_exchange_connect": (c_int, [c_void_p, c_void_p]),
+    "evg_exchange_connect_local": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "evg_exchange_buffer": (c_void_p, [c_void_p]),
+    "evg_exchange_set_wait_limit": (c_int, [c_void_p, c_int64]),
+    "evg_exchange_sum_round": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_void_p,
+                                       c_void_p]),
+    "evg_exchange_destroy": (c_int, [c_void_p]),
     "evg_device_status": (c_int, [c_int]),
     "evg_cast_from_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "evg_flush_l2": (c_int, [c_void_p, c_int64, c_void_p]),

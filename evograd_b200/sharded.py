@@ -8,9 +8,13 @@ RMSNorm (``[2, hidden]`` / ``[hidden]`` floats per step):
     rope                contiguous batch blocks, tables replicated, no exchange
     layernorm, rmsnorm, fused_add_rms_norm
                         contiguous row blocks; every rank forms float32
-                        dweight/dbias over ITS rows, one all_reduce(SUM), and only
-                        then rounds to the parameter dtype (rounding before the sum
-                        would not match a single-device float32 accumulation)
+                        dweight/dbias over ITS rows, the sums of all ranks are
+                        added and only then rounded to the parameter dtype
+                        (rounding before the sum would not match a single-device
+                        float32 accumulation). On one node the exchange is ONE
+                        small kernel per rank that reads the other ranks' sums
+                        through peer memory (:class:`PeerExchange`); the fallback
+                        is all_reduce(SUM) followed by a rounding kernel.
     causal attention    contiguous blocks of the B*H (batch, head) units, no exchange
 
 The reference has no distributed path (its ``--gpus`` runs independent searches);
@@ -65,19 +69,125 @@ class NormKernels:
                            ops.cast_from_f32, ops.fused_add_rmsnorm_fwd, ops.fused_add_rmsnorm_bwd)
 
 
+class PeerExchange:
+    """Sum of per-rank float32 vectors over the ranks of one node, rounded once,
+    through peer memory: each rank owns a small device buffer, the others map it
+    with CUDA IPC, and :meth:`sum_round` enqueues one single-block kernel per rank
+    that publishes this rank's values, waits (bounded) for the other ranks' and
+    adds all of them in rank order. The IPC handles travel through
+    ``torch.distributed.all_gather_object`` once, at construction; every rank
+    must construct the object and call :meth:`sum_round` in the same order.
+
+    ``lib`` is injectable so the host logic can run against a stand-in without a
+    GPU."""
+
+    def __init__(self, max_floats: int, group=None, lib=None):
+        import ctypes
+
+        if lib is None:
+            from . import _cabi as lib
+        self._lib = lib
+        self.world, self.rank = _world(group)
+        self.max_floats = int(max_floats)
+        handle = (ctypes.c_ubyte * 64)()
+        out = ctypes.c_void_p()
+        lib.call("evg_exchange_create", self.max_floats, self.world, self.rank,
+                 ctypes.byref(out), ctypes.cast(handle, ctypes.c_void_p))
+        self._x = out
+        if self.world > 1:
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, bytes(handle), group=group)
+            blob = b"".join(gathered)
+            buf = (ctypes.c_ubyte * len(blob)).from_buffer_copy(blob)
+            lib.call("evg_exchange_connect", self._x, ctypes.cast(buf, ctypes.c_void_p))
+        self.calls = 0
+
+    def sum_round(self, partial: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        """``partial``: contiguous float32 on this rank's device. Returns the sum over
+        ranks rounded to ``dtype`` (same shape), identical bits on every rank."""
+        if partial.dtype != torch.float32 or not partial.is_contiguous():
+            raise TypeError("partial sums must be contiguous float32")
+        if partial.numel() > self.max_floats:
+            raise ValueError(f"{partial.numel()} values exceed the exchange buffer ({self.max_floats})")
+        out = torch.empty(partial.shape, dtype=dtype, device=partial.device)
+        en = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
+        stream = torch.cuda.current_stream(partial.device).cuda_stream if partial.is_cuda else None
+        self._lib.call("evg_exchange_sum_round", self._x, partial.data_ptr(), partial.numel(),
+                       out.data_ptr(), en, None, stream)
+        self.calls += 1
+        return out
+
+    def close(self):
+        if getattr(self, "_x", None):
+            self._lib.call("evg_exchange_destroy", self._x)
+            self._x = None
+
+    def __del__(self):  # best effort; explicit close() is preferred
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class ShardedNorm:
     """LayerNorm / RMSNorm autograd pair over a row shard with the cross-rank
     parameter-gradient reduction. ``kind`` is "layernorm", "rmsnorm" or
     "fused_add_rms_norm" (whose forward also takes ``residual`` and whose backward
-    returns ``(dx, dr, dweight)`` with ``dr is dx``)."""
+    returns ``(dx, dr, dweight)`` with ``dr is dx``).
 
-    def __init__(self, kind: str, group=None, kernels: NormKernels | None = None):
+    ``exchange``: "peer" sums the partial sums with :class:`PeerExchange` (one node,
+    one kernel per rank and step), "allreduce" uses ``all_reduce`` + a rounding
+    kernel, "auto" (default) takes "peer" on CUDA ranks when the buffers of the
+    other ranks can be mapped and "allreduce" otherwise. The choice is made at the
+    first backward and is the same on every rank."""
+
+    def __init__(self, kind: str, group=None, kernels: NormKernels | None = None,
+                 exchange: str = "auto", hidden_max: int = 16384):
         if kind not in ("layernorm", "rmsnorm", "fused_add_rms_norm"):
             raise ValueError(f"kind must be layernorm, rmsnorm or fused_add_rms_norm, got {kind!r}")
+        if exchange not in ("auto", "peer", "allreduce"):
+            raise ValueError(f"exchange must be auto, peer or allreduce, got {exchange!r}")
         self.kind = kind
         self.group = group
         self.k = kernels or NormKernels.cuda()
         self.collectives = 0  # all_reduce calls issued so far
+        self.exchange = exchange
+        self._peer = None
+        self._peer_tried = False
+        self._hidden_max = hidden_max
+
+    def exchange_name(self) -> str:
+        if self._peer is not None:
+            return "peer memory: one kernel per rank reads all ranks' float32 sums (CUDA IPC)"
+        return "nccl all_reduce of the float32 sums + rounding kernel"
+
+    def _peer_exchange(self, partial):
+        """The PeerExchange to use for this tensor, or None (all ranks agree)."""
+        if self._peer is not None or self._peer_tried:
+            return self._peer
+        self._peer_tried = True
+        world, _ = _world(self.group)
+        want = self.exchange != "allreduce" and world > 1 and partial.is_cuda
+        ok = 0
+        peer = None
+        if want:
+            try:
+                peer = PeerExchange(2 * self._hidden_max, self.group)
+                ok = 1
+            except Exception:
+                if self.exchange == "peer":
+                    raise
+                ok = 0
+        if world > 1:
+            # take it only if every rank could map every other rank's buffer
+            flag = torch.tensor([ok], device=partial.device, dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            ok = int(flag.item())
+        if ok and peer is not None:
+            self._peer = peer
+        elif peer is not None:
+            peer.close()
+        return self._peer
 
     def forward_with_saved(self, x_shard, weight, bias=None, eps: float = 1e-5, residual=None):
         if self.kind == "fused_add_rms_norm":
@@ -108,10 +218,14 @@ class ShardedNorm:
             dx, partial = self.k.rmsnorm_bwd(dy_shard, x, weight, rstd, partials_f32=True)
         if partial.dtype != torch.float32:
             raise TypeError("local backward must return float32 partial sums")
-        if world > 1:
-            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
-            self.collectives += 1
-        rounded = self.k.cast_from_f32(partial, weight.dtype)
+        peer = self._peer_exchange(partial) if world > 1 else None
+        if peer is not None and partial.numel() <= peer.max_floats:
+            rounded = peer.sum_round(partial, weight.dtype)
+        else:
+            if world > 1:
+                dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+                self.collectives += 1
+            rounded = self.k.cast_from_f32(partial, weight.dtype)
         if self.kind == "layernorm":
             return dx, rounded[0], rounded[1]
         if self.kind == "fused_add_rms_norm":

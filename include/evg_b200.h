@@ -32,8 +32,12 @@ extern "C" {
 
 /* 2: added geglu, fused add + rmsnorm, grouped-query attention, evoattention,
  *    the no-allocation rmsnorm backward and the bounded-wait self-test; every
- *    version-1 entry point is unchanged. */
-#define EVG_ABI_VERSION 2
+ *    version-1 entry point is unchanged.
+ * 3: added the evg_exchange_* calls (cross-GPU sum of parameter-gradient
+ *    partial sums over peer memory); evoattention head sizes 32 / 64 run on the
+ *    tensor cores; attention entry points reject a scale that is not positive
+ *    and finite. */
+#define EVG_ABI_VERSION 3
 
 enum evg_dtype { EVG_F32 = 0, EVG_F16 = 1, EVG_BF16 = 2 };
 
@@ -357,6 +361,50 @@ int evg_device_status(int reset);
  */
 int evg_selftest_bounded_wait(int64_t limit_cycles, int* observed_abort_word,
                               void* stream);
+
+/* ------------------------------------------------- cross-GPU parameter sums
+ * One process per GPU; LayerNorm / RMSNorm over a row shard leave every rank
+ * with float32 partial sums of dweight (and dbias) over its own rows. These
+ * calls add the partial sums of all ranks of ONE node and round once, in a
+ * single small kernel per rank that reads the other ranks' buffers through
+ * peer memory (CUDA IPC mappings, plain loads, no multicast): every rank adds
+ * in rank order and therefore obtains the same bits. They replace an
+ * all_reduce(SUM) of the float32 sums followed by evg_cast_from_f32.
+ * No counterpart in the reference (its --gpus option runs independent
+ * searches; nothing there shards an operator).
+ *
+ * evg_exchange_create    allocates this rank's buffer (the only allocation;
+ *                        room for max_floats values per step), writes the 64
+ *                        byte IPC handle other ranks need to ipc_handle.
+ * evg_exchange_connect   all_handles = the n_ranks handles in rank order (the
+ *                        caller gathers them with its own collective); maps
+ *                        the other ranks' buffers.
+ * evg_exchange_connect_local   same-process wiring for tests: peer_buffers[r]
+ *                        is the device address of rank r's buffer
+ *                        (evg_exchange_buffer of its handle).
+ * evg_exchange_sum_round enqueues the step's kernel on `stream`: partial is
+ *                        this rank's float32 sums (count values), out
+ *                        (optional) receives the sum over ranks rounded to
+ *                        dtype, out_f32 (optional) the float32 sum. Every rank
+ *                        must make the same sequence of calls; the kernels of
+ *                        the ranks wait for one another, so each rank needs
+ *                        its own GPU. The waits are bounded
+ *                        (evg_exchange_set_wait_limit, SM cycles, default
+ *                        4e9): a rank whose peers do not arrive gives up, and
+ *                        evg_device_status() then reports EVG_ETIMEOUT.
+ *                        Safe to capture in a CUDA graph and replay (the step
+ *                        counter lives in device memory).
+ */
+typedef struct evg_exchange evg_exchange;
+int evg_exchange_create(int64_t max_floats, int n_ranks, int rank,
+                        evg_exchange** out, unsigned char* ipc_handle);
+int evg_exchange_connect(evg_exchange* x, const unsigned char* all_handles);
+int evg_exchange_connect_local(evg_exchange* x, void* const* peer_buffers);
+void* evg_exchange_buffer(evg_exchange* x);
+int evg_exchange_set_wait_limit(evg_exchange* x, int64_t cycles);
+int evg_exchange_sum_round(evg_exchange* x, const float* partial, int64_t count,
+                           void* out, int dtype, float* out_f32, void* stream);
+int evg_exchange_destroy(evg_exchange* x);
 
 /* ------------------------------------------------------------------ helpers
  * dst[i] = round_to_dtype(src[i]) for float32 src; used after the cross-GPU

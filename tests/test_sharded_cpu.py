@@ -153,3 +153,64 @@ def test_single_process_needs_no_group():
     assert torch.allclose(y, y_ref, atol=1e-5, rtol=1e-5)
     assert torch.allclose(dx, g_ref["dx"], atol=1e-5, rtol=1e-5)
     assert torch.allclose(dw, g_ref["dweight"], atol=1e-5, rtol=1e-5)
+
+
+class _FakeExchangeLib:
+    """Stand-in for the C ABI: records the calls a PeerExchange makes; the "kernel"
+    is an all_reduce, so two gloo ranks can run the host logic without a GPU."""
+
+    def __init__(self, rank):
+        self.rank = rank
+        self.blob = None
+        self.destroyed = 0
+
+    def call(self, name, *args):
+        import ctypes
+
+        if name == "evg_exchange_create":
+            max_floats, world, rank, out, handle = args
+            ctypes.memmove(handle, bytes([rank + 1]) * 64, 64)
+            out._obj.value = 1234
+        elif name == "evg_exchange_connect":
+            self.blob = ctypes.string_at(args[1], 128)
+        elif name == "evg_exchange_sum_round":
+            pass
+        elif name == "evg_exchange_destroy":
+            self.destroyed += 1
+        else:
+            raise AssertionError(name)
+
+
+def _peer_exchange_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from evograd_b200.sharded import PeerExchange
+
+        lib = _FakeExchangeLib(rank)
+        ex = PeerExchange(64, lib=lib)
+        # every rank receives all handles, in rank order
+        assert lib.blob == bytes([1]) * 64 + bytes([2]) * 64, lib.blob
+        with pytest.raises(ValueError):
+            ex.sum_round(torch.zeros(65), torch.float32)
+        with pytest.raises(TypeError):
+            ex.sum_round(torch.zeros(8, dtype=torch.float64), torch.float32)
+        out = ex.sum_round(torch.zeros(8), torch.bfloat16)
+        assert out.dtype == torch.bfloat16 and out.shape == (8,) and ex.calls == 1
+        ex.close()
+        ex.close()
+        assert lib.destroyed == 1
+        results[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_exchange_gathers_handles_in_rank_order():
+    world = 2
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_peer_exchange_worker, args=(world, port, results), nprocs=world, join=True)
+        assert dict(results) == {0: "ok", 1: "ok"}
