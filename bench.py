@@ -1011,7 +1011,8 @@ def parity_n(world, rank):
             if not bool((err <= bound).all()):
                 raise AssertionError(f"parity at N={world}: {kind} {nm} max-abs {errs[nm]:.3e}")
             # and every rank holds the same bits
-            lo, hi = grads[1 + i].clone().view(torch.int16), grads[1 + i].clone().view(torch.int16)
+            bits = grads[1 + i].contiguous().view(torch.int16).to(torch.int32)
+            lo, hi = bits.clone(), bits.clone()
             torch.distributed.all_reduce(lo, op=torch.distributed.ReduceOp.MIN)
             torch.distributed.all_reduce(hi, op=torch.distributed.ReduceOp.MAX)
             if not torch.equal(lo, hi):

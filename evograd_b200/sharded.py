@@ -73,8 +73,9 @@ class PeerExchange:
     """Sum of per-rank float32 vectors over the ranks of one node, rounded once,
     through peer memory: each rank owns a small device buffer, the others map it
     with CUDA IPC, and :meth:`sum_round` enqueues one single-block kernel per rank
-    that publishes this rank's values, waits (bounded) for the other ranks' and
-    adds all of them in rank order. The IPC handles travel through
+    that writes this rank's values into every rank's buffer, waits (bounded) for
+    the other ranks' values to arrive in its own and adds all of them in rank
+    order. The IPC handles travel through
     ``torch.distributed.all_gather_object`` once, at construction; every rank
     must construct the object and call :meth:`sum_round` in the same order.
 
@@ -102,14 +103,16 @@ class PeerExchange:
             lib.call("evg_exchange_connect", self._x, ctypes.cast(buf, ctypes.c_void_p))
         self.calls = 0
 
-    def sum_round(self, partial: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    def sum_round(self, partial: torch.Tensor, dtype: torch.dtype, out=None) -> torch.Tensor:
         """``partial``: contiguous float32 on this rank's device. Returns the sum over
-        ranks rounded to ``dtype`` (same shape), identical bits on every rank."""
+        ranks rounded to ``dtype`` (same shape), identical bits on every rank. The
+        kernel goes to the current stream; ``out`` may be preallocated."""
         if partial.dtype != torch.float32 or not partial.is_contiguous():
             raise TypeError("partial sums must be contiguous float32")
         if partial.numel() > self.max_floats:
             raise ValueError(f"{partial.numel()} values exceed the exchange buffer ({self.max_floats})")
-        out = torch.empty(partial.shape, dtype=dtype, device=partial.device)
+        if out is None:
+            out = torch.empty(partial.shape, dtype=dtype, device=partial.device)
         en = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
         stream = torch.cuda.current_stream(partial.device).cuda_stream if partial.is_cuda else None
         self._lib.call("evg_exchange_sum_round", self._x, partial.data_ptr(), partial.numel(),
@@ -158,7 +161,8 @@ class ShardedNorm:
 
     def exchange_name(self) -> str:
         if self._peer is not None:
-            return "peer memory: one kernel per rank reads all ranks' float32 sums (CUDA IPC)"
+            return ("peer memory: one kernel per rank writes its float32 sums into every rank's "
+                    "buffer (CUDA IPC) and adds what arrived in its own")
         return "nccl all_reduce of the float32 sums + rounding kernel"
 
     def _peer_exchange(self, partial):

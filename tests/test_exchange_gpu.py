@@ -83,7 +83,7 @@ def test_a_peer_that_never_arrives_ends_in_a_timeout_status():
 
     n = 1024
     x, _ = _create(n, 2, 0)
-    silent = torch.zeros(n * 8 + 4096, device="cuda", dtype=torch.uint8)
+    silent = torch.zeros(16 * (n * 4 + 256) + 16 * 128 + 512, device="cuda", dtype=torch.uint8)
     try:
         peers = (ctypes.c_void_p * 2)(_cabi.lib.evg_exchange_buffer(x), silent.data_ptr())
         _cabi.call("evg_exchange_connect_local", x, peers)
