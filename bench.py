@@ -1254,6 +1254,12 @@ def main():
                     help="smaller causal-attention case (profiling captures only; head_dim stays 128)")
     ap.add_argument("--rows", type=int, default=None,
                     help="fewer rows for the chosen row-wise workload (profiling captures only)")
+    ap.add_argument("--hidden", type=int, default=None,
+                    help="another row width for a norm workload (profiling captures only)")
+    ap.add_argument("--rope-batch", type=int, default=None,
+                    help="smaller batch for the rope workload (profiling captures only)")
+    ap.add_argument("--evo-shape", default=None, metavar="B,S,H,N,D",
+                    help="another evoattention case (profiling captures only)")
     args = ap.parse_args()
     if args.rows:
         cls = WORKLOADS[args.workload]
@@ -1268,6 +1274,19 @@ def main():
         b, h, sq = (int(t) for t in args.attention_shape.split(","))
         AttentionWL.B, AttentionWL.H, AttentionWL.S = b, h, sq
         AttentionWL.name = f"causal_attention_bf16_{b}x{h}x{sq}x128"
+    if args.hidden:
+        cls = WORKLOADS[args.workload]
+        if not hasattr(cls, "hidden"):
+            ap.error(f"--hidden does not apply to workload {args.workload}")
+        cls.hidden = args.hidden
+    if args.rope_batch:
+        RopeWL.B = args.rope_batch
+        RopeWL.name = f"rope_bf16_qk_{args.rope_batch}x4096x32x128"
+    if args.evo_shape:
+        b, sq, h, n, dd = (int(t) for t in args.evo_shape.split(","))
+        EvoAttentionWL.B, EvoAttentionWL.S, EvoAttentionWL.H = b, sq, h
+        EvoAttentionWL.N, EvoAttentionWL.D = n, dd
+        EvoAttentionWL.name = f"evoattention_bf16_{b}x{sq}x{h}x{n}x{dd}"
     if args.impl == "reference":
         run_reference(args)
     else:
