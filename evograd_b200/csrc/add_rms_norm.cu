@@ -217,6 +217,7 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
     bulk_load_1d(dst + 2 * row_bytes, dy + row * cols, row_bytes, &full[s]);
   };
   long long n_issued = 0;  // thread 0 only
+  bool aborted = false;    // a wait of this thread was given up
   if (tid == 0)
     for (int64_t i = 0; i < stages && i < n_mine; ++i, ++n_issued) issue(i);
 
@@ -240,7 +241,7 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       rs_next = *rstd_p;
     }
     const float rb = round_to<T>(rs);
-    mbar_wait(&full[s], parity, ctx, 411);
+    aborted |= !mbar_wait(&full[s], parity, ctx, 411);
     const uint8_t* sx = ring + (size_t)s * 3 * row_bytes;
     const uint8_t* sr = sx + row_bytes;
     const uint8_t* sg = sr + row_bytes;
@@ -284,7 +285,7 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       c[0] = lo + hi;
     }
     block_allreduce_sum_fixed<1, THREADS / 32>(c, scratch, phase);  // all done with stage s
-    if (tid == 0 && i + stages < n_mine && !*(volatile int*)abort_flag) {  // no new copies after a timeout
+    if (tid == 0 && i + stages < n_mine && !aborted) {  // no new copies after a timeout
       issue(i + stages);
       ++n_issued;
     }
@@ -320,7 +321,7 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       parity ^= 1;
     }
   }
-  if (tid == 0 && *(volatile int*)abort_flag) ring_drain(full, stages, n_issued, wait_limit);
+  if (tid == 0 && aborted) ring_drain(full, stages, n_issued, wait_limit);
   float* pw = partial + (size_t)blockIdx.x * cols;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {

@@ -225,6 +225,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
     bulk_load_1d(dst + row_bytes, dy + row * cols, row_bytes, &full[s]);
   };
   long long n_issued = 0;  // thread 0 only
+  bool aborted = false;    // a wait of this thread was given up
   if (tid == 0)
     for (int64_t i = 0; i < stages && i < n_mine; ++i, ++n_issued) issue(i);
 
@@ -267,7 +268,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
         mu_next = *mean_p;
       }
     }
-    mbar_wait(&full[s], parity, ctx, 401);
+    aborted |= !mbar_wait(&full[s], parity, ctx, 401);
     const uint8_t* sx = ring + (size_t)s * 2 * row_bytes;
     const uint8_t* sg = sx + row_bytes;
     const f32x2 rs2 = f2_splat(rs), nmr2 = f2_splat(nmr);
@@ -314,7 +315,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
       }
     }
     block_allreduce_sum_fixed<NV, THREADS / 32>(c, scratch, phase);  // all done with stage s
-    if (tid == 0 && i + stages < n_mine && !*(volatile int*)abort_flag) {  // no new copies after a timeout
+    if (tid == 0 && i + stages < n_mine && !aborted) {  // no new copies after a timeout
       issue(i + stages);
       ++n_issued;
     }
@@ -349,7 +350,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
       parity ^= 1;
     }
   }
-  if (tid == 0 && *(volatile int*)abort_flag) ring_drain(full, stages, n_issued, wait_limit);
+  if (tid == 0 && aborted) ring_drain(full, stages, n_issued, wait_limit);
   // One group per block: the partial row goes out straight from registers.
   float* pw = partial + (size_t)blockIdx.x * cols;
   float* pb = partial + ((size_t)gridDim.x + blockIdx.x) * cols;
@@ -509,7 +510,8 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
                                       (T*)dx, partial, rows, (int)hidden, stages, wait_limit);   \
     launched = true;                                                                             \
   }
-      EVG_RING(256, 1) EVG_RING(256, 2) EVG_RING(256, 4) EVG_RING(256, 8)
+      EVG_RING(256, 1) EVG_RING(256, 2) EVG_RING(256, 3) EVG_RING(256, 4) EVG_RING(256, 6)
+      EVG_RING(256, 8)
       EVG_RING(512, 1) EVG_RING(512, 2) EVG_RING(512, 4) EVG_RING(512, 8)
 #undef EVG_RING
     }

@@ -71,21 +71,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Waits for the phase with the given parity to complete, at most
 // ctx.limit_cycles; on timeout sets the abort word (code identifies the wait).
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
+// Returns false when the wait was given up (now, or by an earlier wait of the
+// block), true when the phase completed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
                                           int code) {
   // Fast path first: a phase that has already completed costs one try_wait and no
   // shared-memory load (the abort word only matters while actually waiting).
-  if (mbar_try_wait(bar, parity)) return;
-  if (*ctx.abort_flag) return;
+  if (mbar_try_wait(bar, parity)) return true;
+  if (*ctx.abort_flag) return false;
   const long long start = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (*ctx.abort_flag) return;
+    if (*ctx.abort_flag) return false;
     if (clock64() - start > ctx.limit_cycles) {
       *ctx.abort_flag = code;
       atomicCAS(ctx.device_status, 0, code);
-      return;
+      return false;
     }
   }
+  return true;
 }
 
 // After an abort the producer stops issuing copies; the ones already issued
