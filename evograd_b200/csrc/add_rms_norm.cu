@@ -216,10 +216,8 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
     bulk_load_1d(dst + row_bytes, r + row * cols, row_bytes, &full[s]);
     bulk_load_1d(dst + 2 * row_bytes, dy + row * cols, row_bytes, &full[s]);
   };
-  long long n_issued = 0;  // thread 0 only
-  bool aborted = false;    // a wait of this thread was given up
   if (tid == 0)
-    for (int64_t i = 0; i < stages && i < n_mine; ++i, ++n_issued) issue(i);
+    for (int64_t i = 0; i < stages && i < n_mine; ++i) issue(i);
 
   f32x2 acc_w[VPT][P];
 #pragma unroll
@@ -241,7 +239,7 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       rs_next = *rstd_p;
     }
     const float rb = round_to<T>(rs);
-    aborted |= !mbar_wait(&full[s], parity, ctx, 411);
+    mbar_wait(&full[s], parity, ctx, 411);
     const uint8_t* sx = ring + (size_t)s * 3 * row_bytes;
     const uint8_t* sr = sx + row_bytes;
     const uint8_t* sg = sr + row_bytes;
@@ -285,10 +283,7 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       c[0] = lo + hi;
     }
     block_allreduce_sum_fixed<1, THREADS / 32>(c, scratch, phase);  // all done with stage s
-    if (tid == 0 && i + stages < n_mine && !aborted) {  // no new copies after a timeout
-      issue(i + stages);
-      ++n_issued;
-    }
+    if (tid == 0 && i + stages < n_mine) issue(i + stages);
     const f32x2 a_s = f2_splat(-(rs * rs) * rs * (c[0] * inv_cols));
     const f32x2 rb2 = f2_splat(rb);
 #pragma unroll
@@ -321,7 +316,9 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       parity ^= 1;
     }
   }
-  if (tid == 0 && aborted) ring_drain(full, stages, n_issued, wait_limit);
+  // After a timeout every wait above fell through, so the last copies may still be
+  // in flight: give them time to land before the block's shared memory is given up.
+  if (tid == 0 && *(volatile int*)abort_flag) settle_after_abort();
   float* pw = partial + (size_t)blockIdx.x * cols;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {

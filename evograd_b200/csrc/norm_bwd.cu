@@ -224,10 +224,8 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
     bulk_load_1d(dst, x + row * cols, row_bytes, &full[s]);
     bulk_load_1d(dst + row_bytes, dy + row * cols, row_bytes, &full[s]);
   };
-  long long n_issued = 0;  // thread 0 only
-  bool aborted = false;    // a wait of this thread was given up
   if (tid == 0)
-    for (int64_t i = 0; i < stages && i < n_mine; ++i, ++n_issued) issue(i);
+    for (int64_t i = 0; i < stages && i < n_mine; ++i) issue(i);
 
   // Element-wise float32 work is done on packed pairs (f32x2): element 2p and
   // 2p+1 of a vector share one instruction.
@@ -268,7 +266,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
         mu_next = *mean_p;
       }
     }
-    aborted |= !mbar_wait(&full[s], parity, ctx, 401);
+    mbar_wait(&full[s], parity, ctx, 401);
     const uint8_t* sx = ring + (size_t)s * 2 * row_bytes;
     const uint8_t* sg = sx + row_bytes;
     const f32x2 rs2 = f2_splat(rs), nmr2 = f2_splat(nmr);
@@ -315,10 +313,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
       }
     }
     block_allreduce_sum_fixed<NV, THREADS / 32>(c, scratch, phase);  // all done with stage s
-    if (tid == 0 && i + stages < n_mine && !aborted) {  // no new copies after a timeout
-      issue(i + stages);
-      ++n_issued;
-    }
+    if (tid == 0 && i + stages < n_mine) issue(i + stages);
     // dx = rs*g - rs*mean(g) - rs*mean(g*xh)*xh
     const f32x2 a_x = f2_splat(-rs * (c[0] * inv_cols));
     const f32x2 a_0 = f2_splat(LN ? -rs * (c[1] * inv_cols) : 0.f);
@@ -350,7 +345,9 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
       parity ^= 1;
     }
   }
-  if (tid == 0 && aborted) ring_drain(full, stages, n_issued, wait_limit);
+  // After a timeout every wait above fell through, so the last copies may still be
+  // in flight: give them time to land before the block's shared memory is given up.
+  if (tid == 0 && *(volatile int*)abort_flag) settle_after_abort();
   // One group per block: the partial row goes out straight from registers.
   float* pw = partial + (size_t)blockIdx.x * cols;
   float* pb = partial + ((size_t)gridDim.x + blockIdx.x) * cols;

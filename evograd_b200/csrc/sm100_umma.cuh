@@ -100,14 +100,15 @@ __device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity, long 
   while (!mbar_try_wait(bar, parity))
     if (clock64() - start > limit_cycles) return;
 }
-// Drains the last `stages` issues of a ring whose issue number i uses barrier
-// full[i % stages] with parity (i / stages) & 1.
-__device__ __forceinline__ void ring_drain(uint64_t* full, int stages, long long n_issued,
-                                           long long limit_cycles) {
-  long long i = n_issued - stages;
-  if (i < 0) i = 0;
-  for (; i < n_issued; ++i)
-    mbar_drain(&full[i % stages], (uint32_t)((i / stages) & 1), limit_cycles);
+// For kernels whose hot loop cannot afford to track what it has issued (one
+// more live register per row costs the norm backward 3 % of its time): after a
+// timeout the issuing thread simply gives the bulk copies still in flight time
+// to land (a copy completes in a few microseconds; this waits a hundred) before
+// the block and its shared memory are given up.
+__device__ __forceinline__ void settle_after_abort() {
+  const long long start = clock64();
+  while (clock64() - start < (1ll << 18)) {
+  }
 }
 
 // TMA: global -> shared tile load, completion counted on an mbarrier.

@@ -90,16 +90,14 @@ softmax_wide_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restr
                          off, n, &sm->full[s]);
     }
   };
-  long long n_issued = 0;  // thread 0 only
-  bool aborted = false;    // a wait of this thread was given up
   if (tid == 0)
-    for (int64_t i = 0; i < stages && i < n_mine; ++i, ++n_issued) issue(i);
+    for (int64_t i = 0; i < stages && i < n_mine; ++i) issue(i);
 
   int s = 0;
   uint32_t parity = 0;
   for (int64_t i = 0; i < n_mine; ++i) {
     const int64_t row = cid + i * n_clusters;
-    if (my_nvec > 0) aborted |= !mbar_wait(&sm->full[s], parity, ctx, 421);
+    if (my_nvec > 0) mbar_wait(&sm->full[s], parity, ctx, 421);
     const uint4* sa = reinterpret_cast<const uint4*>(buf + (size_t)s * stage_bytes);
     const uint4* sb = sa + vec_per_block;
     const int par = (int)(i & 1);
@@ -166,16 +164,14 @@ softmax_wide_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restr
       }
     }
     __syncthreads();  // every thread has finished reading stage s
-    if (tid == 0 && i + stages < n_mine && !aborted) {
-      issue(i + stages);  // no new copies after a timeout
-      ++n_issued;
-    }
+    if (tid == 0 && i + stages < n_mine) issue(i + stages);
     if (++s == stages) {
       s = 0;
       parity ^= 1;
     }
   }
-  if (tid == 0 && my_nvec > 0 && aborted) ring_drain(sm->full, stages, n_issued, wait_limit);
+  // after a timeout the last copies may still be in flight: give them time to land
+  if (tid == 0 && my_nvec > 0 && *(volatile int*)&sm->abort_flag) settle_after_abort();
   // No block may leave while a peer can still write into its slots: the last
   // write to this block happens before the last cluster barrier it passed.
 }
