@@ -1164,7 +1164,21 @@ def run_ours(args):
 # captures: bytes (already scaled to the bench's row count where the capture ran
 # on fewer rows), the file the summary of the capture is in, the kernel sources
 # the capture belongs to and the digest of those sources when it was taken.
-TRAFFIC_NCU = {}
+_ROW_HEADERS = ["evg_common.cuh", "rowcfg.cuh", "norm_reduce.cuh", "sm100_umma.cuh"]
+TRAFFIC_NCU = {
+    # filled in from the captures summarised under profiles/ (python bench.py --source-digest NAME
+    # prints the digest of a workload's kernel sources as they are now)
+}
+TRAFFIC_SOURCES = {
+    "layernorm": ["norm_bwd.cu", *_ROW_HEADERS],
+    "rmsnorm": ["norm_bwd.cu", *_ROW_HEADERS],
+    "fused_add_rms_norm": ["add_rms_norm.cu", *_ROW_HEADERS],
+    "geglu": ["glu.cu", "evg_common.cuh"],
+    "swiglu": ["glu.cu", "evg_common.cuh"],
+    "softmax_vocab": ["softmax_wide.cu", "softmax_wide.cuh", "evg_common.cuh", "sm100_umma.cuh"],
+    "softmax": ["softmax.cu", "evg_common.cuh", "rowcfg.cuh"],
+    "rope": ["rope.cu", "evg_common.cuh"],
+}
 
 
 def _source_digest(files):
@@ -1245,6 +1259,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="layernorm")
+    ap.add_argument("--source-digest", default=None, metavar="WORKLOAD",
+                    help="print the digest of a workload's kernel sources and exit")
     ap.add_argument("--no-per-op", action="store_true", help="skip the per-operator table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
@@ -1261,6 +1277,9 @@ def main():
     ap.add_argument("--evo-shape", default=None, metavar="B,S,H,N,D",
                     help="another evoattention case (profiling captures only)")
     args = ap.parse_args()
+    if args.source_digest:
+        print(_source_digest(TRAFFIC_SOURCES[args.source_digest]))
+        return
     if args.rows:
         cls = WORKLOADS[args.workload]
         if not hasattr(cls, "rows"):
