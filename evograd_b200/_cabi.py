@@ -159,6 +159,16 @@ SIGNATURES = {
     "evg_exchange_sum_round": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_void_p,
                                        c_void_p]),
     "evg_exchange_destroy": (c_int, [c_void_p]),
+    "evg_layernorm_bwd_exchange": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p],
+    ),
+    "evg_rmsnorm_bwd_exchange": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+         c_int64, c_int, c_void_p, c_void_p],
+    ),
     "evg_device_status": (c_int, [c_int]),
     "evg_cast_from_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "evg_flush_l2": (c_int, [c_void_p, c_int64, c_void_p]),

@@ -3,84 +3,41 @@
 //
 // Every rank owns one small buffer in its own device memory that the other ranks
 // of the node map through CUDA IPC; it holds, twice (two slots), one area per
-// source rank. One single-block kernel per rank and step
+// source rank. A step of a rank
 //   1. takes the next epoch e from a counter in device memory (so a captured
 //      graph that is replayed keeps counting),
-//   2. WRITES the rank's float32 partial sums into its area of slot e % 2 in
-//      every rank's buffer (plain peer stores, no multicast) and then publishes
-//      them with one release store of e per destination,
-//   3. waits, with a cycle budget, until all of its OWN flags of slot e % 2 read
-//      e: it polls local memory, so no poll and no data read crosses the link,
-//   4. adds the areas of all ranks in rank order, so every rank forms the same
-//      bits, rounds once to the parameter dtype and writes the result.
-// Two slots are enough: rank r overwrites its area of slot e % 2 in rank p's
-// buffer at epoch e + 2, which r reaches only after it has seen p's flag e + 1,
-// and p sends e + 1 only after its own reads of epoch e have finished.
+//   2. WRITES each of its float32 sums, paired with e in one 64-bit store, into
+//      its area of slot e % 2 in every rank's buffer (plain peer stores, no
+//      multicast),
+//   3. polls, element by element and with a cycle budget, the pairs in its OWN
+//      buffer until each source rank's pair carries e: no poll and no data read
+//      crosses the link, and there is no fence and no separate flag (a
+//      release store at system scope per step cost 10 us more than all the rest),
+//   4. adds the values in rank order, so every rank forms the same bits, rounds
+//      once to the parameter dtype and writes the result.
+// Two slots are enough: a rank overwrites its areas of slot e % 2 at epoch e + 2,
+// which it reaches only after it has read every rank's pairs of epoch e + 1, and
+// a rank writes e + 1 only after its own reads of epoch e have finished.
 // A wait that runs out records EVG_ETIMEOUT in the sticky device status and the
 // kernel returns (its results are then undefined); nothing spins without a bound.
 // Kernels of different ranks wait on one another, so the ranks must be on
 // different GPUs.
+// The kernel here handles a whole vector in one block (evg_exchange_sum_round);
+// the normalisation backward runs the same protocol inside the second stage of
+// its column reduction, block by block (colreduce_exchange_kernel).
 #include <cstring>
 
 #include "evg_common.cuh"
+#include "exchange.cuh"
 
 namespace evg {
 namespace {
 
-constexpr int kMaxRanks = 8;
+using namespace xchg;
+
 constexpr int kExchangeThreads = 1024;
-constexpr int kExchangeWaitId = 951;
 
 __device__ int g_exchange_status = 0;
-
-// Layout of a rank's buffer: [slot][source rank] data areas, then
-// [slot][source rank] flags (one 128-byte line each), then the epoch counter.
-struct Layout {
-  int64_t max_floats;
-  __host__ __device__ size_t area_bytes() const { return ((size_t)max_floats * 4 + 255) & ~(size_t)255; }
-  __host__ __device__ size_t area_offset(int slot, int src) const {
-    return (size_t)(slot * kMaxRanks + src) * area_bytes();
-  }
-  __host__ __device__ size_t flag_offset(int slot, int src) const {
-    return 2 * kMaxRanks * area_bytes() + (size_t)(slot * kMaxRanks + src) * 128;
-  }
-  __host__ __device__ size_t counter_offset() const {
-    return 2 * kMaxRanks * area_bytes() + 2 * kMaxRanks * 128;
-  }
-  __host__ __device__ size_t total_bytes() const { return counter_offset() + 256; }
-};
-
-struct Peers {
-  uint8_t* base[kMaxRanks];
-};
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ float4 ld_relaxed_sys_f32x4(const float* p) {
-  float4 v;
-  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-
-template <typename T>
-__device__ __forceinline__ void write_sum(T* out, float* out_f32, int64_t i, float v) {
-  if (out) out[i] = from_f32<T>(v);
-  if (out_f32) out_f32[i] = v;
-}
 
 template <typename T>
 __global__ void __launch_bounds__(kExchangeThreads)
@@ -96,76 +53,33 @@ exchange_sum_round_kernel(Peers peers, Layout lay, int n_ranks, int rank,
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const int slot = (int)(epoch & 1u);
-  const bool vec = (count & 3) == 0 && (reinterpret_cast<uintptr_t>(partial) & 15u) == 0;
-  // 2. this rank's values into its area in every rank's buffer (its own included)
-  if (vec) {
-    for (int64_t j = threadIdx.x; j < count / 4; j += blockDim.x) {
-      const float4 v = reinterpret_cast<const float4*>(partial)[j];
+  for (int64_t i = threadIdx.x; i < count; i += blockDim.x) {
+    const float v = partial[i];
 #pragma unroll
-      for (int p = 0; p < kMaxRanks; ++p)
-        if (p < n_ranks)
-          reinterpret_cast<float4*>(peers.base[p] + lay.area_offset(slot, rank))[j] = v;
-    }
-  } else {
-    for (int64_t i = threadIdx.x; i < count; i += blockDim.x) {
-      const float v = partial[i];
-#pragma unroll
-      for (int p = 0; p < kMaxRanks; ++p)
-        if (p < n_ranks)
-          reinterpret_cast<float*>(peers.base[p] + lay.area_offset(slot, rank))[i] = v;
-    }
+    for (int p = 0; p < kMaxRanks; ++p)
+      if (p < n_ranks)
+        st_pair_sys(reinterpret_cast<uint2*>(peers.base[p] + lay.pair_area_offset(slot, rank)) + i, v,
+                    epoch);
   }
-  __syncthreads();
-  // One release store at system scope per destination publishes the values: the
-  // block barrier orders every thread's writes before it (a system-wide fence in
-  // every thread costs tens of microseconds).
-  if ((int)threadIdx.x < n_ranks)
-    st_release_sys(
-        reinterpret_cast<uint32_t*>(peers.base[threadIdx.x] + lay.flag_offset(slot, rank)), epoch);
-  // 3. wait for every source rank's flag in this rank's own buffer
-  if ((int)threadIdx.x < n_ranks) {
-    const uint32_t* flag =
-        reinterpret_cast<const uint32_t*>(mine + lay.flag_offset(slot, threadIdx.x));
-    const long long start = clock64();
-    while (ld_acquire_sys(flag) != epoch) {
-      if (clock64() - start > wait_limit) {
-        atomicCAS(&g_exchange_status, 0, kExchangeWaitId);
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  // 4. After a timeout the sums below read whatever the areas hold; the host learns
-  // of it from the status word. The sum runs over the ranks in rank order on
-  // every rank.
-  if (vec) {
-    for (int64_t j = threadIdx.x; j < count / 4; j += blockDim.x) {
-      float4 v[kMaxRanks];
-#pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < n_ranks)
-          v[r] = ld_relaxed_sys_f32x4(
-              reinterpret_cast<const float*>(mine + lay.area_offset(slot, r)) + 4 * j);
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < n_ranks) {
-          acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w;
+  const long long start = clock64();
+  bool gave_up = false;
+  for (int64_t i = threadIdx.x; i < count; i += blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < n_ranks; ++r) {
+      const uint2* cell = reinterpret_cast<const uint2*>(mine + lay.pair_area_offset(slot, r)) + i;
+      uint2 v = ld_pair_sys(cell);
+      while (v.y != epoch && !gave_up) {
+        if (clock64() - start > wait_limit) {
+          atomicCAS(&g_exchange_status, 0, kExchangeWaitId);
+          gave_up = true;  // the remaining elements are read as they are
+          break;
         }
-      write_sum<T>(out, out_f32, 4 * j + 0, acc.x);
-      write_sum<T>(out, out_f32, 4 * j + 1, acc.y);
-      write_sum<T>(out, out_f32, 4 * j + 2, acc.z);
-      write_sum<T>(out, out_f32, 4 * j + 3, acc.w);
+        v = ld_pair_sys(cell);
+      }
+      acc += __uint_as_float(v.x);
     }
-  } else {
-    for (int64_t i = threadIdx.x; i < count; i += blockDim.x) {
-      float acc = 0.f;
-#pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < n_ranks)
-          acc += ld_relaxed_sys_f32(reinterpret_cast<const float*>(mine + lay.area_offset(slot, r)) + i);
-      write_sum<T>(out, out_f32, i, acc);
-    }
+    if (out) out[i] = from_f32<T>(acc);
+    if (out_f32) out_f32[i] = acc;
   }
 }
 
@@ -187,18 +101,6 @@ const bool g_exchange_registered = (register_device_status(read_exchange_status)
 }  // namespace evg
 
 using namespace evg;
-
-struct evg_exchange {
-  Layout lay;
-  int n_ranks = 0;
-  int rank = 0;
-  int device = 0;
-  bool connected = false;
-  void* local = nullptr;             // cudaMalloc'ed by create
-  void* opened[kMaxRanks] = {};      // cudaIpcOpenMemHandle results (to close)
-  Peers peers{};
-  long long wait_limit = 4000000000ll;
-};
 
 extern "C" int evg_exchange_create(int64_t max_floats, int n_ranks, int rank, evg_exchange** out,
                                    unsigned char* ipc_handle) {

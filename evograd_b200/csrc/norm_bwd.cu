@@ -457,7 +457,7 @@ template <typename T, bool LN>
 int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* mean,
                     const float* rstd, void* dx, void* dweight, void* dbias, float* out_f32,
                     void* workspace, int64_t workspace_bytes, int64_t rows, int64_t hidden,
-                    cudaStream_t stream, int64_t block_limit = 0) {
+                    cudaStream_t stream, int64_t block_limit = 0, evg_exchange* xchg = nullptr) {
   constexpr int N = Vec<T>::N;
   constexpr int NV = LN ? 2 : 1;
   const char* op = LN ? "layernorm_bwd" : "rmsnorm_bwd";
@@ -567,6 +567,16 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
   if (rc) return rc;
   if ((int64_t)blocks * hidden * NV * (int64_t)sizeof(float) > workspace_bytes)
     return fail(EVG_EWORKSPACE, "%s: internal: partial rows exceed workspace", op);
+  if (xchg) {
+    // stage 2 and the sum over ranks in one kernel
+    dim3 grid((unsigned)((hidden + 31) / 32), NV);
+    int* status = nullptr;
+    cudaGetSymbolAddress((void**)&status, g_norm_device_status);
+    colreduce_exchange_kernel<T><<<grid, dim3(32, 32), 0, stream>>>(
+        partial, blocks, hidden, (T*)dweight, (T*)dbias, xchg->peers, xchg->lay, xchg->n_ranks,
+        xchg->rank, xchg->wait_limit, status);
+    return check_launch("norm_bwd colreduce + exchange");
+  }
   if (dweight || dbias || out_f32) {
     dim3 grid((unsigned)((hidden + 31) / 32), NV);
     colreduce_kernel<T><<<grid, dim3(32, 32), 0, stream>>>(partial, blocks, hidden, (T*)dweight,
@@ -623,6 +633,60 @@ extern "C" int evg_rmsnorm_bwd(const void* dy, const void* x, const void* weight
     return launch_norm_bwd<T, false>(dy, x, weight, nullptr, rstd, dx, dweight, nullptr,
                                      dweight_f32, workspace, workspace_bytes, rows, hidden,
                                      (cudaStream_t)stream);
+  });
+}
+
+// ------------------------------------------------------------------------
+// Backward over a row shard with the parameter gradients summed over the ranks
+// of an exchange (one process per GPU): stage 2 of the column reduction and the
+// cross-GPU sum are one kernel.
+namespace {
+int check_exchange(const char* op, const evg_exchange* x, int64_t hidden, int nv) {
+  if (!x) return fail(EVG_ENULL, "%s: null exchange handle", op);
+  if (!x->connected) return fail(EVG_EUNSUPPORTED, "%s: the exchange's peers are not connected", op);
+  if ((int64_t)nv * hidden > x->lay.max_floats)
+    return fail(EVG_EUNSUPPORTED, "%s: %lld values exceed the exchange buffer (%lld)", op,
+                (long long)((int64_t)nv * hidden), (long long)x->lay.max_floats);
+  if ((hidden + 31) / 32 * nv > xchg::kMaxBlocks)
+    return fail(EVG_EUNSUPPORTED, "%s: hidden=%lld needs more than %d exchange blocks", op,
+                (long long)hidden, xchg::kMaxBlocks);
+  return EVG_OK;
+}
+}  // namespace
+
+extern "C" int evg_layernorm_bwd_exchange(const void* dy, const void* x, const void* weight,
+                                          const float* mean, const float* rstd, void* dx,
+                                          void* dweight, void* dbias, void* workspace,
+                                          int64_t workspace_bytes, int64_t rows, int64_t hidden,
+                                          int dtype, evg_exchange* exchange, void* stream) {
+  if (!dy || !x || !weight || !mean || !rstd || !dx || !dweight || !dbias)
+    return fail(EVG_ENULL, "layernorm_bwd_exchange: null pointer argument");
+  if (rows <= 0 || hidden <= 0)
+    return fail(EVG_EBADSHAPE, "layernorm_bwd_exchange: rows=%lld hidden=%lld (rows must be >= 1)",
+                (long long)rows, (long long)hidden);
+  if (int rc = check_exchange("layernorm_bwd_exchange", exchange, hidden, 2)) return rc;
+  return EVG_DISPATCH_DTYPE(dtype, [&] {
+    return launch_norm_bwd<T, true>(dy, x, weight, mean, rstd, dx, dweight, dbias, nullptr,
+                                    workspace, workspace_bytes, rows, hidden,
+                                    (cudaStream_t)stream, 0, exchange);
+  });
+}
+
+extern "C" int evg_rmsnorm_bwd_exchange(const void* dy, const void* x, const void* weight,
+                                        const float* rstd, void* dx, void* dweight,
+                                        void* workspace, int64_t workspace_bytes, int64_t rows,
+                                        int64_t hidden, int dtype, evg_exchange* exchange,
+                                        void* stream) {
+  if (!dy || !x || !weight || !rstd || !dx || !dweight)
+    return fail(EVG_ENULL, "rmsnorm_bwd_exchange: null pointer argument");
+  if (rows <= 0 || hidden <= 0)
+    return fail(EVG_EBADSHAPE, "rmsnorm_bwd_exchange: rows=%lld hidden=%lld (rows must be >= 1)",
+                (long long)rows, (long long)hidden);
+  if (int rc = check_exchange("rmsnorm_bwd_exchange", exchange, hidden, 1)) return rc;
+  return EVG_DISPATCH_DTYPE(dtype, [&] {
+    return launch_norm_bwd<T, false>(dy, x, weight, nullptr, rstd, dx, dweight, nullptr, nullptr,
+                                     workspace, workspace_bytes, rows, hidden,
+                                     (cudaStream_t)stream, 0, exchange);
   });
 }
 

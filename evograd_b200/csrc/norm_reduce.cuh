@@ -2,6 +2,7 @@
 // partial rows and the second stage of the atomic-free column reduction.
 #pragma once
 #include "evg_common.cuh"
+#include "exchange.cuh"
 
 namespace evg {
 
@@ -39,6 +40,78 @@ colreduce_kernel(const float* __restrict__ partial, int blocks, int64_t cols, T*
     if (out) out[col] = from_f32<T>(t);
     if (out_f32) out_f32[(size_t)which * cols + col] = t;
   }
+}
+
+// Stage 2 fused with the cross-GPU sum. Every block adds the partial rows of its
+// 32 columns as above and then, on its own, takes the next epoch e from its own
+// counter in the rank's exchange buffer and writes each of its 32 sums, paired
+// with e in one 8-byte store, into its area of slot e % 2 in EVERY rank's buffer
+// (plain peer stores, no multicast). The thread that owns a column then polls
+// the pairs of that column in its OWN rank's buffer until each source rank's
+// pair carries e, adds the values in rank order and rounds: no fence, no
+// separate flag, no poll across the link, no block waiting for another block of
+// its grid, and bit-identical results on every rank. Two slots are enough: a
+// block reaches epoch e + 2 only after it has read every rank's pair of epoch
+// e + 1, which a rank writes only after its reads of epoch e. A wait that runs
+// out records the wait's id in *status and the thread goes on with what it has.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+colreduce_exchange_kernel(const float* __restrict__ partial, int blocks, int64_t cols, T* out_w,
+                          T* out_b, xchg::Peers peers, xchg::Layout lay, int n_ranks, int rank,
+                          long long wait_limit, int* status) {
+  using namespace xchg;
+  __shared__ float tile[32][33];
+  __shared__ uint32_t s_epoch;
+  const int which = blockIdx.y;
+  const int bid = blockIdx.y * gridDim.x + blockIdx.x;
+  const float* src = partial + (size_t)which * blocks * cols;
+  const int64_t col = (int64_t)blockIdx.x * 32 + threadIdx.x;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (col < cols) {
+    int p = threadIdx.y;
+    for (; p + 96 < blocks; p += 128) {
+      s0 += src[(size_t)p * cols + col];
+      s1 += src[(size_t)(p + 32) * cols + col];
+      s2 += src[(size_t)(p + 64) * cols + col];
+      s3 += src[(size_t)(p + 96) * cols + col];
+    }
+    for (; p < blocks; p += 32) s0 += src[(size_t)p * cols + col];
+  }
+  tile[threadIdx.y][threadIdx.x] = (s0 + s1) + (s2 + s3);
+  uint8_t* mine = peers.base[rank];
+  if (threadIdx.x == 0 && threadIdx.y == 0) {
+    uint32_t* counter = reinterpret_cast<uint32_t*>(mine + lay.block_counter_offset(bid));
+    s_epoch = ++*counter;
+  }
+  __syncthreads();
+  if (threadIdx.y != 0 || col >= cols) return;  // warp 0: one thread per column
+  const uint32_t epoch = s_epoch;
+  const int slot = (int)(epoch & 1u);
+  const size_t elem = (size_t)which * cols + (size_t)col;
+  float t = tile[0][threadIdx.x];
+#pragma unroll
+  for (int i = 1; i < 32; ++i) t += tile[i][threadIdx.x];
+#pragma unroll
+  for (int p = 0; p < kMaxRanks; ++p)
+    if (p < n_ranks)
+      st_pair_sys(reinterpret_cast<uint2*>(peers.base[p] + lay.pair_area_offset(slot, rank)) + elem, t,
+                  epoch);
+  float acc = 0.f;
+  const long long start = clock64();
+  for (int r = 0; r < n_ranks; ++r) {
+    const uint2* cell = reinterpret_cast<const uint2*>(mine + lay.pair_area_offset(slot, r)) + elem;
+    uint2 v = ld_pair_sys(cell);
+    while (v.y != epoch) {
+      if (clock64() - start > wait_limit) {
+        atomicCAS(status, 0, kFusedExchangeWaitId);
+        break;
+      }
+      v = ld_pair_sys(cell);
+    }
+    acc += __uint_as_float(v.x);
+  }
+  T* out = which == 0 ? out_w : out_b;
+  if (out) out[col] = from_f32<T>(acc);
 }
 #endif  // __CUDACC__
 

@@ -116,13 +116,16 @@ def layernorm_fwd(x, weight, bias, eps: float = 1e-5):
     return y.view(x.shape), mean, rstd
 
 
-def layernorm_bwd(dy, x, weight, mean, rstd, *, partials_f32: bool = False):
+def layernorm_bwd(dy, x, weight, mean, rstd, *, partials_f32: bool = False, exchange=None):
     """Returns ``(dx, dweight, dbias)``.
 
     With ``partials_f32`` the parameter gradients come back as ONE float32
     tensor ``[2, hidden]`` (row 0 dweight, row 1 dbias) instead of two tensors in
     the parameter dtype, for callers that sum them across ranks before rounding:
-    ``(dx, dwdb_f32, None)``.
+    ``(dx, dwdb_f32, None)``. With ``exchange`` (a connected
+    :class:`evograd_b200.sharded.PeerExchange`; x and dy are this rank's row
+    shard) dweight / dbias are the sums over ALL ranks' rows, formed inside the
+    second stage of the column reduction, rounded once, identical on every rank.
     """
     dev = _require_cuda(dy, x, weight, mean, rstd)
     _same("dy", dy, "x", x)
@@ -143,6 +146,14 @@ def layernorm_bwd(dy, x, weight, mean, rstd, *, partials_f32: bool = False):
     with torch.cuda.device(dev):
         ws_bytes = lib.evg_layernorm_bwd_workspace_bytes(rows, hidden, en)
         ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+        if exchange is not None and not partials_f32:
+            dwdb2 = torch.empty(2, hidden, device=dev, dtype=x.dtype)
+            call("evg_layernorm_bwd_exchange", g2.data_ptr(), x2.data_ptr(),
+                 weight.contiguous().data_ptr(), mean.contiguous().data_ptr(),
+                 rstd.contiguous().data_ptr(), dx.data_ptr(), dwdb2[0].data_ptr(),
+                 dwdb2[1].data_ptr(), ws.data_ptr(), ws_bytes, rows, hidden, en, exchange.handle,
+                 _stream(dev))
+            return dx.view(x.shape), dwdb2[0], dwdb2[1]
         if partials_f32:
             dwdb = torch.empty(2, hidden, device=dev, dtype=torch.float32)
             dweight = dbias = None
@@ -176,8 +187,9 @@ def rmsnorm_fwd(x, weight, eps: float = 1e-5):
     return y.view(x.shape), rstd
 
 
-def rmsnorm_bwd(dy, x, weight, rstd, *, partials_f32: bool = False):
-    """Returns ``(dx, dweight)``; ``dweight`` is float32 when ``partials_f32``."""
+def rmsnorm_bwd(dy, x, weight, rstd, *, partials_f32: bool = False, exchange=None):
+    """Returns ``(dx, dweight)``; ``dweight`` is float32 when ``partials_f32``. With
+    ``exchange`` (see :func:`layernorm_bwd`) dweight is the sum over all ranks' rows."""
     dev = _require_cuda(dy, x, weight, rstd)
     _same("dy", dy, "x", x)
     _check_param("weight", weight, x)
@@ -195,6 +207,12 @@ def rmsnorm_bwd(dy, x, weight, rstd, *, partials_f32: bool = False):
         ws_bytes = lib.evg_rmsnorm_bwd_workspace_bytes(rows, hidden, en)
         ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
         dweight = torch.empty(hidden, device=dev, dtype=out_dtype)
+        if exchange is not None and not partials_f32:
+            call("evg_rmsnorm_bwd_exchange", g2.data_ptr(), x2.data_ptr(),
+                 weight.contiguous().data_ptr(), rstd.contiguous().data_ptr(), dx.data_ptr(),
+                 dweight.data_ptr(), ws.data_ptr(), ws_bytes, rows, hidden, en, exchange.handle,
+                 _stream(dev))
+            return dx.view(x.shape), dweight
         call("evg_rmsnorm_bwd", g2.data_ptr(), x2.data_ptr(), weight.contiguous().data_ptr(),
              rstd.contiguous().data_ptr(), dx.data_ptr(),
              None if partials_f32 else dweight.data_ptr(),

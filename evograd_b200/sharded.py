@@ -95,6 +95,7 @@ class PeerExchange:
         lib.call("evg_exchange_create", self.max_floats, self.world, self.rank,
                  ctypes.byref(out), ctypes.cast(handle, ctypes.c_void_p))
         self._x = out
+        self.handle = out  # what the C entry points that take an exchange expect
         if self.world > 1:
             gathered = [None] * self.world
             dist.all_gather_object(gathered, bytes(handle), group=group)
@@ -161,8 +162,8 @@ class ShardedNorm:
 
     def exchange_name(self) -> str:
         if self._peer is not None:
-            return ("peer memory: one kernel per rank writes its float32 sums into every rank's "
-                    "buffer (CUDA IPC) and adds what arrived in its own")
+            return ("peer memory (CUDA IPC): the column-reduce kernel's blocks write their float32 "
+                    "sums into every rank's buffer and add what arrived in their own")
         return "nccl all_reduce of the float32 sums + rounding kernel"
 
     def _peer_exchange(self, partial):
@@ -211,6 +212,18 @@ class ShardedNorm:
         """Returns ``(dx_shard, dweight[, dbias])`` with the parameter gradients
         summed over ALL ranks' rows and rounded once, identical on every rank."""
         world, _ = _world(self.group)
+        # LayerNorm / RMSNorm with a peer exchange: the cross-rank sum happens inside the
+        # second stage of the column reduction, no separate launch.
+        if world > 1 and self.kind != "fused_add_rms_norm" and dy_shard.is_cuda:
+            weight = saved[1]
+            peer = self._peer_exchange(dy_shard)
+            nv = 2 if self.kind == "layernorm" else 1
+            if peer is not None and nv * weight.numel() <= peer.max_floats:
+                if self.kind == "layernorm":
+                    x, weight, mean, rstd = saved
+                    return self.k.layernorm_bwd(dy_shard, x, weight, mean, rstd, exchange=peer)
+                x, weight, rstd = saved
+                return self.k.rmsnorm_bwd(dy_shard, x, weight, rstd, exchange=peer)
         if self.kind == "layernorm":
             x, weight, mean, rstd = saved
             dx, partial, _ = self.k.layernorm_bwd(dy_shard, x, weight, mean, rstd, partials_f32=True)

@@ -406,6 +406,27 @@ int evg_exchange_set_wait_limit(evg_exchange* x, int64_t cycles);
 int evg_exchange_sum_round(evg_exchange* x, const float* partial, int64_t count,
                            void* out, int dtype, float* out_f32, void* stream);
 int evg_exchange_destroy(evg_exchange* x);
+/*
+ * LayerNorm / RMSNorm backward over this rank's row shard with dweight (and
+ * dbias) summed over the ranks of `exchange`: as evg_layernorm_bwd /
+ * evg_rmsnorm_bwd, but the second stage of the column reduction also does the
+ * cross-GPU sum, block by block (every block of 32 columns exchanges its own
+ * sums; no extra launch). dweight / dbias receive the sums over ALL ranks'
+ * rows, rounded once, identical on every rank. Every rank must make the same
+ * sequence of calls on the exchange; workspace as for the plain entry points.
+ * No counterpart in the reference.
+ */
+int evg_layernorm_bwd_exchange(const void* dy, const void* x, const void* weight,
+                               const float* mean, const float* rstd, void* dx,
+                               void* dweight, void* dbias, void* workspace,
+                               int64_t workspace_bytes, int64_t rows,
+                               int64_t hidden, int dtype, evg_exchange* exchange,
+                               void* stream);
+int evg_rmsnorm_bwd_exchange(const void* dy, const void* x, const void* weight,
+                             const float* rstd, void* dx, void* dweight,
+                             void* workspace, int64_t workspace_bytes,
+                             int64_t rows, int64_t hidden, int dtype,
+                             evg_exchange* exchange, void* stream);
 
 /* ------------------------------------------------------------------ helpers
  * dst[i] = round_to_dtype(src[i]) for float32 src; used after the cross-GPU

@@ -83,7 +83,7 @@ def test_a_peer_that_never_arrives_ends_in_a_timeout_status():
 
     n = 1024
     x, _ = _create(n, 2, 0)
-    silent = torch.zeros(16 * (n * 4 + 256) + 16 * 128 + 512, device="cuda", dtype=torch.uint8)
+    silent = torch.zeros(48 * (n * 4 + 256) + 64 * 1024, device="cuda", dtype=torch.uint8)
     try:
         peers = (ctypes.c_void_p * 2)(_cabi.lib.evg_exchange_buffer(x), silent.data_ptr())
         _cabi.call("evg_exchange_connect_local", x, peers)
@@ -97,6 +97,67 @@ def test_a_peer_that_never_arrives_ends_in_a_timeout_status():
         assert torch.isfinite(y[0] if isinstance(y, tuple) else y).all()
     finally:
         _cabi.call("evg_exchange_destroy", x)
+
+
+class _Handle:
+    def __init__(self, x):
+        self.handle = x
+
+
+@pytest.mark.parametrize("op,rows,hidden,dtype", [
+    ("layernorm", 700, 4096, torch.bfloat16), ("rmsnorm", 700, 4096, torch.bfloat16),
+    ("layernorm", 33, 1000, torch.float32), ("rmsnorm", 2049, 1024, torch.float16),
+])
+def test_fused_column_reduce_and_exchange_with_one_rank(op, rows, hidden, dtype):
+    """With one rank the sum over ranks is the rank's own sum: the fused second stage
+    must give the bits of the plain backward, step after step (the slots alternate)."""
+    from evograd_b200 import _cabi, ops
+
+    x_h, _ = _create(2 * hidden, 1, 0)
+    try:
+        for seed in (1, 2, 3):
+            g = torch.Generator(device="cuda").manual_seed(seed)
+            x = torch.randn(rows, hidden, device="cuda", generator=g).to(dtype)
+            dy = torch.randn(rows, hidden, device="cuda", generator=g).to(dtype)
+            w = torch.randn(hidden, device="cuda", generator=g).to(dtype)
+            if op == "layernorm":
+                b = torch.randn(hidden, device="cuda", generator=g).to(dtype)
+                _, mean, rstd = ops.layernorm_fwd(x, w, b, 1e-5)
+                ref = ops.layernorm_bwd(dy, x, w, mean, rstd)
+                got = ops.layernorm_bwd(dy, x, w, mean, rstd, exchange=_Handle(x_h))
+            else:
+                _, rstd = ops.rmsnorm_fwd(x, w, 1e-6)
+                ref = ops.rmsnorm_bwd(dy, x, w, rstd)
+                got = ops.rmsnorm_bwd(dy, x, w, rstd, exchange=_Handle(x_h))
+            for a, b_ in zip(ref, got):
+                assert torch.equal(a, b_)
+        ops.device_status()
+    finally:
+        _cabi.call("evg_exchange_destroy", x_h)
+
+
+def test_fused_exchange_gives_up_on_a_silent_peer():
+    from evograd_b200 import _cabi, ops
+    from evograd_b200._cabi import EvgError
+
+    hidden = 1024
+    x_h, _ = _create(2 * hidden, 2, 0)
+    silent = torch.zeros(48 * (2 * hidden * 4 + 256) + 64 * 1024, device="cuda", dtype=torch.uint8)
+    try:
+        peers = (ctypes.c_void_p * 2)(_cabi.lib.evg_exchange_buffer(x_h), silent.data_ptr())
+        _cabi.call("evg_exchange_connect_local", x_h, peers)
+        _cabi.call("evg_exchange_set_wait_limit", x_h, 2_000_000)
+        x = torch.randn(64, hidden, device="cuda").to(torch.bfloat16)
+        w = torch.ones(hidden, device="cuda", dtype=torch.bfloat16)
+        _, rstd = ops.rmsnorm_fwd(x, w, 1e-6)
+        ops.rmsnorm_bwd(x, x, w, rstd, exchange=_Handle(x_h))
+        with pytest.raises(EvgError, match="EVG_ETIMEOUT"):
+            ops.device_status()
+        ops.device_status()
+        dx, dw = ops.rmsnorm_bwd(x, x, w, rstd)  # the context keeps working
+        assert torch.isfinite(dx.float()).all() and torch.isfinite(dw.float()).all()
+    finally:
+        _cabi.call("evg_exchange_destroy", x_h)
 
 
 def test_argument_checks():
