@@ -365,11 +365,11 @@ int evg_selftest_bounded_wait(int64_t limit_cycles, int* observed_abort_word,
 /* ------------------------------------------------- cross-GPU parameter sums
  * One process per GPU; LayerNorm / RMSNorm over a row shard leave every rank
  * with float32 partial sums of dweight (and dbias) over its own rows. These
- * calls add the partial sums of all ranks of ONE node and round once, in a
- * single small kernel per rank that writes its sums into the other ranks'
- * buffers through peer memory (CUDA IPC mappings, plain stores, no multicast)
- * and then adds what arrived in its own: every rank adds in rank order and
- * therefore obtains the same bits. They replace an
+ * calls add the partial sums of all ranks of ONE node and round once: a rank
+ * writes each sum, paired with a step counter in one 64-bit store, into the
+ * other ranks' buffers through peer memory (CUDA IPC mappings, plain stores,
+ * no multicast) and then adds what arrived in its own; every rank adds in
+ * rank order and therefore obtains the same bits. They replace an
  * all_reduce(SUM) of the float32 sums followed by evg_cast_from_f32.
  * No counterpart in the reference (its --gpus option runs independent
  * searches; nothing there shards an operator).
