@@ -447,7 +447,7 @@ struct BwdPlan {
 // `block_limit` > 0 bounds the number of partial rows (callers with a fixed scratch).
 template <typename T, bool LN>
 int64_t norm_bwd_workspace(int64_t rows, int64_t hidden, int64_t block_limit = 0) {
-  int64_t blocks = max_partial_blocks();
+  int64_t blocks = max_partial_blocks(hidden);
   if (block_limit > 0 && blocks > block_limit) blocks = block_limit;
   if (blocks > rows) blocks = rows > 0 ? rows : 1;
   return blocks * hidden * (LN ? 2 : 1) * (int64_t)sizeof(float);
@@ -467,7 +467,7 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
                 (long long)workspace_bytes, (long long)need);
   if (!aligned16(workspace)) return fail(EVG_EALIGN, "%s: workspace not 16-byte aligned", op);
   float* partial = (float*)workspace;
-  int cap = max_partial_blocks();
+  int cap = max_partial_blocks(hidden);
   if (block_limit > 0 && cap > block_limit) cap = (int)block_limit;
   int blocks = 0;
   const bool vec_ok = hidden % N == 0 && aligned16(x) && aligned16(dy) && aligned16(dx) &&
@@ -513,19 +513,22 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
 #undef EVG_RING
     }
   }
-  if (LN && narrow_rows && hidden / N <= 128 && !tune("rows.force_generic") &&
-      !tune("layernorm_bwd.group")) {
-    // LayerNorm keeps two column sums per element, so rows of up to 128 vectors use two
-    // vectors per thread (32 accumulators) rather than four: groups of 32 / 64 threads
-    // ([65536, 1024] bf16: 0.55 -> 0.65 of HBM peak; wider rows measured better as they were).
+  // (16-bit RMSNorm rows measured better on the four-vector group shape below: 0.84 / 0.76.)
+  if (narrow_rows && (LN || sizeof(T) == 4) && !tune("rows.force_generic") &&
+      !tune(LN ? "layernorm_bwd.group" : "rmsnorm_bwd.group")) {
+    // Rows of fewer than 256 vectors: ONE vector per thread (groups of 32 ... 256
+    // threads), so a thread keeps 8 or 16 column sums instead of 32 or 64, the
+    // kernel needs ~60 registers and four blocks share an SM ([65536, 1024] bf16
+    // LayerNorm backward: 0.65 of the copy bandwidth with two vectors per thread
+    // and two blocks per SM).
     const int nv = (int)(hidden / N);
-    const int G = nv <= 64 ? 32 : 64;
+    const int G = nv <= 32 ? 32 : nv <= 64 ? 64 : nv <= 128 ? 128 : 256;
     const int threads = 256, groups = threads / G;
     const size_t smem =
         ((size_t)groups * 2 * NV * (G / 32) + (size_t)(NV + 1) * hidden) * sizeof(float);
 #define EVG_XN(g)                                                                              \
   if (!launched && G == g) {                                                                   \
-    auto kern = norm_bwd_kernel<T, g, 2, LN>;                                                  \
+    auto kern = norm_bwd_kernel<T, g, 1, LN>;                                                  \
     if (smem > 48 * 1024)                                                                      \
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
     blocks = persistent_grid(kern, threads, smem, rows, groups, cap);                          \
@@ -533,7 +536,7 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
                                             rstd, (T*)dx, partial, rows, (int)hidden);         \
     launched = true;                                                                           \
   }
-    EVG_XN(32) EVG_XN(64)
+    EVG_XN(32) EVG_XN(64) EVG_XN(128) EVG_XN(256)
 #undef EVG_XN
   }
   if (!launched && vec_ok && !tune("rows.force_generic") &&

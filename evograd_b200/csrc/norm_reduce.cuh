@@ -116,10 +116,13 @@ colreduce_exchange_kernel(const float* __restrict__ partial, int blocks, int64_t
 #endif  // __CUDACC__
 
 // Persistent blocks (= partial rows of the column reduction) the backward
-// kernels may launch: SMs x `norm_bwd.blocks_per_sm` (default 2).
-inline int max_partial_blocks() {
+// kernels may launch: SMs x `norm_bwd.blocks_per_sm`; by default 2, and 4 for
+// rows of at most 2048 elements, whose kernels keep few values per thread, fit
+// four blocks on an SM and need them to hide their load latency (a partial row
+// is then at most 8 KB).
+inline int max_partial_blocks(int64_t hidden = (int64_t)1 << 40) {
   int per_sm = tune("norm_bwd.blocks_per_sm");
-  if (per_sm <= 0) per_sm = 2;
+  if (per_sm <= 0) per_sm = hidden <= 2048 ? 4 : 2;
   return device_info().sm_count * per_sm;
 }
 
