@@ -1165,10 +1165,6 @@ def run_ours(args):
 # on fewer rows), the file the summary of the capture is in, the kernel sources
 # the capture belongs to and the digest of those sources when it was taken.
 _ROW_HEADERS = ["evg_common.cuh", "rowcfg.cuh", "norm_reduce.cuh", "sm100_umma.cuh"]
-TRAFFIC_NCU = {
-    # filled in from the captures summarised under profiles/ (python bench.py --source-digest NAME
-    # prints the digest of a workload's kernel sources as they are now)
-}
 TRAFFIC_SOURCES = {
     "layernorm": ["norm_bwd.cu", *_ROW_HEADERS],
     "rmsnorm": ["norm_bwd.cu", *_ROW_HEADERS],
@@ -1178,6 +1174,26 @@ TRAFFIC_SOURCES = {
     "softmax_vocab": ["softmax_wide.cu", "softmax_wide.cuh", "evg_common.cuh", "sm100_umma.cuh"],
     "softmax": ["softmax.cu", "evg_common.cuh", "rowcfg.cuh"],
     "rope": ["rope.cu", "evg_common.cuh"],
+}
+TRAFFIC_NCU = {
+    # python bench.py --source-digest NAME prints the digest of a workload's kernel sources as
+    # they are now; an entry whose digest no longer matches is reported as stale, not used
+    "layernorm": {"bytes": 381900000, "profile": "profiles/layernorm_bf16_16384x4096.md",
+                 "sources": TRAFFIC_SOURCES["layernorm"], "digest": "c4e02a563019"},
+    "rmsnorm": {"bytes": 678100000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
+               "sources": TRAFFIC_SOURCES["rmsnorm"], "digest": "c4e02a563019"},
+    "fused_add_rms_norm": {"bytes": 975300000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
+                          "sources": TRAFFIC_SOURCES["fused_add_rms_norm"], "digest": "90d6f7fc4e31"},
+    "geglu": {"bytes": 4294000000, "profile": "profiles/geglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
+             "sources": TRAFFIC_SOURCES["geglu"], "digest": "bb456aae4e70"},
+    "swiglu": {"bytes": 4299000000, "profile": "profiles/swiglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
+              "sources": TRAFFIC_SOURCES["swiglu"], "digest": "bb456aae4e70"},
+    "softmax_vocab": {"bytes": 2859000000, "profile": "profiles/softmax_bf16_512x128256.md (512 rows, scaled x 8)",
+                     "sources": TRAFFIC_SOURCES["softmax_vocab"], "digest": "9f8abf4a231e"},
+    "softmax": {"bytes": 33600000, "profile": "profiles/softmax_f32_4096x1024.md",
+               "sources": TRAFFIC_SOURCES["softmax"], "digest": "9aba8149d309"},
+    "rope": {"bytes": 841600000, "profile": "profiles/rope_bf16_qk_2x4096x32x128.md (batch 2, scaled x 4)",
+            "sources": TRAFFIC_SOURCES["rope"], "digest": "c1372015957c"},
 }
 
 
