@@ -126,9 +126,9 @@ extern "C" int evg_causal_attention_fwd(const void* q, const void* k, const void
 
 extern "C" int64_t evg_causal_attention_bwd_workspace_bytes(int64_t B, int64_t H, int64_t S,
                                                             int64_t D, int dtype) {
-  (void)D; (void)dtype;
+  (void)dtype;
   if (B <= 0 || H <= 0 || S <= 0) return 0;
-  return attn::bwd2_workspace_bytes(B, H, S);
+  return attn::bwd2_workspace_bytes(B, H, S, D);
 }
 
 extern "C" int evg_causal_attention_bwd(const void* dout, const void* q, const void* k,
@@ -195,8 +195,8 @@ extern "C" int64_t evg_causal_gqa_attention_bwd_workspace_bytes(int64_t B, int64
   (void)Hkv;
   if (B <= 0 || Hq <= 0 || S <= 0) return 0;
   // the tensor-core path needs the larger scratch; it also covers the generic one
-  (void)D; (void)dtype;
-  return attn::bwd2_workspace_bytes(B, Hq, S);
+  (void)dtype;
+  return attn::bwd2_workspace_bytes(B, Hq, S, D);
 }
 
 extern "C" int evg_causal_gqa_attention_bwd(const void* dout, const void* q, const void* k,

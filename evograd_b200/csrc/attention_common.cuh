@@ -96,9 +96,10 @@ constexpr size_t kControlBytes = 24 * 8 + 64;
 int launch_fwd2_any(int head_dim, int fmt, const void* q, const void* k, const void* v, void* o,
                     float* lse, int64_t B, int64_t H, int64_t Hkv, int64_t S, float scale,
                     cudaStream_t stream);
-// Pipelined backward (attention_bwd2.cu): scratch = two float32 arrays padded
-// to whole tiles per (batch, head). fmt: 0 float16, 1 bfloat16.
-int64_t bwd2_workspace_bytes(int64_t B, int64_t H, int64_t S);
+// Pipelined backward (attention_bwd2.cu, attention_bwd3.cu): scratch = two float32
+// arrays padded to whole tiles per (batch, head), plus, at head size 128, a
+// float32 copy of dQ with the same padding. fmt: 0 float16, 1 bfloat16.
+int64_t bwd2_workspace_bytes(int64_t B, int64_t H, int64_t S, int64_t D);
 int launch_bwd2_any(int head_dim, int fmt, const void* dout, const void* q, const void* k,
                     const void* v, const void* o, const float* lse, void* dq, void* dk, void* dv,
                     float* workspace, int64_t B, int64_t H, int64_t Hkv, int64_t S, float scale,
