@@ -47,7 +47,8 @@ using namespace attn;
 using namespace attn_bwd;
 
 constexpr int kCG3 = 4;                       // column groups of compute warps
-constexpr int kThreads3 = 64 + 128 * kCG3;    // TMA warp, MMA warp, 16 compute warps
+// TMA warp, MMA warp, 16 compute warps, 4 warps that take dQ^T out of tensor memory
+constexpr int kThreads3 = 64 + 128 * kCG3 + 128;
 constexpr uint32_t kChunkBytes = 64 * 128 * 2;  // 64 queries x 128 keys of 16-bit dS^T
 
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -112,7 +113,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(q_full + i, 1); mbar_init(q_empty + i, 1);
       mbar_init(do_full + i, 1); mbar_init(do_empty + i, 1);
       mbar_init(dp_full + i, 1); mbar_init(pds_full + i, 4 * CG);
-      mbar_init(ds_full + i, 4 * CG); mbar_init(dq_full + i, 1); mbar_init(d_free + i, 4 * CG);
+      mbar_init(ds_full + i, 4 * CG); mbar_init(dq_full + i, 1); mbar_init(d_free + i, 4);
     }
     mbar_init(s_full, 1); mbar_init(x_free, 4 * CG);
     fence_mbar_init();
@@ -255,6 +256,32 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       __syncwarp();
     }
     if (lead) mma_commit(done);
+  } else if (r.warp >= 2 + 4 * CG) {
+    // dQ^T of every chunk: this warp's 32 lanes (head columns) x 64 query columns
+    // of D, one 128-byte line of the float32 dQ copy per warp instruction. The
+    // additions queue up behind the L2's float32 adders, which is why they have
+    // warps of their own: nothing else waits for them.
+    const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
+    int it = 0, bhq = bh * group;
+    for (int c = 0; c < n_git; ++c) {
+      const uint32_t par = (uint32_t)(c & 1);
+      float* tile_dst = dq_acc + ((size_t)bhq * S_pad + (size_t)(kvt + it) * kTile) * HD + r.row;
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        mbar_wait(dq_full + ch, par, ctx, 741);
+        __syncwarp();
+        tc_fence_after_sync();
+        uint32_t acc[2][32];
+        tmem_ld(tD + lane_base, acc[0]);
+        tmem_ld(tD + lane_base + 32, acc[1]);
+        tmem_wait_ld();
+        warp_arrive(d_free + ch, r.lane);
+        float* dst = tile_dst + ch * 64 * HD;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) red_add_f32(dst + j * HD, __uint_as_float(acc[j >> 5][j & 31]));
+      }
+      if (++it == n_it) { it = 0; ++bhq; }
+    }
   } else if (r.is_compute) {
     const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
     const int kv_glob = kv0 + r.row;
@@ -280,22 +307,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
       for (int g = 0; g < CPW / 2; ++g) pp[g] = pack2<FMT>(p[2 * g], p[2 * g + 1]);
     };
-    // dQ^T of a finished chunk: 16 query columns of D, lanes = head columns; one
-    // 128-byte line of the float32 dQ copy per warp instruction.
-    auto drain = [&](int ch, uint32_t parity, size_t acc_row0) {
-      mbar_wait(dq_full + ch, parity, ctx, 741);
-      __syncwarp();
-      tc_fence_after_sync();
-      uint32_t acc[CPW];
-      tmem_ld(tD + lane_base + col0, acc);
-      tmem_wait_ld();
-      warp_arrive(d_free + ch, r.lane);
-      float* dst = dq_acc + (acc_row0 + ch * 64 + col0) * HD + r.row;
-#pragma unroll
-      for (int j = 0; j < CPW; ++j) red_add_f32(dst + j * HD, __uint_as_float(acc[j]));
-    };
-    int it = 0, bhq = bh * group;
-    size_t row_prev = 0;  // first row of the previous tile in the float32 dQ copy
+    int it = 0;
     // P^T of the very first chunk
     mbar_wait(do_full + 0, 0, ctx, 742);
     mbar_wait(s_full, 0, ctx, 743);
@@ -307,9 +319,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const uint32_t par = (uint32_t)(c & 1);
       const float* stat = s_stat + st * 256;
       const int q0 = (kvt + it) * kTile;
-      const size_t row_cur = (size_t)bhq * S_pad + q0;
-      int it1 = it + 1, bhq1 = bhq;
-      if (it1 == n_it) { it1 = 0; ++bhq1; }
+      const int it1 = it + 1 == n_it ? 0 : it + 1;
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         // dS^T of chunk (c, ch): into Y behind P^T, and into shared memory
@@ -331,10 +341,6 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           dd[2 * g] = pack2<FMT>(d[0], d[1]);
           dd[2 * g + 1] = pack2<FMT>(d[2], d[3]);
         }
-        tmem_st(tY + lane_base + col0, pp);
-        tmem_st(tY + lane_base + col0 + CPW / 2, dd);
-        tmem_wait_st();
-        warp_arrive(pds_full + ch, r.lane);
         {
           // Row r.row (a key) of the chunk's [128 keys x 64 queries] tile, 16-byte
           // pieces 2g and 2g+1 of its 128 bytes, at their swizzled places.
@@ -344,16 +350,14 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
               make_uint4(dd[0], dd[1], dd[2], dd[3]);
           *reinterpret_cast<uint4*>(row_ptr + (((2 * r.half + 1) ^ sw) << 4)) =
               make_uint4(dd[4], dd[5], dd[6], dd[7]);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (r.lane == 0) mbar_arrive(ds_full + ch);
         }
-        // dQ^T of the chunk before this one
-        if (ch == 0) {
-          if (c > 0) drain(1, par ^ 1u, row_prev);
-        } else {
-          drain(0, par, row_cur);
-        }
+        tmem_st(tY + lane_base + col0, pp);
+        tmem_st(tY + lane_base + col0 + CPW / 2, dd);
+        fence_proxy_async_smem();  // the shared-memory copy is read by the tensor pipe
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (r.lane == 0) { mbar_arrive(pds_full + ch); mbar_arrive(ds_full + ch); }
         // P^T of the chunk after this one
         if (ch == 0) {
           exp_chunk(64 + col0, stat + 64 + col0, it == 0, q0 + 64 + col0);
@@ -366,11 +370,8 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           exp_chunk(col0, s_stat + (st ^ 1) * 256 + col0, it1 == 0, (kvt + it1) * kTile + col0);
         }
       }
-      row_prev = row_cur;
       it = it1;
-      bhq = bhq1;
     }
-    drain(1, (uint32_t)((n_git - 1) & 1), row_prev);
     mbar_wait(done, 0, ctx, 747);
     __syncwarp();
     tc_fence_after_sync();
