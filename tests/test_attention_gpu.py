@@ -96,11 +96,39 @@ def test_unit_scale_inputs_standard_normal():
     assert_checks(_strict_checks(got, {"o": o_ref, **g_ref}), "N(0,1) inputs")
 
 
-def test_backward_is_bit_reproducible():
+def _close_in_last_bits(a, b):
+    """Two roundings of float32 sums whose terms were added in a different order."""
+    a, b = a.float(), b.float()
+    return bool(((a - b).abs() <= 2 ** -6 * b.abs() + 1e-3).all())
+
+
+def test_backward_reproducibility():
+    """dk and dv are accumulated in tensor memory in a fixed order: same bits every
+    run. At head size 128 dq is summed over key tiles with float32 global adds in
+    arrival order, so it may move in the last bit; ``attention.two_kernel_bwd``
+    selects the split backward whose dq is bit-reproducible too."""
+    from evograd_b200 import _cabi
+
     inputs = to_device(ao.make_inputs("causal_attention", dict(B=1, H=3, S=640, D=128), "bfloat16"))
     _, g1, _ = run_pair("causal_attention", inputs)
     _, g2, _ = run_pair("causal_attention", inputs)
-    for a, b in zip(g1, g2):
+    assert _close_in_last_bits(g1[0], g2[0])
+    assert torch.equal(g1[1], g2[1]) and torch.equal(g1[2], g2[2])
+    try:
+        _cabi.tune_set("attention.two_kernel_bwd", 1)
+        _, s1, _ = run_pair("causal_attention", inputs)
+        _, s2, _ = run_pair("causal_attention", inputs)
+    finally:
+        _cabi.tune_set("attention.two_kernel_bwd", 0)
+    for a, b in zip(s1, s2):
+        assert torch.equal(a, b)
+    # both backward paths: same dk / dv bits, dq equal up to the order of the float32 sum
+    assert torch.equal(g1[1], s1[1]) and torch.equal(g1[2], s1[2])
+    assert _close_in_last_bits(g1[0], s1[0])
+    inputs64 = to_device(ao.make_inputs("causal_attention", dict(B=1, H=2, S=384, D=64), "bfloat16"))
+    _, h1, _ = run_pair("causal_attention", inputs64)
+    _, h2, _ = run_pair("causal_attention", inputs64)
+    for a, b in zip(h1, h2):
         assert torch.equal(a, b)
 
 
@@ -182,6 +210,11 @@ def test_grouped_query_attention_matches_the_oracle(B, Hq, Hkv, S, D, dtype):
     for n, got, ref in zip(("dq", "dk", "dv"), (dq, dk, dv), g_ref):
         checks.append(ao.check(n, got, ref.to(dt), *tol_g))
     assert_checks(checks, f"gqa {B}x{Hq}/{Hkv}x{S}x{D} {dtype}")
-    # deterministic: same bits on a second run
+    # same bits on a second run (dq at head size 128 on the tensor cores: float32 adds in
+    # arrival order, so only up to the last bit)
     dq2, dk2, dv2 = ops.causal_gqa_attention_bwd(dod, qd, kd, vd, o, lse)
-    assert torch.equal(dk, dk2) and torch.equal(dv, dv2) and torch.equal(dq, dq2)
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    if D == 128 and dtype != "float32":
+        assert _close_in_last_bits(dq, dq2)
+    else:
+        assert torch.equal(dq, dq2)
