@@ -273,11 +273,16 @@ int64_t evg_causal_attention_bwd_workspace_bytes(int64_t B, int64_t H, int64_t S
                                                  int64_t D, int dtype);
 /*
  * delta = rowsum(do*o); P = exp(scale*s - lse); dV = P^T dO; dP = dO V^T;
- * dS = P*(dP - delta); dQ = scale*dS K; dK = scale*dS^T Q.  Deterministic:
- * dK/dV are accumulated by the block that owns a key tile and dQ by the block
- * that owns a query tile, so no atomics and no float32 dq buffer are used.
+ * dS = P*(dP - delta); dQ = scale*dS K; dK = scale*dS^T Q.
+ * dK/dV are accumulated in a fixed order by the block that owns a key tile:
+ * same bits on every run. At head size 128 the same block also forms its part
+ * of dQ and adds it to a float32 copy with global float32 adds, so dq can
+ * differ in the last bit between runs; the tunable "attention.two_kernel_bwd"
+ * = 1 (and head size 64) uses a second kernel that owns a query tile instead:
+ * no atomics, bit-reproducible dq, about 6 % slower.
  * workspace holds two float32 arrays padded to whole 128-row tiles per (batch,
- * head): delta and the log-sum-exp in log2 units.
+ * head), delta and the log-sum-exp in log2 units, and at head size 128 the
+ * float32 dQ copy [B*H, padded S, 128] (ask the _workspace_bytes function).
  */
 int evg_causal_attention_bwd(const void* dout, const void* q, const void* k,
                              const void* v, const void* o, const float* lse,
