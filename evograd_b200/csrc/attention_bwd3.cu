@@ -91,8 +91,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint64_t* s_full = bs.bars + 9;
   uint64_t* x_free = bs.bars + 10;
   uint64_t* dp_full = bs.bars + 11;   // [2] by chunk parity
-  uint64_t* pds_full = bs.bars + 13;  // [2] P^T / dS^T of the chunk are in Y
-  uint64_t* ds_full = bs.bars + 15;   // [2] dS^T of the chunk is in shared memory
+  uint64_t* pds_full = bs.bars + 13;  // [2] P^T / dS^T of the chunk are in Y, dS^T in shared memory too
   uint64_t* dq_full = bs.bars + 17;   // [2] dQ^T of the chunk is in D
   uint64_t* d_free = bs.bars + 19;    // [2] D has been read
   uint64_t* done = bs.bars + 21;
@@ -113,7 +112,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(q_full + i, 1); mbar_init(q_empty + i, 1);
       mbar_init(do_full + i, 1); mbar_init(do_empty + i, 1);
       mbar_init(dp_full + i, 1); mbar_init(pds_full + i, 4 * CG);
-      mbar_init(ds_full + i, 4 * CG); mbar_init(dq_full + i, 1); mbar_init(d_free + i, 4);
+      mbar_init(dq_full + i, 1); mbar_init(d_free + i, 4);
     }
     mbar_init(s_full, 1); mbar_init(x_free, 4 * CG);
     fence_mbar_init();
@@ -220,15 +219,17 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const uint32_t par = (uint32_t)(c & 1), par1 = (uint32_t)(((c + 1) >> 1) & 1);
       const bool more = c + 1 < n_git;
       const uint32_t do_saddr = smem_u32(sDO0 + st * TB), q_saddr = smem_u32(sQ0 + st * TB);
+      // One wait on the critical path per chunk (P^T / dS^T are ready), with the
+      // waits that are normally satisfied long before taken care of ahead of it:
+      // every wait, satisfied or not, costs this warp about a hundred cycles, and
+      // the tensor pipe's queue is only a few instructions deep.
       // chunk 0
+      if (c > 0) mbar_wait(d_free + 1, par ^ 1u, ctx, 726);
       mbar_wait(pds_full + 0, par, ctx, 724);
       tc_fence_after_sync();
       issue_dv(0, do_saddr, c == 0);
       issue_dk(0, q_saddr, c == 0);
       issue_dp(1, do_saddr);
-      mbar_wait(ds_full + 0, par, ctx, 725);
-      if (c > 0) mbar_wait(d_free + 1, par ^ 1u, ctx, 726);
-      tc_fence_after_sync();
       issue_dq(0);
       if (more) {
         mbar_wait(q_full + st1, par1, ctx, 727);
@@ -238,20 +239,15 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (lead) mma_commit(s_full);
       }
       // chunk 1
+      mbar_wait(d_free + 0, par, ctx, 735);
+      if (more) mbar_wait(do_full + st1, par1, ctx, 733);
       mbar_wait(pds_full + 1, par, ctx, 729);
       tc_fence_after_sync();
       issue_dv(1, do_saddr, false);
       if (lead) mma_commit(do_empty + st);
       issue_dk(1, q_saddr, false);
       if (lead) mma_commit(q_empty + st);
-      if (more) {
-        mbar_wait(do_full + st1, par1, ctx, 733);
-        tc_fence_after_sync();
-        issue_dp(0, smem_u32(sDO0 + st1 * TB));
-      }
-      mbar_wait(ds_full + 1, par, ctx, 734);
-      mbar_wait(d_free + 0, par, ctx, 735);
-      tc_fence_after_sync();
+      if (more) issue_dp(0, smem_u32(sDO0 + st1 * TB));
       issue_dq(1);
       __syncwarp();
     }
@@ -357,7 +353,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (r.lane == 0) { mbar_arrive(pds_full + ch); mbar_arrive(ds_full + ch); }
+        if (r.lane == 0) mbar_arrive(pds_full + ch);
         // P^T of the chunk after this one
         if (ch == 0) {
           exp_chunk(64 + col0, stat + 64 + col0, it == 0, q0 + 64 + col0);
