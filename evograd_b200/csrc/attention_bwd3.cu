@@ -91,7 +91,8 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint64_t* s_full = bs.bars + 9;
   uint64_t* x_free = bs.bars + 10;
   uint64_t* dp_full = bs.bars + 11;   // [2] by chunk parity
-  uint64_t* pds_full = bs.bars + 13;  // [2] P^T / dS^T of the chunk are in Y, dS^T in shared memory too
+  uint64_t* pds_full = bs.bars + 13;  // [2] P^T / dS^T of the chunk are in Y
+  uint64_t* ds_full = bs.bars + 15;   // [2] dS^T of the chunk is in shared memory
   uint64_t* dq_full = bs.bars + 17;   // [2] dQ^T of the chunk is in D
   uint64_t* d_free = bs.bars + 19;    // [2] D has been read
   uint64_t* done = bs.bars + 21;
@@ -112,7 +113,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(q_full + i, 1); mbar_init(q_empty + i, 1);
       mbar_init(do_full + i, 1); mbar_init(do_empty + i, 1);
       mbar_init(dp_full + i, 1); mbar_init(pds_full + i, 4 * CG);
-      mbar_init(dq_full + i, 1); mbar_init(d_free + i, 4);
+      mbar_init(ds_full + i, 4 * CG); mbar_init(dq_full + i, 1); mbar_init(d_free + i, 4);
     }
     mbar_init(s_full, 1); mbar_init(x_free, 4 * CG);
     fence_mbar_init();
@@ -230,6 +231,8 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       issue_dv(0, do_saddr, c == 0);
       issue_dk(0, q_saddr, c == 0);
       issue_dp(1, do_saddr);
+      mbar_wait(ds_full + 0, par, ctx, 725);  // long since complete: not on the critical path
+      tc_fence_after_sync();
       issue_dq(0);
       if (more) {
         mbar_wait(q_full + st1, par1, ctx, 727);
@@ -248,6 +251,8 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       issue_dk(1, q_saddr, false);
       if (lead) mma_commit(q_empty + st);
       if (more) issue_dp(0, smem_u32(sDO0 + st1 * TB));
+      mbar_wait(ds_full + 1, par, ctx, 734);
+      tc_fence_after_sync();
       issue_dq(1);
       __syncwarp();
     }
@@ -282,26 +287,41 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
     const int kv_glob = kv0 + r.row;
     const int col0 = r.half * CPW;  // first query column inside a chunk of this warp
-    float p[CPW];                   // P^T of the chunk that comes next
+    f32x2 p2[CPW / 2];  // P^T of the chunk that comes next, two query columns per element
     uint32_t pp[CPW / 2];
-    // P^T of one chunk from 16 columns of X; `diag`: queries before the key are masked.
-    auto exp_chunk = [&](uint32_t x_col, const float* lse_ptr, bool diag, int q_first) {
+    const f32x2 neg_scale2 = f2_splat(-scale_log2);
+    // P^T of one chunk from 16 columns of X, two columns per packed instruction:
+    // t = lse2 - s c, p = 2^-t. `diag`: queries before the key are masked. When
+    // `release` is set, X is handed back as soon as its columns are in registers.
+    auto exp_chunk = [&](uint32_t x_col, const float* lse_ptr, bool diag, int q_first, bool release) {
       uint32_t sr[CPW];
       tmem_ld(tX + lane_base + x_col, sr);
       tmem_wait_ld();
+      if (release) warp_arrive(x_free, r.lane);
       const float4* lse4 = reinterpret_cast<const float4*>(lse_ptr);
 #pragma unroll
       for (int g = 0; g < CPW / 4; ++g) {
         const float4 l4 = lse4[g];
-        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+        const f32x2 t01 = f2_fma(f2_make(__uint_as_float(sr[4 * g]), __uint_as_float(sr[4 * g + 1])),
+                                 neg_scale2, f2_make(l4.x, l4.y));
+        const f32x2 t23 = f2_fma(f2_make(__uint_as_float(sr[4 * g + 2]), __uint_as_float(sr[4 * g + 3])),
+                                 neg_scale2, f2_make(l4.z, l4.w));
+        float t[4];
+        f2_split(t01, t[0], t[1]);
+        f2_split(t23, t[2], t[3]);
+        float pe[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float pe = fast_exp2(fmaf(__uint_as_float(sr[4 * g + e]), scale_log2, -lv[e]));
-          p[4 * g + e] = (diag && q_first + 4 * g + e < kv_glob) ? 0.f : pe;
+        for (int e = 0; e < 4; ++e) pe[e] = fast_exp2(-t[e]);
+        if (diag) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (q_first + 4 * g + e < kv_glob) pe[e] = 0.f;
         }
+        p2[2 * g] = f2_make(pe[0], pe[1]);
+        p2[2 * g + 1] = f2_make(pe[2], pe[3]);
+        pp[2 * g] = pack2<FMT>(pe[0], pe[1]);
+        pp[2 * g + 1] = pack2<FMT>(pe[2], pe[3]);
       }
-#pragma unroll
-      for (int g = 0; g < CPW / 2; ++g) pp[g] = pack2<FMT>(p[2 * g], p[2 * g + 1]);
     };
     int it = 0;
     // P^T of the very first chunk
@@ -309,7 +329,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     mbar_wait(s_full, 0, ctx, 743);
     __syncwarp();
     tc_fence_after_sync();
-    exp_chunk(col0, s_stat + col0, true, kvt * kTile + col0);
+    exp_chunk(col0, s_stat + col0, true, kvt * kTile + col0, false);
     for (int c = 0; c < n_git; ++c) {
       const int st = c & 1;
       const uint32_t par = (uint32_t)(c & 1);
@@ -327,43 +347,51 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         tmem_wait_ld();
         const float4* del4 = reinterpret_cast<const float4*>(stat + 128 + ch * 64 + col0);
         uint32_t dd[CPW / 2];
+        const f32x2 minus_one2 = f2_splat(-1.0f);
 #pragma unroll
         for (int g = 0; g < CPW / 4; ++g) {
           const float4 d4 = del4[g];
-          const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          // dS = P (dP - delta), two columns at a time
+          const f32x2 a01 = f2_fma(f2_make(d4.x, d4.y), minus_one2,
+                                   f2_make(__uint_as_float(dr[4 * g]), __uint_as_float(dr[4 * g + 1])));
+          const f32x2 a23 = f2_fma(f2_make(d4.z, d4.w), minus_one2,
+                                   f2_make(__uint_as_float(dr[4 * g + 2]), __uint_as_float(dr[4 * g + 3])));
           float d[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) d[e] = p[4 * g + e] * (__uint_as_float(dr[4 * g + e]) - dv[e]);
+          f2_split(f2_mul(p2[2 * g], a01), d[0], d[1]);
+          f2_split(f2_mul(p2[2 * g + 1], a23), d[2], d[3]);
           dd[2 * g] = pack2<FMT>(d[0], d[1]);
           dd[2 * g + 1] = pack2<FMT>(d[2], d[3]);
         }
+        // P^T / dS^T into Y first: the products that wait for them are the critical path.
+        tmem_st(tY + lane_base + col0, pp);
+        tmem_st(tY + lane_base + col0 + CPW / 2, dd);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (r.lane == 0) mbar_arrive(pds_full + ch);
         {
-          // Row r.row (a key) of the chunk's [128 keys x 64 queries] tile, 16-byte
-          // pieces 2g and 2g+1 of its 128 bytes, at their swizzled places.
+          // dS^T for the dQ^T product: row r.row (a key) of the chunk's [128 keys x 64
+          // queries] tile, 16-byte pieces 2g and 2g+1 of its 128 bytes, at their
+          // swizzled places.
           uint8_t* row_ptr = sDS + ch * kChunkBytes + r.row * 128;
           const int sw = r.row & 7;
           *reinterpret_cast<uint4*>(row_ptr + (((2 * r.half) ^ sw) << 4)) =
               make_uint4(dd[0], dd[1], dd[2], dd[3]);
           *reinterpret_cast<uint4*>(row_ptr + (((2 * r.half + 1) ^ sw) << 4)) =
               make_uint4(dd[4], dd[5], dd[6], dd[7]);
+          fence_proxy_async_smem();  // read by the tensor pipe
+          __syncwarp();
+          if (r.lane == 0) mbar_arrive(ds_full + ch);
         }
-        tmem_st(tY + lane_base + col0, pp);
-        tmem_st(tY + lane_base + col0 + CPW / 2, dd);
-        fence_proxy_async_smem();  // the shared-memory copy is read by the tensor pipe
-        tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (r.lane == 0) mbar_arrive(pds_full + ch);
         // P^T of the chunk after this one
         if (ch == 0) {
-          exp_chunk(64 + col0, stat + 64 + col0, it == 0, q0 + 64 + col0);
-          warp_arrive(x_free, r.lane);
+          exp_chunk(64 + col0, stat + 64 + col0, it == 0, q0 + 64 + col0, true);
         } else if (c + 1 < n_git) {
           mbar_wait(do_full + (st ^ 1), (uint32_t)(((c + 1) >> 1) & 1), ctx, 745);
           mbar_wait(s_full, par ^ 1u, ctx, 746);
           __syncwarp();
           tc_fence_after_sync();
-          exp_chunk(col0, s_stat + (st ^ 1) * 256 + col0, it1 == 0, (kvt + it1) * kTile + col0);
+          exp_chunk(col0, s_stat + (st ^ 1) * 256 + col0, it1 == 0, (kvt + it1) * kTile + col0, false);
         }
       }
       it = it1;
