@@ -223,17 +223,20 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       // One wait on the critical path per chunk (P^T / dS^T are ready), with the
       // waits that are normally satisfied long before taken care of ahead of it:
       // every wait, satisfied or not, costs this warp about a hundred cycles, and
-      // the tensor pipe's queue is only a few instructions deep.
+      // the tensor pipe's queue is only a few instructions deep. dQ^T runs one
+      // chunk behind, so its operand in shared memory and its place in D are
+      // ready by the time it is issued.
       // chunk 0
-      if (c > 0) mbar_wait(d_free + 1, par ^ 1u, ctx, 726);
+      if (c > 0) {
+        mbar_wait(d_free + 0, par ^ 1u, ctx, 726);
+        mbar_wait(ds_full + 1, par ^ 1u, ctx, 725);
+      }
       mbar_wait(pds_full + 0, par, ctx, 724);
       tc_fence_after_sync();
       issue_dv(0, do_saddr, c == 0);
       issue_dk(0, q_saddr, c == 0);
       issue_dp(1, do_saddr);
-      mbar_wait(ds_full + 0, par, ctx, 725);  // long since complete: not on the critical path
-      tc_fence_after_sync();
-      issue_dq(0);
+      if (c > 0) issue_dq(1);  // of tile c - 1
       if (more) {
         mbar_wait(q_full + st1, par1, ctx, 727);
         mbar_wait(x_free, par, ctx, 728);
@@ -242,7 +245,8 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (lead) mma_commit(s_full);
       }
       // chunk 1
-      mbar_wait(d_free + 0, par, ctx, 735);
+      if (c > 0) mbar_wait(d_free + 1, par ^ 1u, ctx, 735);
+      mbar_wait(ds_full + 0, par, ctx, 734);
       if (more) mbar_wait(do_full + st1, par1, ctx, 733);
       mbar_wait(pds_full + 1, par, ctx, 729);
       tc_fence_after_sync();
@@ -251,10 +255,15 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       issue_dk(1, q_saddr, false);
       if (lead) mma_commit(q_empty + st);
       if (more) issue_dp(0, smem_u32(sDO0 + st1 * TB));
-      mbar_wait(ds_full + 1, par, ctx, 734);
+      issue_dq(0);
+      __syncwarp();
+    }
+    {
+      const uint32_t last = (uint32_t)((n_git - 1) & 1);
+      mbar_wait(d_free + 0, last, ctx, 736);
+      mbar_wait(ds_full + 1, last, ctx, 737);
       tc_fence_after_sync();
       issue_dq(1);
-      __syncwarp();
     }
     if (lead) mma_commit(done);
   } else if (r.warp >= 2 + 4 * CG) {
@@ -369,6 +378,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         tc_fence_before_sync();
         __syncwarp();
         if (r.lane == 0) mbar_arrive(pds_full + ch);
+        if (c > 0) mbar_wait(dq_full + ch, par ^ 1u, ctx, 748);  // the buffer's last reader is done
         {
           // dS^T for the dQ^T product: row r.row (a key) of the chunk's [128 keys x 64
           // queries] tile, 16-byte pieces 2g and 2g+1 of its 128 bytes, at their
@@ -379,9 +389,6 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
               make_uint4(dd[0], dd[1], dd[2], dd[3]);
           *reinterpret_cast<uint4*>(row_ptr + (((2 * r.half + 1) ^ sw) << 4)) =
               make_uint4(dd[4], dd[5], dd[6], dd[7]);
-          fence_proxy_async_smem();  // read by the tensor pipe
-          __syncwarp();
-          if (r.lane == 0) mbar_arrive(ds_full + ch);
         }
         // P^T of the chunk after this one
         if (ch == 0) {
@@ -393,6 +400,12 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           tc_fence_after_sync();
           exp_chunk(col0, s_stat + (st ^ 1) * 256 + col0, it1 == 0, (kvt + it1) * kTile + col0, false);
         }
+        // The tensor pipe reads the shared-memory copy of dS^T a whole chunk later:
+        // its proxy fence waits here, behind the exponentials, where the stores have
+        // long landed.
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (r.lane == 0) mbar_arrive(ds_full + ch);
       }
       it = it1;
     }
