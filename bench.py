@@ -1197,6 +1197,17 @@ TRAFFIC_NCU = {
 }
 
 
+TRAFFIC_NOTES = {
+    # tensor-bound workloads: the DRAM bytes of the small-case captures do not grow in proportion
+    # to the work (tiles are re-read from L2), so no per-launch figure is scaled from them
+    "attention": "not scaled: 287 MB per fused backward launch at [1, 32, 4096, 128] "
+                 "(profiles/causal_attention_bf16_1x32x4096x128.md), DRAM throughput 8 %",
+    "decoder_layer": "not scaled: see profiles/llama3_decoder_layer_bf16_1x4096.md",
+    "evoattention": "not scaled: see profiles/evoattention_bf16_1x64x4x256x32.md",
+    "evoattention_n384": "not scaled: see profiles/evoattention_bf16_1x64x4x256x32.md",
+}
+
+
 def _source_digest(files):
     import hashlib
 
@@ -1212,7 +1223,7 @@ def ncu_traffic(workload):
     exists or the kernel sources changed after it was taken."""
     entry = TRAFFIC_NCU.get(workload)
     if entry is None:
-        return None, "no ncu capture for this workload"
+        return None, TRAFFIC_NOTES.get(workload, "no ncu capture for this workload")
     try:
         now = _source_digest(entry["sources"])
     except OSError:

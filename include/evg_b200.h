@@ -279,7 +279,7 @@ int64_t evg_causal_attention_bwd_workspace_bytes(int64_t B, int64_t H, int64_t S
  * of dQ and adds it to a float32 copy with global float32 adds, so dq can
  * differ in the last bit between runs; the tunable "attention.two_kernel_bwd"
  * = 1 (and head size 64) uses a second kernel that owns a query tile instead:
- * no atomics, bit-reproducible dq, about 6 % slower.
+ * no atomics, bit-reproducible dq, about 10 % slower.
  * workspace holds two float32 arrays padded to whole 128-row tiles per (batch,
  * head), delta and the log-sum-exp in log2 units, and at head size 128 the
  * float32 dQ copy [B*H, padded S, 128] (ask the _workspace_bytes function).
