@@ -801,6 +801,10 @@ def measure_e2e(wl, steps, warmup, world):
         from evograd_b200.host_pipeline import pipeline_for
 
         op, row_names, param_names, out_names, grad_names = spec
+        # one rank: the whole step is replayed from a CUDA graph (4 % faster than enqueueing it
+        # call by call; more than 8-16 chunks lose to the per-copy cost of the link either way);
+        # several ranks (an all_reduce inside the step) enqueue it call by call
+        graphed = world == 1 and os.environ.get("EVG_E2E_GRAPH", "1") != "0"
         n_chunks = int(os.environ.get("EVG_E2E_CHUNKS", "8"))
         pipe, finish = pipeline_for(op, eps=dev_set.get("eps", 1e-5), chunks=n_chunks)
         host_rows = {n: host[n] for n in row_names}
@@ -823,15 +827,16 @@ def measure_e2e(wl, steps, warmup, world):
         def step(_i):
             for n in param_names:
                 params[n].copy_(host[n], non_blocking=True)
-            live[0] = pipe.run(host_rows, params, host_out, host_grads,
-                               finish_all if finish else None)
+            run = pipe.run_graphed if graphed else pipe.run
+            live[0] = run(host_rows, params, host_out, host_grads, finish_all if finish else None)
 
         ms = time_steps(step, steps, warmup, barrier=_barrier_fn(world))
         ms = _max_over_ranks(ms, world)
         del live, params, host_rows, host_out
         torch.cuda.empty_cache()
         return ms, h2d, d2h, (f"host_pipeline: {n_chunks} row chunks, copy-in / kernels / copy-out "
-                              "overlapped on three streams")
+                              "overlapped on three streams"
+                              + (", the step replayed from one CUDA graph" if graphed else ""))
     outs = wl.step(dev_set)
     host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
     h2d = sum(v.numel() * v.element_size() for v in host.values() if torch.is_tensor(v))

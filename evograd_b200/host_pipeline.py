@@ -121,6 +121,33 @@ class HostRowPipeline:
             caller.wait_stream(s)
         return keep
 
+    def run_graphed(self, host_rows: dict, params: dict, host_out: dict, host_param_grads=None,
+                    finish_params=None):
+        """The same step replayed from a CUDA graph: with many small chunks the
+        enqueueing of a step (a dozen calls per chunk) takes longer than the
+        copies, and the link idles. The graph is captured on the first call for a
+        given set of host and device buffers (addresses and shapes) and replayed
+        on the caller's current stream afterwards; it holds the device tensors of
+        the step, so nothing needs to be kept by the caller. ``finish_params`` must
+        be capturable (no host synchronisation)."""
+        def ident(d):
+            return tuple((n, t.data_ptr(), tuple(t.shape), t.dtype) for n, t in (d or {}).items())
+
+        key = (ident(host_rows), ident(params), ident(host_out), ident(host_param_grads),
+               self.chunks, self.slots)
+        cached = getattr(self, "_graph", None)
+        if cached is None or cached[0] != key:
+            # once outside a capture: staging buffers, lazy initialisation of the kernels
+            self.run(host_rows, params, host_out, host_param_grads, finish_params)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=torch.cuda.Stream(self.device)):
+                keep = self.run(host_rows, params, host_out, host_param_grads, finish_params)
+            cached = (key, graph, keep)
+            self._graph = cached
+        cached[1].replay()
+        return None
+
 
 # ------------------------------------------------------------------ per operator
 def _layernorm_chunk(eps):
