@@ -514,7 +514,10 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
     }
   }
   // (16-bit RMSNorm rows measured better on the four-vector group shape below: 0.84 / 0.76.)
-  if (narrow_rows && (LN || sizeof(T) == 4) && !tune("rows.force_generic") &&
+  // (Rows of 129 ... 192 vectors fill three quarters of a 256-thread group; the
+  // three-vector shape of the general path has no idle lanes there.)
+  if (narrow_rows && (LN || sizeof(T) == 4) && !(hidden / N > 128 && hidden / N <= 192) &&
+      !tune("rows.force_generic") &&
       !tune(LN ? "layernorm_bwd.group" : "rmsnorm_bwd.group")) {
     // Rows of fewer than 256 vectors: ONE vector per thread (groups of 32 ... 256
     // threads), so a thread keeps 8 or 16 column sums instead of 32 or 64, the

@@ -15,8 +15,8 @@ namespace evg {
 
 // (G, VPT) shapes that are instantiated. Keep in sync with pick_rowcfg().
 #define EVG_ROWCFG_LIST(X) \
-  X(32, 1) X(32, 2) X(32, 4) X(64, 4) X(64, 8) X(128, 4) X(256, 2) X(256, 3) X(256, 4) X(512, 1) \
-  X(512, 4) X(1024, 4) X(1024, 8)
+  X(32, 1) X(32, 2) X(32, 4) X(64, 3) X(64, 4) X(64, 8) X(128, 3) X(128, 4) X(256, 2) X(256, 3) \
+  X(256, 4) X(512, 1) X(512, 4) X(1024, 4) X(1024, 8)
 
 // Upper bound on the block size a (G, VPT) kernel may be launched with; it is
 // also the kernel's __launch_bounds__, which fixes the register budget.
@@ -56,7 +56,9 @@ inline bool pick_rowcfg(const char* op, int64_t nvec, RowCfg& cfg, int prefer_th
   } else if (nvec <= 32) { G = 32; V = 1; }
   else if (nvec <= 64) { G = 32; V = 2; }
   else if (nvec <= 128) { G = 32; V = 4; }
+  else if (nvec <= 192) { G = 64; V = 3; }  // e.g. 1536 bf16 columns: no idle quarter of a group
   else if (nvec <= 256) { G = 64; V = 4; }
+  else if (nvec <= 384) { G = 128; V = 3; }  // e.g. 3072 bf16 columns
   else if (nvec <= 512 && narrow) { G = 256; V = 2; }
   else if (nvec <= 512) { G = 128; V = 4; }
   else if (nvec <= 768) { G = 256; V = 3; }  // e.g. 5120 bf16 columns: no idle quarter of a group
