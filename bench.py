@@ -926,6 +926,30 @@ def per_op_entry(wl, steps, warmup, world, peaks):
     return e
 
 
+# Row shapes away from the baseline configurations (narrow rows, rows that do not
+# fill a power-of-two group, very wide rows): LayerNorm / RMSNorm forward and
+# backward as fractions of the copy bandwidth, same method as per_op.
+OFF_BASELINE_SHAPES = [(65536, 1024), (49152, 1536), (32768, 3072), (8192, 5120), (2048, 16384)]
+
+
+def off_baseline_table(device, steps, warmup, peaks):
+    table = []
+    for rows, hidden in OFF_BASELINE_SHAPES:
+        entry = {"shape": [rows, hidden], "dtype": "bf16"}
+        for kind, base in (("layernorm", LayerNormWL), ("rmsnorm", RMSNormWL)):
+            cls = type(f"{base.__name__}Off", (base,), {"rows": rows, "hidden": hidden})
+            w = cls(device)
+            e = per_op_entry(w, steps, warmup, 1, peaks)
+            entry[kind] = {"fwd_ms": e["fwd_ms"], "bwd_ms": e["bwd_ms"],
+                           "fwd_frac_of_hbm_peak": round(e["fwd_gbs"] / peaks["hbm_gbs"], 4),
+                           "bwd_frac_of_hbm_peak": round(e["bwd_gbs"] / peaks["hbm_gbs"], 4),
+                           "buffer_sets": e["buffer_sets"]}
+            del w
+            torch.cuda.empty_cache()
+        table.append(entry)
+    return table
+
+
 def strong_scaling(world, steps, warmup, peaks):
     """The baseline shapes cut `world` ways (rows, batch or (batch, head) units per
     rank; LayerNorm/RMSNorm with the cross-rank dweight/dbias exchange): step
@@ -1140,6 +1164,10 @@ def run_ours(args):
             del w2
             torch.cuda.empty_cache()
         line["per_op"] = per_op
+
+    if world == 1 and not args.no_per_op:
+        line["off_baseline"] = off_baseline_table(device, max(3, args.steps // 2),
+                                                  max(3, args.warmup), peaks)
 
     if world > 1 and not args.no_strong:
         line["strong"] = strong_scaling(world, max(3, args.steps // 2), max(3, args.warmup), peaks)

@@ -16,7 +16,10 @@ namespace {
 // is unpacked to float32 registers ONCE and weight/bias are staged in shared
 // memory as float32, laid out so that consecutive threads read consecutive
 // float4 (slot q of vector idx lives at [q * nvec + idx]).
-template <typename T, int G, int VPT, bool LN>
+// WBP (groups of 512 threads and more, 16-bit LayerNorm): weight and bias stay in
+// their 16-bit form in shared memory, because float32 copies of both for a row of
+// 8192+ columns leave room for one block per SM only.
+template <typename T, int G, int VPT, bool LN, bool WBP = false>
 __global__ void __launch_bounds__(rowcfg_max_threads(G), G > 512 ? 1 : 2)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
                 T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
@@ -30,20 +33,28 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __res
   const int nvec = cols / N;
   float4* w4 = smem4;                              // [Q][nvec]
   float4* b4 = smem4 + (size_t)Q * nvec;           // [Q][nvec] (LayerNorm only)
-  float* scratch = reinterpret_cast<float*>(smem4 + (size_t)(LN ? 2 : 1) * Q * nvec) +
-                   gid * (2 * (G / 32));
+  uint4* wp = reinterpret_cast<uint4*>(smem4);     // WBP: [nvec] packed weight, then bias
+  uint4* bp = wp + nvec;
+  float* scratch = WBP ? reinterpret_cast<float*>(wp + (size_t)(LN ? 2 : 1) * nvec)
+                       : reinterpret_cast<float*>(smem4 + (size_t)(LN ? 2 : 1) * Q * nvec);
+  scratch += gid * (2 * (G / 32));
   int phase = 0;
   for (int idx = threadIdx.x; idx < nvec; idx += blockDim.x) {
-    float f[N];
-    unpack<T>(*reinterpret_cast<const uint4*>(w + (size_t)idx * N), f);
-#pragma unroll
-    for (int q = 0; q < Q; ++q)
-      w4[q * nvec + idx] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
-    if constexpr (LN) {
-      unpack<T>(*reinterpret_cast<const uint4*>(b + (size_t)idx * N), f);
+    if constexpr (WBP) {
+      wp[idx] = *reinterpret_cast<const uint4*>(w + (size_t)idx * N);
+      if constexpr (LN) bp[idx] = *reinterpret_cast<const uint4*>(b + (size_t)idx * N);
+    } else {
+      float f[N];
+      unpack<T>(*reinterpret_cast<const uint4*>(w + (size_t)idx * N), f);
 #pragma unroll
       for (int q = 0; q < Q; ++q)
-        b4[q * nvec + idx] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+        w4[q * nvec + idx] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+      if constexpr (LN) {
+        unpack<T>(*reinterpret_cast<const uint4*>(b + (size_t)idx * N), f);
+#pragma unroll
+        for (int q = 0; q < Q; ++q)
+          b4[q * nvec + idx] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+      }
     }
   }
   __syncthreads();
@@ -94,6 +105,16 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __res
       const int idx = lig + k * G;
       if (idx < nvec) {
         float o[N];
+        if constexpr (WBP) {
+          float wj[N], bj[N];
+          unpack<T>(wp[idx], wj);
+          if constexpr (LN) unpack<T>(bp[idx], bj);
+#pragma unroll
+          for (int j = 0; j < N; ++j) {
+            if constexpr (LN) o[j] = fmaf(fmaf(xf[k][j], rs, nmr), wj[j], bj[j]);
+            else o[j] = (xf[k][j] * rs) * wj[j];
+          }
+        } else
 #pragma unroll
         for (int qq = 0; qq < Q; ++qq) {
           const float4 wv = w4[qq * nvec + idx];
@@ -166,11 +187,13 @@ int launch_norm_fwd(const void* x, const void* w, const void* b, void* y, float*
   RowCfg cfg;
   if (vec_ok && !tune("rows.force_generic") && pick_rowcfg(op, hidden / N, cfg)) {
     const int groups = cfg.threads / cfg.G;
-    const size_t smem = (size_t)(LN ? 2 : 1) * hidden * sizeof(float) +
+    constexpr bool kCanPack = LN && sizeof(T) == 2;
+    const bool packed = kCanPack && cfg.G >= 512;
+    const size_t smem = (size_t)(LN ? 2 : 1) * hidden * (packed ? sizeof(T) : sizeof(float)) +
                         (size_t)groups * 2 * (cfg.G / 32) * sizeof(float);
 #define EVG_X(g, v)                                                                           \
   if (cfg.G == g && cfg.VPT == v && smem <= (size_t)device_info().max_smem_optin) {           \
-    auto kern = norm_fwd_kernel<T, g, v, LN>;                                                 \
+    auto kern = norm_fwd_kernel<T, g, v, LN, (kCanPack && g >= 512)>;                         \
     if (smem > 48 * 1024)                                                                     \
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
     const int grid = persistent_grid(kern, cfg.threads, smem, rows, groups);                  \
