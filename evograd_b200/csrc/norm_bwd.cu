@@ -179,7 +179,7 @@ __device__ int g_norm_device_status = 0;
 // The block-wide reduction barrier of row i also tells the issuing thread that
 // stage i % STAGES has been read by everyone and can be refilled.
 template <typename T, int THREADS, int VPT, bool LN>
-__global__ void __launch_bounds__(THREADS, (THREADS == 256 && VPT <= 2) ? 2 : 1)
+__global__ void __launch_bounds__(THREADS, (THREADS == 256 && VPT <= 3) ? 2 : 1)
 norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                      const float* __restrict__ mean, const float* __restrict__ rstd,
                      T* __restrict__ dx, float* __restrict__ partial, int64_t rows, int cols,
