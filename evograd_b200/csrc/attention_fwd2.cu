@@ -154,28 +154,38 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_wait(s_full + wg, j & 1, ctx, 709);
       __syncwarp();
       tc_fence_after_sync();
-      // Pass 1: row maximum, 32 columns at a time, four independent partial
-      // maxima so the comparisons do not form one long dependent chain.
+      // Pass 1: row maximum. Score columns [0, 64) stay in registers for pass 2;
+      // [64, 96) arrive in the same round trip to tensor memory and [96, 128) while
+      // the first maxima are being formed: two load latencies per tile are exposed
+      // instead of the eight of a chunk-by-chunk walk in both passes (there are only
+      // two softmax warps per scheduler to hide them). Four independent partial
+      // maxima keep the comparisons from forming one long dependent chain.
       const int kv0 = j * kTile;
       const bool diag = (j == qt[wg]);
+      uint32_t keep[64], tmp[32];
+      tmem_ld32(tSw + lane_base, *reinterpret_cast<uint32_t(*)[32]>(&keep[0]));
+      tmem_ld32(tSw + lane_base + 32, *reinterpret_cast<uint32_t(*)[32]>(&keep[32]));
+      tmem_ld32(tSw + lane_base + 64, tmp);
+      tmem_wait_ld();
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32];
-        tmem_ld32(tSw + lane_base + c * 32, sr);
-        tmem_wait_ld();
+      auto fold = [&](const uint32_t* v, int col0, int n) {
         if (diag) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float t = __uint_as_float(sr[i]);
-            if (kv0 + c * 32 + i > q_glob) t = -INFINITY;
+          for (int i = 0; i < n; ++i) {
+            float t = __uint_as_float(v[i]);
+            if (kv0 + col0 + i > q_glob) t = -INFINITY;
             mx4[i & 3] = fmaxf(mx4[i & 3], t);
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[i]));
+          for (int i = 0; i < n; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
         }
-      }
+      };
+      fold(tmp, 64, 32);
+      tmem_ld32(tSw + lane_base + 96, tmp);
+      fold(keep, 0, 64);
+      tmem_wait_ld();
+      fold(tmp, 96, 32);
       // scale_log2 > 0, so scaling commutes with the maximum
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       const bool grow = mx > m_run + kRescaleThreshold;  // always true on the first tile
@@ -200,15 +210,13 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       // columns [16c, 16c+16), which belong to score chunks already consumed.
       const float neg_m = -m_run;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32], pr[16];
-        tmem_ld32(tSw + lane_base + c * 32, sr);
-        tmem_wait_ld();
+      // 32 score columns -> 16 packed probability columns at [16 c, 16 c + 16)
+      auto probs = [&](const uint32_t* v, int c) {
+        uint32_t pr[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * i]), scale_log2, neg_m));
-          float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * i + 1]), scale_log2, neg_m));
+          float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), scale_log2, neg_m));
+          float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), scale_log2, neg_m));
           if (diag) {
             if (kv0 + c * 32 + 2 * i > q_glob) p0 = 0.f;
             if (kv0 + c * 32 + 2 * i + 1 > q_glob) p1 = 0.f;
@@ -217,7 +225,16 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           pr[i] = pack2<FMT>(p0, p1);
         }
         tmem_st16(tSw + lane_base + c * 16, pr);
-      }
+      };
+      // columns [64, 128) come back from tensor memory under the exponentials of [0, 64)
+      uint32_t late[32];
+      tmem_ld32(tSw + lane_base + 64, late);
+      probs(&keep[0], 0);
+      tmem_ld32(tSw + lane_base + 96, tmp);
+      probs(&keep[32], 1);
+      tmem_wait_ld();
+      probs(late, 2);
+      probs(tmp, 3);
       const float lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       l_run += lsum;
       tmem_wait_st();
