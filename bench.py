@@ -1211,21 +1211,21 @@ TRAFFIC_SOURCES = {
 TRAFFIC_NCU = {
     # python bench.py --source-digest NAME prints the digest of a workload's kernel sources as
     # they are now; an entry whose digest no longer matches is reported as stale, not used
-    "layernorm": {"bytes": 381900000, "profile": "profiles/layernorm_bf16_16384x4096.md",
-                 "sources": TRAFFIC_SOURCES["layernorm"], "digest": "c4e02a563019"},
-    "rmsnorm": {"bytes": 678100000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
-               "sources": TRAFFIC_SOURCES["rmsnorm"], "digest": "c4e02a563019"},
-    "fused_add_rms_norm": {"bytes": 975300000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
-                          "sources": TRAFFIC_SOURCES["fused_add_rms_norm"], "digest": "90d6f7fc4e31"},
-    "geglu": {"bytes": 4294000000, "profile": "profiles/geglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
+    "layernorm": {"bytes": 382200000, "profile": "profiles/layernorm_bf16_16384x4096.md",
+                 "sources": TRAFFIC_SOURCES["layernorm"], "digest": "cae7476223bb"},
+    "rmsnorm": {"bytes": 674500000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
+               "sources": TRAFFIC_SOURCES["rmsnorm"], "digest": "cae7476223bb"},
+    "fused_add_rms_norm": {"bytes": 975700000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
+                          "sources": TRAFFIC_SOURCES["fused_add_rms_norm"], "digest": "30e168a60c7e"},
+    "geglu": {"bytes": 4293000000, "profile": "profiles/geglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
              "sources": TRAFFIC_SOURCES["geglu"], "digest": "bb456aae4e70"},
-    "swiglu": {"bytes": 4299000000, "profile": "profiles/swiglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
+    "swiglu": {"bytes": 4317000000, "profile": "profiles/swiglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
               "sources": TRAFFIC_SOURCES["swiglu"], "digest": "bb456aae4e70"},
-    "softmax_vocab": {"bytes": 2859000000, "profile": "profiles/softmax_bf16_512x128256.md (512 rows, scaled x 8)",
+    "softmax_vocab": {"bytes": 2858000000, "profile": "profiles/softmax_bf16_512x128256.md (512 rows, scaled x 8)",
                      "sources": TRAFFIC_SOURCES["softmax_vocab"], "digest": "9f8abf4a231e"},
     "softmax": {"bytes": 33600000, "profile": "profiles/softmax_f32_4096x1024.md",
-               "sources": TRAFFIC_SOURCES["softmax"], "digest": "9aba8149d309"},
-    "rope": {"bytes": 841600000, "profile": "profiles/rope_bf16_qk_2x4096x32x128.md (batch 2, scaled x 4)",
+               "sources": TRAFFIC_SOURCES["softmax"], "digest": "1c5eac59092e"},
+    "rope": {"bytes": 840800000, "profile": "profiles/rope_bf16_qk_2x4096x32x128.md (batch 2, scaled x 4)",
             "sources": TRAFFIC_SOURCES["rope"], "digest": "c1372015957c"},
 }
 
