@@ -65,7 +65,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                  const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
                  float* __restrict__ dq_acc, void* __restrict__ dk_ptr, void* __restrict__ dv_ptr,
                  int S, int S_pad, int group, float scale, long long wait_limit,
-                 uint32_t smem_bytes, int heads_fastest) {
+                 uint32_t smem_bytes, int n_bh, int head_group) {
   constexpr int HD = 128;
   constexpr int CG = kCG3;
   constexpr int CPW = 64 / CG;  // query columns of a chunk per compute warp (16)
@@ -97,13 +97,10 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint64_t* d_free = bs.bars + 19;    // [2] D has been read
   uint64_t* done = bs.bars + 21;
   const Roles r = roles();  // r.half is the warp's column group, 0 .. CG-1
-  // Key tile 0 meets the most query tiles: heaviest blocks first. A large grid walks
-  // the key tiles of one head after another (blocks that run together then share that
-  // head's Q and dO tiles in L2); a grid of a few waves puts ALL heads' heavy tiles
-  // first instead, or the last head's heaviest block would start when most SMs are
-  // already idle.
-  const int kvt = heads_fastest ? blockIdx.y : blockIdx.x;
-  const int bh = heads_fastest ? blockIdx.x : blockIdx.y;
+  // Key tile 0 meets the most query tiles: the heaviest blocks of a group of heads
+  // start first (map_block).
+  int kvt, bh;
+  map_block(blockIdx.x, S_pad / kTile, n_bh, head_group, kvt, bh);
   const int kv0 = kvt * kTile;
   const int n_it = S_pad / kTile - kvt;
   // Grouped-query attention: the query tiles of each of the `group` query heads
@@ -460,13 +457,11 @@ int launch3(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
   if (smem > most) smem = most;
   auto kern = attn_bwd3_kernel<FMT>;
   if (int rc = reserve_smem(kern, smem)) return rc;
-  const int64_t n_blocks = (S_pad / kTile) * B * Hkv;
-  const int heads_fastest = n_blocks <= 6 * (int64_t)device_info().sm_count && S_pad / kTile <= 65535;
-  dim3 grid((unsigned)(S_pad / kTile), (unsigned)(B * Hkv));
-  if (heads_fastest) grid = dim3((unsigned)(B * Hkv), (unsigned)(S_pad / kTile));
+  dim3 grid((unsigned)((S_pad / kTile) * B * Hkv));
   kern<<<grid, kThreads3, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq_acc, dk, dv,
                                           (int)S, (int)S_pad, (int)(H / Hkv), scale,
-                                          wait_limit_cycles2(), (uint32_t)smem, heads_fastest);
+                                          wait_limit_cycles2(), (uint32_t)smem, (int)(B * Hkv),
+                                          head_group_for((S_pad / kTile) * B * Hkv, B * Hkv));
   if (int rc = check_launch("causal_attention_bwd fused")) return rc;
   const int64_t vectors = B * H * S * 16;
   attn_bwd3_finish_kernel<FMT><<<(unsigned)((vectors + 255) / 256), 256, 0, stream>>>(

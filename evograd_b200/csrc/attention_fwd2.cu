@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(kFwd2Threads, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, void* __restrict__ o_ptr,
                  float* __restrict__ lse_ptr, int S, int group, float scale_log2,
-                 long long wait_limit, int heads_fastest) {
+                 long long wait_limit, int n_pairs, int n_bh, int head_group) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   BlockSetup bs = carve(smem_raw, 6 * TB);
@@ -51,11 +51,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint64_t* o_done = bs.bars + 13;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = (S + kTile - 1) / kTile;
-  // Heaviest pairs first. A large grid walks the pairs of one head after another
-  // (blocks that run together share that head's K and V tiles in L2); a grid of a few
-  // waves puts ALL heads' heavy pairs first, so that no heavy block starts late.
-  const int pair = heads_fastest ? (int)(gridDim.y - 1 - blockIdx.y) : (int)(gridDim.x - 1 - blockIdx.x);
-  const int bh = heads_fastest ? blockIdx.x : blockIdx.y;
+  // Heaviest pairs first, for a group of heads at a time (map_block).
+  int pair, bh;
+  map_block(blockIdx.x, n_pairs, n_bh, head_group, pair, bh);
+  pair = n_pairs - 1 - pair;
   const int bh_kv = bh / group;  // grouped-query attention: `group` query heads per k/v head
   const int qt[2] = {2 * pair, 2 * pair + 1};
   const bool b_active = qt[1] < n_tiles;
@@ -309,13 +308,12 @@ int launch_fwd2(const void* q, const void* k, const void* v, void* o, float* lse
   }
   const int64_t n_tiles = (S + kTile - 1) / kTile;
   const int64_t n_pairs = (n_tiles + 1) / 2;
-  const int heads_fastest = n_pairs * B * H <= 6 * (int64_t)device_info().sm_count && n_pairs <= 65535;
-  dim3 grid((unsigned)n_pairs, (unsigned)(B * H));
-  if (heads_fastest) grid = dim3((unsigned)(B * H), (unsigned)n_pairs);
+  dim3 grid((unsigned)(n_pairs * B * H));
   const int t = tune("attention.wait_limit");
   const long long limit = t > 0 ? (long long)t * 1000000ll : 2000000000ll;
   kern<<<grid, kFwd2Threads, smem, stream>>>(mq, mk, mv, o, lse, (int)S, (int)(H / Hkv),
-                                             scale * kLog2e, limit, heads_fastest);
+                                             scale * kLog2e, limit, (int)n_pairs, (int)(B * H),
+                                             head_group_for(n_pairs * B * H, B * H));
   return check_launch("causal_attention_fwd");
 }
 
