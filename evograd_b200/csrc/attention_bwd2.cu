@@ -51,7 +51,7 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                     const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
                     void* __restrict__ dq_ptr, int S, int S_pad, int group, float scale,
-                    long long wait_limit) {
+                    long long wait_limit, int n_bh, int head_group) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   BlockSetup bs = carve(smem_raw, 7 * TB);
@@ -72,8 +72,9 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint64_t* ds_full = bs.bars + 15;  // [2]
   uint64_t* done = bs.bars + 17;
   const Roles r = roles();
-  const int qtile = gridDim.x - 1 - blockIdx.x;  // heaviest tiles first
-  const int bh = blockIdx.y;
+  int qtile, bh;  // heaviest tiles first (map_block)
+  map_block(blockIdx.x, S_pad / kTile, n_bh, head_group, qtile, bh);
+  qtile = S_pad / kTile - 1 - qtile;
   const int bh_kv = bh / group;  // `group` query heads share one k/v head
   const int q0 = qtile * kTile;
   const int n_it = qtile + 1;
@@ -249,7 +250,8 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                       const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
                       void* __restrict__ dk_ptr, void* __restrict__ dv_ptr, int S, int S_pad,
-                      int group, float scale, long long wait_limit, uint32_t smem_bytes) {
+                      int group, float scale, long long wait_limit, uint32_t smem_bytes, int n_bh,
+                      int head_group) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   constexpr uint32_t kTiles = 4 + QST;
@@ -280,8 +282,8 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   // First packed P^T column (inside Y_ch) of the chunk's query k-step kk.
   auto p_col = [](int kk) { return (kk * 16 / CPW) * CPW + (kk * 16 % CPW) / 2; };
   const Roles r = roles();  // r.half is the warp's column group, 0 .. CG-1
-  const int kvt = blockIdx.x;  // key tile 0 meets the most query tiles: heaviest first
-  const int bh = blockIdx.y;
+  int kvt, bh;  // key tile 0 meets the most query tiles: heaviest first (map_block)
+  map_block(blockIdx.x, S_pad / kTile, n_bh, head_group, kvt, bh);
   const int kv0 = kvt * kTile;
   const int n_it = S_pad / kTile - kvt;
   // Grouped-query attention: the query tiles of each of the `group` query heads
@@ -543,7 +545,7 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
       return launch_bwd3_128(FMT, mq, mk, mv, mdo, lse2_pad, delta_pad, workspace + 2 * padded_rows,
                              dq, dk, dv, B, H, Hkv, S, S_pad, scale, stream);
   }
-  dim3 grid((unsigned)n_q, (unsigned)(B * H));
+  dim3 grid((unsigned)(n_q * B * H));
   const long long limit = wait_limit_cycles2();
   {
     // 7 tiles of 32 KB at head size 128 leave 768 bytes of the 227 KB for alignment.
@@ -553,10 +555,11 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
     constexpr int CG = 4;  // 16 compute warps
     auto kern = attn_bwd2_dkdv_kernel<HD, FMT, 3, CG>;
     if (int rc = reserve_smem(kern, smem)) return rc;
-    dim3 grid_kv((unsigned)n_q, (unsigned)(B * Hkv));
+    dim3 grid_kv((unsigned)(n_q * B * Hkv));
     kern<<<grid_kv, 64 + 128 * CG, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
                                                    (int)S, (int)S_pad, group, scale, limit,
-                                                   (uint32_t)smem);
+                                                   (uint32_t)smem, (int)(B * Hkv),
+                                                   head_group_for(n_q * B * Hkv, B * Hkv));
     if (int rc = check_launch("causal_attention_bwd dkdv")) return rc;
   }
   {
@@ -564,7 +567,8 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
     auto kern = attn_bwd2_dq_kernel<HD, FMT>;
     if (int rc = reserve_smem(kern, smem)) return rc;
     kern<<<grid, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq, (int)S,
-                                            (int)S_pad, group, scale, limit);
+                                            (int)S_pad, group, scale, limit, (int)(B * H),
+                                            head_group_for(n_q * B * H, B * H));
     if (int rc = check_launch("causal_attention_bwd dq")) return rc;
   }
   return EVG_OK;
