@@ -78,8 +78,9 @@ template <int FMT> __device__ __forceinline__ uint32_t pack2(float lo, float hi)
 // taken in groups of `head_group`: within a group ALL heads' item 0 come first, then
 // all item 1, ... A grid of a few waves uses one group (no heavy block starts when
 // most SMs have nothing left to do: at 32 query / 8 k/v heads and 4096 tokens the
-// forward went from 178 to 144 us); a large grid uses groups of one head, so that
-// the blocks that run together read the same head's tiles from L2.
+// forward went from 178 to 144 us); a large grid uses groups of four heads, so that
+// the blocks that run together read the same few heads' tiles from L2 (one head per
+// group leaves the last head's heaviest block for the end: 0.5-1.5 % slower).
 __device__ __forceinline__ void map_block(int64_t id, int n_x, int n_bh, int head_group, int& x,
                                           int& bh) {
   const int64_t per_group = (int64_t)head_group * n_x;
@@ -90,9 +91,9 @@ __device__ __forceinline__ void map_block(int64_t id, int n_x, int n_bh, int hea
   x = r / in_group;
   bh = first + r % in_group;
 }
-// One group of all heads for grids of up to six waves, one head per group beyond.
+// One group of all heads for grids of up to six waves, four heads per group beyond.
 inline int head_group_for(int64_t n_blocks, int64_t n_bh) {
-  return n_blocks <= 6 * (int64_t)device_info().sm_count ? (int)n_bh : 1;
+  return n_blocks <= 6 * (int64_t)device_info().sm_count ? (int)n_bh : 4;
 }
 
 struct BlockSetup {
