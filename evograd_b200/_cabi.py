@@ -112,6 +112,16 @@ SIGNATURES = {
         [c_void_p] * 10 + [c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int,
                            c_void_p],
     ),
+    "evg_causal_gqa_attention_fwd_tm": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+         c_int64, c_float, c_int, c_void_p],
+    ),
+    "evg_causal_gqa_attention_bwd_tm": (
+        c_int,
+        [c_void_p] * 10 + [c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int,
+                           c_void_p],
+    ),
     "evg_evoattention_fwd": (
         c_int,
         [c_void_p] * 7 + [c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_void_p],

@@ -222,3 +222,51 @@ extern "C" int evg_causal_gqa_attention_bwd(const void* dout, const void* q, con
   return attn::launch_generic_bwd(dtype, dout, q, k, v, o, lse, dq, dk, dv, workspace,
                                   workspace_bytes, B, Hq, Hkv, S, D, scale, st);
 }
+
+extern "C" int evg_causal_gqa_attention_fwd_tm(const void* q, const void* k, const void* v,
+                                               void* o_token_major, float* lse, int64_t B,
+                                               int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                                               float scale, int dtype, void* stream) {
+  if (!q || !k || !v || !o_token_major || !lse)
+    return fail(EVG_ENULL, "causal_gqa_attention_fwd_tm: null pointer argument");
+  if (int rc = check_gqa_args("causal_gqa_attention_fwd_tm", B, Hq, Hkv, S, D, dtype, scale))
+    return rc;
+  if (!tensor_core_shape(D, dtype) || !aligned16(q) || !aligned16(k) || !aligned16(v) ||
+      !aligned16(o_token_major))
+    return fail(EVG_EUNSUPPORTED,
+                "causal_gqa_attention_fwd_tm: 16-bit, head size 64 / 128, 16-byte aligned only");
+  attn::Layouts lay;
+  lay.o_token_major = 1;
+  return attn::launch_fwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, q, k, v, o_token_major, lse, B,
+                               Hq, Hkv, S, scale, (cudaStream_t)stream, lay);
+}
+
+extern "C" int evg_causal_gqa_attention_bwd_tm(const void* dout, const void* q, const void* k,
+                                               const void* v, const void* o_token_major,
+                                               const float* lse, void* dq, void* dk,
+                                               void* dv_token_major, void* workspace,
+                                               int64_t workspace_bytes, int64_t B, int64_t Hq,
+                                               int64_t Hkv, int64_t S, int64_t D, float scale,
+                                               int dtype, void* stream) {
+  if (!dout || !q || !k || !v || !o_token_major || !lse || !dq || !dk || !dv_token_major)
+    return fail(EVG_ENULL, "causal_gqa_attention_bwd_tm: null pointer argument");
+  if (int rc = check_gqa_args("causal_gqa_attention_bwd_tm", B, Hq, Hkv, S, D, dtype, scale))
+    return rc;
+  const int64_t need = evg_causal_gqa_attention_bwd_workspace_bytes(B, Hq, Hkv, S, D, dtype);
+  if (!workspace || workspace_bytes < need)
+    return fail(EVG_EWORKSPACE, "causal_gqa_attention_bwd_tm: workspace %lld bytes, need %lld",
+                (long long)workspace_bytes, (long long)need);
+  bool aligned = aligned16(workspace);
+  for (const void* p : {dout, q, k, v, o_token_major, (const void*)dq, (const void*)dk,
+                        (const void*)dv_token_major})
+    aligned = aligned && aligned16(p);
+  if (!tensor_core_shape(D, dtype) || !aligned)
+    return fail(EVG_EUNSUPPORTED,
+                "causal_gqa_attention_bwd_tm: 16-bit, head size 64 / 128, 16-byte aligned only");
+  attn::Layouts lay;
+  lay.o_token_major = 1;
+  lay.dv_token_major = 1;
+  return attn::launch_bwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, dout, q, k, v, o_token_major, lse,
+                               dq, dk, dv_token_major, (float*)workspace, B, Hq, Hkv, S, scale,
+                               (cudaStream_t)stream, lay);
+}

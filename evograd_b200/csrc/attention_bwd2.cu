@@ -251,7 +251,7 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
                       void* __restrict__ dk_ptr, void* __restrict__ dv_ptr, int S, int S_pad,
                       int group, float scale, long long wait_limit, uint32_t smem_bytes, int n_bh,
-                      int head_group) {
+                      int head_group, int heads_kv, int dv_tm) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   constexpr uint32_t kTiles = 4 + QST;
@@ -506,7 +506,7 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     mbar_wait(done, 0, ctx, 630);
     __syncwarp();
     tc_fence_after_sync();
-    store_rows<HD, FMT, CG>(tDV, dv_ptr, bh, kv0, S, 1.0f, r);
+    store_rows<HD, FMT, CG>(tDV, dv_ptr, bh, kv0, S, 1.0f, r, heads_kv, dv_tm);
     store_rows<HD, FMT, CG>(tDK, dk_ptr, bh, kv0, S, scale, r);
   }
   tc_fence_before_sync();
@@ -518,7 +518,7 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 template <int HD, int FMT>
 int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, const void* o,
                 const float* lse, void* dq, void* dk, void* dv, float* workspace, int64_t B,
-                int64_t H, int64_t Hkv, int64_t S, float scale, cudaStream_t stream) {
+                int64_t H, int64_t Hkv, int64_t S, float scale, cudaStream_t stream, Layouts lay) {
   CUtensorMap mq, mk, mv, mdo;
   const int group = (int)(H / Hkv);
   if (!encode_tile_map_16bit(&mq, q, FMT, HD, S, B * H, kTile) ||
@@ -535,7 +535,8 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
     constexpr int TPR = HD / 8;
     const int64_t threads = padded_rows * TPR;  // a multiple of 256
     attn_prepare_kernel<HD, FMT><<<(unsigned)(threads / 256), 256, 0, stream>>>(
-        dout, o, lse, lse2_pad, delta_pad, (int)S, (int)S_pad, padded_rows);
+        dout, o, lse, lse2_pad, delta_pad, (int)S, (int)S_pad, padded_rows, (int)H,
+        lay.o_token_major);
     if (int rc = check_launch("causal_attention_bwd prepare")) return rc;
   }
   // Head size 128: one fused pass with a float32 dQ copy (behind the two arrays
@@ -543,7 +544,7 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
   if constexpr (HD == 128) {
     if (!tune("attention.two_kernel_bwd"))
       return launch_bwd3_128(FMT, mq, mk, mv, mdo, lse2_pad, delta_pad, workspace + 2 * padded_rows,
-                             dq, dk, dv, B, H, Hkv, S, S_pad, scale, stream);
+                             dq, dk, dv, B, H, Hkv, S, S_pad, scale, stream, lay.dv_token_major);
   }
   dim3 grid((unsigned)(n_q * B * H));
   const long long limit = wait_limit_cycles2();
@@ -559,7 +560,8 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
     kern<<<grid_kv, 64 + 128 * CG, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dk, dv,
                                                    (int)S, (int)S_pad, group, scale, limit,
                                                    (uint32_t)smem, (int)(B * Hkv),
-                                                   head_group_for(n_q * B * Hkv, B * Hkv));
+                                                   head_group_for(n_q * B * Hkv, B * Hkv), (int)Hkv,
+                                                   lay.dv_token_major);
     if (int rc = check_launch("causal_attention_bwd dkdv")) return rc;
   }
   {
@@ -603,16 +605,16 @@ int64_t bwd2_workspace_bytes(int64_t B, int64_t H, int64_t S, int64_t D) {
 int launch_bwd2_any(int head_dim, int fmt, const void* dout, const void* q, const void* k,
                     const void* v, const void* o, const float* lse, void* dq, void* dk, void* dv,
                     float* workspace, int64_t B, int64_t H, int64_t Hkv, int64_t S, float scale,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, Layouts lay) {
   if (head_dim == 128)
     return fmt == 1 ? launch_bwd2<128, 1>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, Hkv,
-                                          S, scale, stream)
+                                          S, scale, stream, lay)
                     : launch_bwd2<128, 0>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, Hkv,
-                                          S, scale, stream);
+                                          S, scale, stream, lay);
   return fmt == 1 ? launch_bwd2<64, 1>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, Hkv, S,
-                                       scale, stream)
+                                       scale, stream, lay)
                   : launch_bwd2<64, 0>(dout, q, k, v, o, lse, dq, dk, dv, workspace, B, H, Hkv, S,
-                                       scale, stream);
+                                       scale, stream, lay);
 }
 
 }  // namespace attn

@@ -65,7 +65,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                  const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
                  float* __restrict__ dq_acc, void* __restrict__ dk_ptr, void* __restrict__ dv_ptr,
                  int S, int S_pad, int group, float scale, long long wait_limit,
-                 uint32_t smem_bytes, int n_bh, int head_group) {
+                 uint32_t smem_bytes, int n_bh, int head_group, int heads_kv, int dv_tm) {
   constexpr int HD = 128;
   constexpr int CG = kCG3;
   constexpr int CPW = 64 / CG;  // query columns of a chunk per compute warp (16)
@@ -414,7 +414,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     mbar_wait(done, 0, ctx, 747);
     __syncwarp();
     tc_fence_after_sync();
-    store_rows<HD, FMT, CG>(tDV, dv_ptr, bh, kv0, S, 1.0f, r);
+    store_rows<HD, FMT, CG>(tDV, dv_ptr, bh, kv0, S, 1.0f, r, heads_kv, dv_tm);
     store_rows<HD, FMT, CG>(tDK, dk_ptr, bh, kv0, S, scale, r);
   }
   tc_fence_before_sync();
@@ -446,7 +446,7 @@ template <int FMT>
 int launch3(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
             const CUtensorMap& mdo, const float* lse2_pad, const float* delta_pad, float* dq_acc,
             void* dq, void* dk, void* dv, int64_t B, int64_t H, int64_t Hkv, int64_t S,
-            int64_t S_pad, float scale, cudaStream_t stream) {
+            int64_t S_pad, float scale, cudaStream_t stream, int dv_tm) {
   const size_t acc_bytes = (size_t)B * H * S_pad * 128 * sizeof(float);
   if (cudaMemsetAsync(dq_acc, 0, acc_bytes, stream) != cudaSuccess) {
     cudaGetLastError();
@@ -461,7 +461,8 @@ int launch3(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
   kern<<<grid, kThreads3, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq_acc, dk, dv,
                                           (int)S, (int)S_pad, (int)(H / Hkv), scale,
                                           wait_limit_cycles2(), (uint32_t)smem, (int)(B * Hkv),
-                                          head_group_for((S_pad / kTile) * B * Hkv, B * Hkv));
+                                          head_group_for((S_pad / kTile) * B * Hkv, B * Hkv), (int)Hkv,
+                                          dv_tm);
   if (int rc = check_launch("causal_attention_bwd fused")) return rc;
   const int64_t vectors = B * H * S * 16;
   attn_bwd3_finish_kernel<FMT><<<(unsigned)((vectors + 255) / 256), 256, 0, stream>>>(
@@ -491,11 +492,11 @@ namespace attn_bwd {
 int launch_bwd3_128(int fmt, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                     const CUtensorMap& mdo, const float* lse2_pad, const float* delta_pad,
                     float* dq_acc, void* dq, void* dk, void* dv, int64_t B, int64_t H, int64_t Hkv,
-                    int64_t S, int64_t S_pad, float scale, cudaStream_t stream) {
+                    int64_t S, int64_t S_pad, float scale, cudaStream_t stream, int dv_token_major) {
   return fmt == 1 ? launch3<1>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq_acc, dq, dk, dv, B, H, Hkv,
-                               S, S_pad, scale, stream)
+                               S, S_pad, scale, stream, dv_token_major)
                   : launch3<0>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq_acc, dq, dk, dv, B, H, Hkv,
-                               S, S_pad, scale, stream);
+                               S, S_pad, scale, stream, dv_token_major);
 }
 
 }  // namespace attn_bwd

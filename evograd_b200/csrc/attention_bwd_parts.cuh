@@ -40,15 +40,18 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
 
 // Rows of a [128 x HD] float32 TMEM accumulator -> 16-bit rows of [B*H, S, HD].
 // The CG column groups of compute warps take HD / CG columns each.
+// heads / token_major: layout of `out` (tensor_row in attention_common.cuh).
 template <int HD, int FMT, int CG = 2>
 __device__ __forceinline__ void store_rows(uint32_t t_acc, void* out, int bh, int row0, int S,
-                                           float scale, const Roles& r) {
+                                           float scale, const Roles& r, int heads = 1,
+                                           int token_major = 0) {
   constexpr int CW = HD / CG;             // columns per warp
   constexpr int PIECE = CW >= 32 ? 32 : 16;  // columns per TMEM read
   const uint32_t lane_base = (uint32_t)(r.quarter * 32) << 16;
   const int row = row0 + r.row;
   const bool ok = row < S;
-  uint8_t* dst = reinterpret_cast<uint8_t*>(out) + ((size_t)bh * S + (ok ? row : 0)) * HD * 2;
+  uint8_t* dst = reinterpret_cast<uint8_t*>(out) +
+                 tensor_row(bh, ok ? row : 0, S, heads, token_major) * HD * 2;
 #pragma unroll
   for (int c = 0; c < CW / PIECE; ++c) {
     const int col = r.half * CW + c * PIECE;
@@ -77,7 +80,8 @@ template <int HD, int FMT>
 __global__ void __launch_bounds__(256)
 attn_prepare_kernel(const void* __restrict__ do_ptr, const void* __restrict__ o_ptr,
                     const float* __restrict__ lse, float* __restrict__ lse2_pad,
-                    float* __restrict__ delta_pad, int S, int S_pad, int64_t padded_rows) {
+                    float* __restrict__ delta_pad, int S, int S_pad, int64_t padded_rows, int heads,
+                    int o_tm) {
   constexpr int TPR = HD / 8;
   const int64_t prow = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / TPR;
   const int part = threadIdx.x % TPR;
@@ -89,7 +93,8 @@ attn_prepare_kernel(const void* __restrict__ do_ptr, const void* __restrict__ o_
   if (ok) {
     const int64_t row = bh * S + q;
     const uint4 a = ld_vec(reinterpret_cast<const uint8_t*>(do_ptr) + (row * HD + part * 8) * 2);
-    const uint4 b = ld_vec(reinterpret_cast<const uint8_t*>(o_ptr) + (row * HD + part * 8) * 2);
+    const uint4 b = ld_vec(reinterpret_cast<const uint8_t*>(o_ptr) +
+                           (tensor_row((int)bh, q, S, heads, o_tm) * HD + part * 8) * 2);
     float af[8], bf[8];
     if constexpr (FMT == 1) { unpack<__nv_bfloat16>(a, af); unpack<__nv_bfloat16>(b, bf); }
     else { unpack<__half>(a, af); unpack<__half>(b, bf); }
@@ -125,7 +130,7 @@ int reserve_smem(Kernel kernel, size_t bytes) {
 int launch_bwd3_128(int fmt, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                     const CUtensorMap& mdo, const float* lse2_pad, const float* delta_pad,
                     float* dq_acc, void* dq, void* dk, void* dv, int64_t B, int64_t H, int64_t Hkv,
-                    int64_t S, int64_t S_pad, float scale, cudaStream_t stream);
+                    int64_t S, int64_t S_pad, float scale, cudaStream_t stream, int dv_token_major);
 
 }  // namespace attn_bwd
 }  // namespace evg

@@ -113,12 +113,27 @@ __device__ __forceinline__ BlockSetup carve(uint8_t* raw, size_t tile_region_byt
 }
 constexpr size_t kControlBytes = 24 * 8 + 64;
 
+// Optional token-major tensors of the tensor-core kernels: o as [B, S, H, D] (written
+// by the forward, read by the backward) and dv as [B, S, Hkv, D], which is how the
+// projections around the attention of a decoder layer want them (no transposing
+// copies). Everything else is [B, H, S, D].
+struct Layouts {
+  int o_token_major = 0;
+  int dv_token_major = 0;
+};
+// Row of a [B, H, S, D] (or, token-major, [B, S, H, D]) tensor that holds position s of
+// (batch, head) pair bh.
+__host__ __device__ __forceinline__ size_t tensor_row(int bh, int s, int S, int heads,
+                                                       int token_major) {
+  return token_major ? ((size_t)(bh / heads) * S + s) * heads + bh % heads : (size_t)bh * S + s;
+}
+
 // Two-tile warp-specialised forward (attention_fwd2.cu).
 // H query heads share Hkv key/value heads (H % Hkv == 0; Hkv == H is plain
 // multi-head attention): query head h reads k/v head h / (H / Hkv).
 int launch_fwd2_any(int head_dim, int fmt, const void* q, const void* k, const void* v, void* o,
                     float* lse, int64_t B, int64_t H, int64_t Hkv, int64_t S, float scale,
-                    cudaStream_t stream);
+                    cudaStream_t stream, Layouts lay = Layouts());
 // Pipelined backward (attention_bwd2.cu, attention_bwd3.cu): scratch = two float32
 // arrays padded to whole tiles per (batch, head), plus, at head size 128, a
 // float32 copy of dQ with the same padding. fmt: 0 float16, 1 bfloat16.
@@ -126,7 +141,7 @@ int64_t bwd2_workspace_bytes(int64_t B, int64_t H, int64_t S, int64_t D);
 int launch_bwd2_any(int head_dim, int fmt, const void* dout, const void* q, const void* k,
                     const void* v, const void* o, const float* lse, void* dq, void* dk, void* dv,
                     float* workspace, int64_t B, int64_t H, int64_t Hkv, int64_t S, float scale,
-                    cudaStream_t stream);
+                    cudaStream_t stream, Layouts lay = Layouts());
 // CUDA-core kernels for float32 and head sizes other than 64 / 128
 // (attention_generic.cu). Scratch: one float32 per query row.
 int64_t generic_bwd_workspace_bytes(int64_t B, int64_t Hq, int64_t S);

@@ -34,7 +34,8 @@ __global__ void __launch_bounds__(kFwd2Threads, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, void* __restrict__ o_ptr,
                  float* __restrict__ lse_ptr, int S, int group, float scale_log2,
-                 long long wait_limit, int n_pairs, int n_bh, int head_group) {
+                 long long wait_limit, int n_pairs, int n_bh, int head_group, int heads,
+                 int o_tm) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   BlockSetup bs = carve(smem_raw, 6 * TB);
@@ -250,8 +251,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       tc_fence_after_sync();
       const float inv_l = 1.0f / l_run;
       const bool row_ok = q_glob < S;
-      uint8_t* orow_g =
-          reinterpret_cast<uint8_t*>(o_ptr) + ((size_t)bh * S + (row_ok ? q_glob : 0)) * HD * 2;
+      uint8_t* orow_g = reinterpret_cast<uint8_t*>(o_ptr) +
+                        tensor_row(bh, row_ok ? q_glob : 0, S, heads, o_tm) * HD * 2;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t orow[32];
@@ -293,7 +294,7 @@ const bool g_fwd2_status_registered = (register_device_status(read_fwd2_status),
 
 template <int HD, int FMT>
 int launch_fwd2(const void* q, const void* k, const void* v, void* o, float* lse, int64_t B,
-                int64_t H, int64_t Hkv, int64_t S, float scale, cudaStream_t stream) {
+                int64_t H, int64_t Hkv, int64_t S, float scale, cudaStream_t stream, Layouts lay) {
   CUtensorMap mq, mk, mv;
   if (!encode_tile_map_16bit(&mq, q, FMT, HD, S, B * H, kTile) ||
       !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * Hkv, kTile) ||
@@ -313,7 +314,8 @@ int launch_fwd2(const void* q, const void* k, const void* v, void* o, float* lse
   const long long limit = t > 0 ? (long long)t * 1000000ll : 2000000000ll;
   kern<<<grid, kFwd2Threads, smem, stream>>>(mq, mk, mv, o, lse, (int)S, (int)(H / Hkv),
                                              scale * kLog2e, limit, (int)n_pairs, (int)(B * H),
-                                             head_group_for(n_pairs * B * H, B * H));
+                                             head_group_for(n_pairs * B * H, B * H), (int)H,
+                                             lay.o_token_major);
   return check_launch("causal_attention_fwd");
 }
 
@@ -323,12 +325,12 @@ namespace attn {
 
 int launch_fwd2_any(int head_dim, int fmt, const void* q, const void* k, const void* v, void* o,
                     float* lse, int64_t B, int64_t H, int64_t Hkv, int64_t S, float scale,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, Layouts lay) {
   if (head_dim == 128)
-    return fmt == 1 ? launch_fwd2<128, 1>(q, k, v, o, lse, B, H, Hkv, S, scale, stream)
-                    : launch_fwd2<128, 0>(q, k, v, o, lse, B, H, Hkv, S, scale, stream);
-  return fmt == 1 ? launch_fwd2<64, 1>(q, k, v, o, lse, B, H, Hkv, S, scale, stream)
-                  : launch_fwd2<64, 0>(q, k, v, o, lse, B, H, Hkv, S, scale, stream);
+    return fmt == 1 ? launch_fwd2<128, 1>(q, k, v, o, lse, B, H, Hkv, S, scale, stream, lay)
+                    : launch_fwd2<128, 0>(q, k, v, o, lse, B, H, Hkv, S, scale, stream, lay);
+  return fmt == 1 ? launch_fwd2<64, 1>(q, k, v, o, lse, B, H, Hkv, S, scale, stream, lay)
+                  : launch_fwd2<64, 0>(q, k, v, o, lse, B, H, Hkv, S, scale, stream, lay);
 }
 
 }  // namespace attn

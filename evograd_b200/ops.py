@@ -516,6 +516,59 @@ def causal_gqa_attention_bwd(do, q, k, v, o, lse, scale: float | None = None):
     return dq, dk, dv
 
 
+def _tensor_core_attention(q) -> bool:
+    return q.dtype in (torch.float16, torch.bfloat16) and q.shape[-1] in (64, 128)
+
+
+def causal_gqa_attention_fwd_tm(q, k, v, scale: float | None = None):
+    """:func:`causal_gqa_attention_fwd` returning ``o`` token-major, ``[B, S, Hq, D]``
+    (what the output projection of a decoder layer reads as ``[B*S, Hq*D]`` without a
+    transposing copy). The tensor-core kernels write that layout directly; other shapes
+    go through the head-major call and one transpose."""
+    dev = _require_cuda(q, k, v)
+    B, Hq, Hkv, S, D = _check_gqa(q, k, v)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    if not _tensor_core_attention(q) or q.numel() == 0:
+        o, lse = causal_gqa_attention_fwd(q, k, v, scale)
+        return o.transpose(1, 2).contiguous(), lse
+    q2, k2, v2 = q.contiguous(), k.contiguous(), v.contiguous()
+    o = torch.empty(B, S, Hq, D, device=dev, dtype=q.dtype)
+    lse = torch.empty(B, Hq, S, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        call("evg_causal_gqa_attention_fwd_tm", q2.data_ptr(), k2.data_ptr(), v2.data_ptr(),
+             o.data_ptr(), lse.data_ptr(), B, Hq, Hkv, S, D, float(scale), _dtype_enum(q),
+             _stream(dev))
+    return o, lse
+
+
+def causal_gqa_attention_bwd_tm(do, q, k, v, o_tm, lse, scale: float | None = None):
+    """Backward for a token-major ``o_tm`` ``[B, S, Hq, D]``; returns ``(dq, dk, dv_tm)``
+    with ``dv_tm`` token-major ``[B, S, Hkv, D]`` and dq, dk head-major."""
+    dev = _require_cuda(do, q, k, v, o_tm, lse)
+    B, Hq, Hkv, S, D = _check_gqa(q, k, v)
+    _same("do", do, "q", q)
+    if tuple(o_tm.shape) != (B, S, Hq, D) or o_tm.dtype != q.dtype:
+        raise ValueError("o_tm must be [B, S, Hq, D] in the dtype of q")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    if not _tensor_core_attention(q) or q.numel() == 0:
+        dq, dk, dv = causal_gqa_attention_bwd(do, q, k, v, o_tm.transpose(1, 2), lse, scale)
+        return dq, dk, dv.transpose(1, 2).contiguous()
+    do2, q2, k2, v2, o2 = (t.contiguous() for t in (do, q, k, v, o_tm))
+    dq, dk = torch.empty_like(q2), torch.empty_like(k2)
+    dv = torch.empty(B, S, Hkv, D, device=dev, dtype=q.dtype)
+    en = _dtype_enum(q)
+    with torch.cuda.device(dev):
+        ws_bytes = lib.evg_causal_gqa_attention_bwd_workspace_bytes(B, Hq, Hkv, S, D, en)
+        ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
+        call("evg_causal_gqa_attention_bwd_tm", do2.data_ptr(), q2.data_ptr(), k2.data_ptr(),
+             v2.data_ptr(), o2.data_ptr(), lse.contiguous().data_ptr(), dq.data_ptr(),
+             dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws_bytes, B, Hq, Hkv, S, D, float(scale),
+             en, _stream(dev))
+    return dq, dk, dv
+
+
 # ------------------------------------------------------------- evoattention
 def _check_evo(q, k, v, res_mask, pair_bias):
     if q.ndim != 5:

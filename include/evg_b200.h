@@ -37,7 +37,7 @@ extern "C" {
  *    partial sums over peer memory); evoattention head sizes 32 / 64 run on the
  *    tensor cores; attention entry points reject a scale that is not positive
  *    and finite. */
-#define EVG_ABI_VERSION 3
+#define EVG_ABI_VERSION 4
 
 enum evg_dtype { EVG_F32 = 0, EVG_F16 = 1, EVG_BF16 = 2 };
 
@@ -315,6 +315,27 @@ int evg_causal_gqa_attention_bwd(const void* dout, const void* q, const void* k,
                                  int64_t workspace_bytes, int64_t B, int64_t Hq,
                                  int64_t Hkv, int64_t S, int64_t D, float scale,
                                  int dtype, void* stream);
+
+/*
+ * The same two calls for a caller whose projections produce and consume
+ * token-major tensors (the decoder layer at
+ * ops/level3/llama3_decoder_layer/forward_ref.py:100-110 transposes o back to
+ * [B,S,H*D] before the output projection, and the gradient of v likewise):
+ * `o` is written / read as [B,S,Hq,D] and `dv` is written as [B,S,Hkv,D]; all
+ * other tensors keep the [B,H,S,D] layout. Tensor-core shapes only (16-bit, D in
+ * {64,128}, 16-byte aligned); EVG_EUNSUPPORTED otherwise.
+ */
+int evg_causal_gqa_attention_fwd_tm(const void* q, const void* k, const void* v,
+                                    void* o_token_major, float* lse, int64_t B,
+                                    int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
+                                    float scale, int dtype, void* stream);
+int evg_causal_gqa_attention_bwd_tm(const void* dout, const void* q, const void* k,
+                                    const void* v, const void* o_token_major,
+                                    const float* lse, void* dq, void* dk,
+                                    void* dv_token_major, void* workspace,
+                                    int64_t workspace_bytes, int64_t B, int64_t Hq,
+                                    int64_t Hkv, int64_t S, int64_t D, float scale,
+                                    int dtype, void* stream);
 
 /* ------------------------------------------------------------ evoattention
  * AlphaFold-3 style EvoformerAttention over [B, S, N, H, D] tensors (S = MSA
