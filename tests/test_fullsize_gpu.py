@@ -152,5 +152,13 @@ def test_rope_q_and_k_at_benchmark_size():
         assert torch.equal(y[:, tok].transpose(1, 2).cpu(), ref)
         n_in, n_out = x.float().norm(dim=-1), y.float().norm(dim=-1)
         assert torch.allclose(n_in, n_out, rtol=2e-2, atol=1e-2)
-    bq, _ = ops.rope_qk_bwd(yq, yk, cos, sin, layout="bthd")
+    bq, bk = ops.rope_qk_bwd(yq, yk, cos, sin, layout="bthd")
     assert torch.allclose(bq.float(), q.float(), atol=6e-2, rtol=2e-2)
+    # the backward on the same sample of positions against autograd of the oracle forward
+    # (upstream gradients: the rotated tensors themselves)
+    for up, got in ((yq, bq), (yk, bk)):
+        ups = up[:, tok].transpose(1, 2).cpu()
+        xs = torch.zeros_like(ups, dtype=torch.float32, requires_grad=True)
+        ref_out = ao.rope_forward(xs, cos_f.float(), sin_f.float())
+        (ref_grad,) = torch.autograd.grad(ref_out, xs, grad_outputs=ups.float())
+        assert torch.equal(got[:, tok].transpose(1, 2).cpu(), ref_grad.to(got.dtype))
