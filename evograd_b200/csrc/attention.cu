@@ -45,6 +45,37 @@ bool encode_tile_map_16bit(CUtensorMap* map, const void* base, int fmt, uint64_t
 }
 
 
+bool encode_tile_map_16bit_4d(CUtensorMap* map, const void* base, int fmt, uint64_t D, uint64_t S,
+                              uint64_t H, uint64_t B, uint32_t box_rows, bool token_major) {
+  using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      encode = (EncodeFn)fn;
+  });
+  if (!encode) return false;
+  const cuuint64_t dims[4] = {D, S, H, B};
+  // byte strides of positions, heads and batches
+  const cuuint64_t strides[3] = {token_major ? H * D * 2 : D * 2, token_major ? D * 2 : S * D * 2,
+                                 H * S * D * 2};
+  const cuuint32_t box[4] = {64, box_rows, 1, 1};
+  const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+  const CUresult rc = encode(
+      map, fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+      const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
 bool encode_tile_map_f32(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                          uint64_t outer, uint32_t box_cols, uint32_t box_rows, bool swizzle128) {
   using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -237,6 +268,7 @@ extern "C" int evg_causal_gqa_attention_fwd_tm(const void* q, const void* k, con
                 "causal_gqa_attention_fwd_tm: 16-bit, head size 64 / 128, 16-byte aligned only");
   attn::Layouts lay;
   lay.o_token_major = 1;
+  lay.v_token_major = 1;
   return attn::launch_fwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, q, k, v, o_token_major, lse, B,
                                Hq, Hkv, S, scale, (cudaStream_t)stream, lay);
 }
@@ -266,6 +298,8 @@ extern "C" int evg_causal_gqa_attention_bwd_tm(const void* dout, const void* q, 
   attn::Layouts lay;
   lay.o_token_major = 1;
   lay.dv_token_major = 1;
+  lay.v_token_major = 1;
+  lay.do_token_major = 1;
   return attn::launch_bwd2_any((int)D, dtype == EVG_BF16 ? 1 : 0, dout, q, k, v, o_token_major, lse,
                                dq, dk, dv_token_major, (float*)workspace, B, Hq, Hkv, S, scale,
                                (cudaStream_t)stream, lay);

@@ -139,7 +139,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   if (r.is_tma && r.lane == 0) {
     mbar_expect_tx(kv_full, 2 * TB);
     load_tile<HD>(sK, &map_k, kv0, bh, kv_full);
-    load_tile<HD>(sV, &map_v, kv0, bh, kv_full);
+    load_tile_bh<HD>(sV, &map_v, kv0, bh, heads_kv, kv_full);
     int it = 0, bhq = bh * group, git = 0;
     for (; git < n_git; ++git) {
       const int st = git & 1;
@@ -151,7 +151,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (git >= 2) mbar_wait(do_empty + st, ((git >> 1) - 1) & 1, ctx, 731);
       if (!*ctx.abort_flag) {
         mbar_expect_tx(do_full + st, TB + 1024);
-        load_tile<HD>(sDO0 + st * TB, &map_do, q0, bhq, do_full + st);
+        load_tile_bh<HD>(sDO0 + st * TB, &map_do, q0, bhq, heads_kv * group, do_full + st);
         bulk_load_1d(s_stat + st * 256, lse2_pad + (size_t)bhq * S_pad + q0, 512, do_full + st);
         bulk_load_1d(s_stat + st * 256 + 128, delta_pad + (size_t)bhq * S_pad + q0, 512,
                      do_full + st);

@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(256)
 attn_prepare_kernel(const void* __restrict__ do_ptr, const void* __restrict__ o_ptr,
                     const float* __restrict__ lse, float* __restrict__ lse2_pad,
                     float* __restrict__ delta_pad, int S, int S_pad, int64_t padded_rows, int heads,
-                    int o_tm) {
+                    int o_tm, int do_tm) {
   constexpr int TPR = HD / 8;
   const int64_t prow = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / TPR;
   const int part = threadIdx.x % TPR;
@@ -91,8 +91,8 @@ attn_prepare_kernel(const void* __restrict__ do_ptr, const void* __restrict__ o_
   const bool ok = q < S;
   float s = 0.f;
   if (ok) {
-    const int64_t row = bh * S + q;
-    const uint4 a = ld_vec(reinterpret_cast<const uint8_t*>(do_ptr) + (row * HD + part * 8) * 2);
+    const uint4 a = ld_vec(reinterpret_cast<const uint8_t*>(do_ptr) +
+                           (tensor_row((int)bh, q, S, heads, do_tm) * HD + part * 8) * 2);
     const uint4 b = ld_vec(reinterpret_cast<const uint8_t*>(o_ptr) +
                            (tensor_row((int)bh, q, S, heads, o_tm) * HD + part * 8) * 2);
     float af[8], bf[8];

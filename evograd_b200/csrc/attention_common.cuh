@@ -30,6 +30,16 @@ __device__ __forceinline__ void load_tile(uint8_t* smem_tile, const CUtensorMap*
     tma_load_3d(smem_tile + a * (kTile * 128), map, a * 64, row0, outer, bar);
 }
 
+// The same through a 4-D map (column, position, head, batch) of a tensor with `heads`
+// heads per batch: v and dO, which may be token-major.
+template <int HD>
+__device__ __forceinline__ void load_tile_bh(uint8_t* smem_tile, const CUtensorMap* map, int row0,
+                                             int bh, int heads, uint64_t* bar) {
+#pragma unroll
+  for (int a = 0; a < HD / 64; ++a)
+    tma_load_4d(smem_tile + a * (kTile * 128), map, a * 64, row0, bh % heads, bh / heads, bar);
+}
+
 // S[128xN] = A[128xHD] * B[NxHD]^T, both tiles K-major (N from the descriptor).
 template <int HD>
 __device__ __forceinline__ void issue_scores(bool lead, uint32_t d_tmem, uint32_t a_saddr,
@@ -113,13 +123,15 @@ __device__ __forceinline__ BlockSetup carve(uint8_t* raw, size_t tile_region_byt
 }
 constexpr size_t kControlBytes = 24 * 8 + 64;
 
-// Optional token-major tensors of the tensor-core kernels: o as [B, S, H, D] (written
-// by the forward, read by the backward) and dv as [B, S, Hkv, D], which is how the
+// Optional token-major tensors of the tensor-core kernels: v, o, dO as [B, S, H, D] and
+// dv as [B, S, Hkv, D], which is how the
 // projections around the attention of a decoder layer want them (no transposing
 // copies). Everything else is [B, H, S, D].
 struct Layouts {
   int o_token_major = 0;
   int dv_token_major = 0;
+  int v_token_major = 0;   // v and dO are read through 4-D TMA maps either way
+  int do_token_major = 0;
 };
 // Row of a [B, H, S, D] (or, token-major, [B, S, H, D]) tensor that holds position s of
 // (batch, head) pair bh.

@@ -97,7 +97,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         load_tile<HD>(sK[st], &map_k, j * kTile, bh_kv, k_full + st);
         if (j >= 2) mbar_wait(v_empty + st, ((j >> 1) - 1) & 1, ctx, 702);
         mbar_expect_tx(v_full + st, TB);
-        load_tile<HD>(sV[st], &map_v, j * kTile, bh_kv, v_full + st);
+        load_tile_bh<HD>(sV[st], &map_v, j * kTile, bh_kv, heads / group, v_full + st);
       }
     }
   } else if (warp == 1) {
@@ -298,7 +298,7 @@ int launch_fwd2(const void* q, const void* k, const void* v, void* o, float* lse
   CUtensorMap mq, mk, mv;
   if (!encode_tile_map_16bit(&mq, q, FMT, HD, S, B * H, kTile) ||
       !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * Hkv, kTile) ||
-      !encode_tile_map_16bit(&mv, v, FMT, HD, S, B * Hkv, kTile))
+      !encode_tile_map_16bit_4d(&mv, v, FMT, HD, S, Hkv, B, kTile, lay.v_token_major != 0))
     return fail(EVG_ELAUNCH, "causal_attention_fwd: cuTensorMapEncodeTiled failed");
   const size_t smem = 6 * tile_bytes<HD>() + kControlBytes + 1024;
   auto kern = attn_fwd2_kernel<HD, FMT>;

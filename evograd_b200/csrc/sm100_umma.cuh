@@ -22,6 +22,11 @@ namespace umma {
 bool encode_tile_map_16bit(CUtensorMap* map, const void* base, int fmt, uint64_t cols,
                            uint64_t rows, uint64_t outer, uint32_t box_rows);
 
+// A 16-bit [B, H, S, D] tensor (token_major: [B, S, H, D]) as a 4-D map with
+// coordinates (column, position, head, batch) and the same [box_rows x 64] tiles.
+bool encode_tile_map_16bit_4d(CUtensorMap* map, const void* base, int fmt, uint64_t D, uint64_t S,
+                              uint64_t H, uint64_t B, uint32_t box_rows, bool token_major);
+
 // The same for a dense float32 [outer, rows, cols] tensor with tiles of
 // [box_rows x box_cols]; swizzle128 needs box_cols == 32 (128 bytes per row).
 bool encode_tile_map_f32(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
@@ -118,6 +123,14 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
       "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
       "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c0, int c1,
+                                            int c2, int c3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
 // Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a

@@ -520,19 +520,22 @@ def _tensor_core_attention(q) -> bool:
     return q.dtype in (torch.float16, torch.bfloat16) and q.shape[-1] in (64, 128)
 
 
-def causal_gqa_attention_fwd_tm(q, k, v, scale: float | None = None):
-    """:func:`causal_gqa_attention_fwd` returning ``o`` token-major, ``[B, S, Hq, D]``
-    (what the output projection of a decoder layer reads as ``[B*S, Hq*D]`` without a
-    transposing copy). The tensor-core kernels write that layout directly; other shapes
-    go through the head-major call and one transpose."""
-    dev = _require_cuda(q, k, v)
+def causal_gqa_attention_fwd_tm(q, k, v_tm, scale: float | None = None):
+    """:func:`causal_gqa_attention_fwd` for a decoder layer's layouts: ``v_tm`` is
+    token-major ``[B, S, Hkv, D]`` (a view of its projection's output) and ``o`` comes
+    back token-major ``[B, S, Hq, D]`` (what the output projection reads as
+    ``[B*S, Hq*D]``); q and k are ``[B, H, S, D]``. The tensor-core kernels read and
+    write those layouts directly; other shapes go through the head-major call and
+    transposing copies."""
+    dev = _require_cuda(q, k, v_tm)
+    v = v_tm.transpose(1, 2)
     B, Hq, Hkv, S, D = _check_gqa(q, k, v)
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     if not _tensor_core_attention(q) or q.numel() == 0:
         o, lse = causal_gqa_attention_fwd(q, k, v, scale)
         return o.transpose(1, 2).contiguous(), lse
-    q2, k2, v2 = q.contiguous(), k.contiguous(), v.contiguous()
+    q2, k2, v2 = q.contiguous(), k.contiguous(), v_tm.contiguous()
     o = torch.empty(B, S, Hq, D, device=dev, dtype=q.dtype)
     lse = torch.empty(B, Hq, S, device=dev, dtype=torch.float32)
     with torch.cuda.device(dev):
@@ -542,20 +545,23 @@ def causal_gqa_attention_fwd_tm(q, k, v, scale: float | None = None):
     return o, lse
 
 
-def causal_gqa_attention_bwd_tm(do, q, k, v, o_tm, lse, scale: float | None = None):
-    """Backward for a token-major ``o_tm`` ``[B, S, Hq, D]``; returns ``(dq, dk, dv_tm)``
-    with ``dv_tm`` token-major ``[B, S, Hkv, D]`` and dq, dk head-major."""
-    dev = _require_cuda(do, q, k, v, o_tm, lse)
+def causal_gqa_attention_bwd_tm(do_tm, q, k, v_tm, o_tm, lse, scale: float | None = None):
+    """Backward for token-major ``do_tm`` / ``o_tm`` ``[B, S, Hq, D]`` and ``v_tm``
+    ``[B, S, Hkv, D]``; returns ``(dq, dk, dv_tm)`` with ``dv_tm`` token-major and dq, dk
+    head-major."""
+    dev = _require_cuda(do_tm, q, k, v_tm, o_tm, lse)
+    v = v_tm.transpose(1, 2)
     B, Hq, Hkv, S, D = _check_gqa(q, k, v)
-    _same("do", do, "q", q)
-    if tuple(o_tm.shape) != (B, S, Hq, D) or o_tm.dtype != q.dtype:
-        raise ValueError("o_tm must be [B, S, Hq, D] in the dtype of q")
+    for name, t in (("do_tm", do_tm), ("o_tm", o_tm)):
+        if tuple(t.shape) != (B, S, Hq, D) or t.dtype != q.dtype:
+            raise ValueError(f"{name} must be [B, S, Hq, D] in the dtype of q")
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     if not _tensor_core_attention(q) or q.numel() == 0:
-        dq, dk, dv = causal_gqa_attention_bwd(do, q, k, v, o_tm.transpose(1, 2), lse, scale)
+        dq, dk, dv = causal_gqa_attention_bwd(do_tm.transpose(1, 2), q, k, v,
+                                              o_tm.transpose(1, 2), lse, scale)
         return dq, dk, dv.transpose(1, 2).contiguous()
-    do2, q2, k2, v2, o2 = (t.contiguous() for t in (do, q, k, v, o_tm))
+    do2, q2, k2, v2, o2 = (t.contiguous() for t in (do_tm, q, k, v_tm, o_tm))
     dq, dk = torch.empty_like(q2), torch.empty_like(k2)
     dv = torch.empty(B, S, Hkv, D, device=dev, dtype=q.dtype)
     en = _dtype_enum(q)

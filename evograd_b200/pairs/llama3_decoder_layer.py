@@ -13,9 +13,10 @@ post-attention residual stream and the gate/up activations. Both normalised
 activations, the SwiGLU product and the head-major copies are recomputed in the
 backward. RoPE reads the projection output through a transposed view and
 writes the attention layout directly (and the reverse in the backward), so no
-separate transpose pass exists for q and k; the attention kernels write o and
-dv token-major ([B, T, H, hd]), which is what the projections around them
-read, so only v and the upstream gradient of o are still transposed by a copy.
+separate transpose pass exists for q and k; the attention kernels read v and the
+upstream gradient of o and write o and dv token-major ([B, T, H, hd]), which
+is how the projections around them produce and consume them: no transposing
+copies at all.
 dK/dV are summed over each query group inside the attention kernel.
 
 Candidate module for evograd's gate and benchmarks (``evograd verify --op
@@ -59,8 +60,8 @@ def _forward_with_saved_impl(x, input_norm_weight, q_weight, k_weight, v_weight,
     v = torch.mm(h, v_weight.t())
     qr = ops.rope_fwd(_heads_first(q, B, T, Hq, hd), cos, sin, layout="bhtd")
     kr = ops.rope_fwd(_heads_first(k, B, T, Hkv, hd), cos, sin, layout="bhtd")
-    vv = _heads_first(v, B, T, Hkv, hd).contiguous()
-    o, lse = ops.causal_gqa_attention_fwd_tm(qr, kr, vv)  # o is [B, T, Hq, hd]: no transpose
+    vv = v.view(B, T, Hkv, hd)  # token-major, as the projection wrote it
+    o, lse = ops.causal_gqa_attention_fwd_tm(qr, kr, vv)  # o is [B, T, Hq, hd] as well
     attn = o.view(B * T, Hq * hd)
     x1 = torch.addmm(x2, attn, o_weight.t())            # residual add in the GEMM epilogue
     h2, rstd2 = ops.rmsnorm_fwd(x1, post_norm_weight, eps)
@@ -97,7 +98,7 @@ def _backward_from_saved_impl(dout, saved_tensors, eps=1e-5):
     # attention
     attn = o.view(B * T, Hq * hd)
     d_o_w = torch.mm(d_x1.t(), attn)
-    d_attn = _heads_first(torch.mm(d_x1, Wo), B, T, Hq, hd).contiguous()
+    d_attn = torch.mm(d_x1, Wo).view(B, T, Hq, hd)
     dq, dk, dv = ops.causal_gqa_attention_bwd_tm(d_attn, qr, kr, vv, o, lse)  # dv [B, T, Hkv, hd]
     dq2 = torch.empty(B, T, Hq, hd, device=dq.device, dtype=dq.dtype)
     dk2 = torch.empty(B, T, Hkv, hd, device=dk.device, dtype=dk.dtype)

@@ -320,17 +320,21 @@ int evg_causal_gqa_attention_bwd(const void* dout, const void* q, const void* k,
  * The same two calls for a caller whose projections produce and consume
  * token-major tensors (the decoder layer at
  * ops/level3/llama3_decoder_layer/forward_ref.py:100-110 transposes o back to
- * [B,S,H*D] before the output projection, and the gradient of v likewise):
- * `o` is written / read as [B,S,Hq,D] and `dv` is written as [B,S,Hkv,D]; all
- * other tensors keep the [B,H,S,D] layout. Tensor-core shapes only (16-bit, D in
- * {64,128}, 16-byte aligned); EVG_EUNSUPPORTED otherwise.
+ * [B,S,H*D] before the output projection, v comes out of its projection as
+ * [B,S,Hkv*D], and their gradients likewise): v, o and dout are read / written
+ * as [B,S,H,D] and dv is written as [B,S,Hkv,D]; q, k, dq, dk (which pass
+ * through RoPE, which changes layout on the way) and lse keep the [B,H,S,D] /
+ * [B,H,S] layout. Tensor-core shapes only (16-bit, D in {64,128}, 16-byte
+ * aligned); EVG_EUNSUPPORTED otherwise.
  */
-int evg_causal_gqa_attention_fwd_tm(const void* q, const void* k, const void* v,
+int evg_causal_gqa_attention_fwd_tm(const void* q, const void* k,
+                                    const void* v_token_major,
                                     void* o_token_major, float* lse, int64_t B,
                                     int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
                                     float scale, int dtype, void* stream);
-int evg_causal_gqa_attention_bwd_tm(const void* dout, const void* q, const void* k,
-                                    const void* v, const void* o_token_major,
+int evg_causal_gqa_attention_bwd_tm(const void* dout_token_major, const void* q,
+                                    const void* k, const void* v_token_major,
+                                    const void* o_token_major,
                                     const float* lse, void* dq, void* dk,
                                     void* dv_token_major, void* workspace,
                                     int64_t workspace_bytes, int64_t B, int64_t Hq,

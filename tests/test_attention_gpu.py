@@ -223,23 +223,25 @@ def test_grouped_query_attention_matches_the_oracle(B, Hq, Hkv, S, D, dtype):
 @pytest.mark.parametrize("B,Hq,Hkv,S,D,dtype", [
     (2, 8, 2, 300, 128, "bfloat16"), (1, 4, 4, 129, 64, "float16"), (1, 2, 1, 65, 32, "float32"),
 ])
-def test_token_major_output_and_dv_equal_the_head_major_results(B, Hq, Hkv, S, D, dtype):
-    """``*_tm`` writes o as [B, S, Hq, D] and dv as [B, S, Hkv, D] (what a decoder layer's
-    projections read): same bits as the head-major call, transposed (dq of the fused
-    head-size-128 backward up to float32 summation order). Shapes off the tensor-core
-    path go through the head-major kernels and a transpose."""
+def test_token_major_tensors_equal_the_head_major_results(B, Hq, Hkv, S, D, dtype):
+    """``*_tm`` reads v and dO as [B, S, H, D] and writes o as [B, S, Hq, D] and dv as
+    [B, S, Hkv, D] (how a decoder layer's projections produce and consume them): same
+    bits as the head-major call, transposed (dq of the fused head-size-128 backward up
+    to float32 summation order). Shapes off the tensor-core path go through the
+    head-major kernels and transposing copies."""
     from evograd_b200 import ops
 
     dt = getattr(torch, dtype)
     torch.manual_seed(S + D)
     q, do = ((torch.randn(B, Hq, S, D) * 0.5).to(dt).cuda() for _ in range(2))
     k, v = ((torch.randn(B, Hkv, S, D) * 0.5).to(dt).cuda() for _ in range(2))
+    v_tm, do_tm = v.transpose(1, 2).contiguous(), do.transpose(1, 2).contiguous()
     o, lse = ops.causal_gqa_attention_fwd(q, k, v)
-    o_tm, lse_tm = ops.causal_gqa_attention_fwd_tm(q, k, v)
+    o_tm, lse_tm = ops.causal_gqa_attention_fwd_tm(q, k, v_tm)
     assert tuple(o_tm.shape) == (B, S, Hq, D) and o_tm.is_contiguous()
     assert torch.equal(o_tm.transpose(1, 2), o) and torch.equal(lse, lse_tm)
     dq, dk, dv = ops.causal_gqa_attention_bwd(do, q, k, v, o, lse)
-    dq2, dk2, dv_tm = ops.causal_gqa_attention_bwd_tm(do, q, k, v, o_tm, lse)
+    dq2, dk2, dv_tm = ops.causal_gqa_attention_bwd_tm(do_tm, q, k, v_tm, o_tm, lse)
     assert tuple(dv_tm.shape) == (B, S, Hkv, D) and dv_tm.is_contiguous()
     assert torch.equal(dv_tm.transpose(1, 2), dv) and torch.equal(dk2, dk)
     if D == 128 and dtype != "float32":
