@@ -51,7 +51,8 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                     const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
                     void* __restrict__ dq_ptr, int S, int S_pad, int group, float scale,
-                    long long wait_limit, int n_bh, int head_group, int heads) {
+                    long long wait_limit, int n_bh, int head_group, int heads, int v_tm,
+                    int do_tm) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   BlockSetup bs = carve(smem_raw, 7 * TB);
@@ -108,7 +109,7 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (r.is_tma && r.lane == 0) {
     mbar_expect_tx(qdo_full, 2 * TB);
     load_tile<HD>(sQ, &map_q, q0, bh, qdo_full);
-    load_tile_bh<HD>(sDO, &map_do, q0, bh, heads, qdo_full);
+    load_tile_bh<HD>(sDO, &map_do, q0, bh, heads, do_tm, qdo_full);
     for (int j = 0; j < n_it; ++j) {
       const int ks = j % 3, vs = j & 1;
       if (j >= 3) mbar_wait(k_empty + ks, ((j / 3) - 1) & 1, ctx, 501);
@@ -116,7 +117,7 @@ attn_bwd2_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       load_tile<HD>(sK[ks], &map_k, j * kTile, bh_kv, k_full + ks);
       if (j >= 2) mbar_wait(v_empty + vs, ((j >> 1) - 1) & 1, ctx, 510);
       mbar_expect_tx(v_full + vs, TB);
-      load_tile_bh<HD>(sV[vs], &map_v, j * kTile, bh_kv, heads / group, v_full + vs);
+      load_tile_bh<HD>(sV[vs], &map_v, j * kTile, bh_kv, heads / group, v_tm, v_full + vs);
     }
   } else if (r.is_mma) {
     // All 32 lanes run this program; `lead` predicates the tcgen05 instructions.
@@ -251,7 +252,7 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
                       void* __restrict__ dk_ptr, void* __restrict__ dv_ptr, int S, int S_pad,
                       int group, float scale, long long wait_limit, uint32_t smem_bytes, int n_bh,
-                      int head_group, int heads_kv, int dv_tm) {
+                      int head_group, int heads_kv, int dv_tm, int v_tm, int do_tm) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   constexpr uint32_t kTiles = 4 + QST;
@@ -321,7 +322,7 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   if (r.is_tma && r.lane == 0) {
     mbar_expect_tx(kv_full, 2 * TB);
     load_tile<HD>(sK, &map_k, kv0, bh, kv_full);
-    load_tile_bh<HD>(sV, &map_v, kv0, bh, heads_kv, kv_full);
+    load_tile_bh<HD>(sV, &map_v, kv0, bh, heads_kv, v_tm, kv_full);
     int it = 0, bhq = bh * group, git = 0;
     int qs = 0, q_round = 0;  // Q stage of tile git and how often the ring has wrapped
     for (; git < n_git; ++git) {
@@ -334,7 +335,7 @@ attn_bwd2_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (git >= 2) mbar_wait(do_empty + ds, ((git >> 1) - 1) & 1, ctx, 631);
       if (!*ctx.abort_flag) {
         mbar_expect_tx(do_full + ds, TB + 1024);
-        load_tile_bh<HD>(sDO0 + ds * TB, &map_do, q0, bhq, heads_kv * group, do_full + ds);
+        load_tile_bh<HD>(sDO0 + ds * TB, &map_do, q0, bhq, heads_kv * group, do_tm, do_full + ds);
         bulk_load_1d(s_stat + ds * 256, lse2_pad + (size_t)bhq * S_pad + q0, 512, do_full + ds);
         bulk_load_1d(s_stat + ds * 256 + 128, delta_pad + (size_t)bhq * S_pad + q0, 512,
                      do_full + ds);
@@ -523,8 +524,8 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
   const int group = (int)(H / Hkv);
   if (!encode_tile_map_16bit(&mq, q, FMT, HD, S, B * H, kTile) ||
       !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * Hkv, kTile) ||
-      !encode_tile_map_16bit_4d(&mv, v, FMT, HD, S, Hkv, B, kTile, lay.v_token_major != 0) ||
-      !encode_tile_map_16bit_4d(&mdo, dout, FMT, HD, S, H, B, kTile, lay.do_token_major != 0))
+      !encode_bh_map(&mv, v, FMT, HD, S, Hkv, B, lay.v_token_major) ||
+      !encode_bh_map(&mdo, dout, FMT, HD, S, H, B, lay.do_token_major))
     return fail(EVG_ELAUNCH, "causal_attention_bwd: cuTensorMapEncodeTiled failed");
   const int64_t n_q = (S + kTile - 1) / kTile;
   const int64_t S_pad = n_q * kTile;
@@ -544,7 +545,7 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
   if constexpr (HD == 128) {
     if (!tune("attention.two_kernel_bwd"))
       return launch_bwd3_128(FMT, mq, mk, mv, mdo, lse2_pad, delta_pad, workspace + 2 * padded_rows,
-                             dq, dk, dv, B, H, Hkv, S, S_pad, scale, stream, lay.dv_token_major);
+                             dq, dk, dv, B, H, Hkv, S, S_pad, scale, stream, lay);
   }
   dim3 grid((unsigned)(n_q * B * H));
   const long long limit = wait_limit_cycles2();
@@ -561,7 +562,8 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
                                                    (int)S, (int)S_pad, group, scale, limit,
                                                    (uint32_t)smem, (int)(B * Hkv),
                                                    head_group_for(n_q * B * Hkv, B * Hkv), (int)Hkv,
-                                                   lay.dv_token_major);
+                                                   lay.dv_token_major, lay.v_token_major,
+                                                   lay.do_token_major);
     if (int rc = check_launch("causal_attention_bwd dkdv")) return rc;
   }
   {
@@ -570,7 +572,8 @@ int launch_bwd2(const void* dout, const void* q, const void* k, const void* v, c
     if (int rc = reserve_smem(kern, smem)) return rc;
     kern<<<grid, kThreads2, smem, stream>>>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq, (int)S,
                                             (int)S_pad, group, scale, limit, (int)(B * H),
-                                            head_group_for(n_q * B * H, B * H), (int)H);
+                                            head_group_for(n_q * B * H, B * H), (int)H,
+                                            lay.v_token_major, lay.do_token_major);
     if (int rc = check_launch("causal_attention_bwd dq")) return rc;
   }
   return EVG_OK;

@@ -65,7 +65,8 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                  const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad,
                  float* __restrict__ dq_acc, void* __restrict__ dk_ptr, void* __restrict__ dv_ptr,
                  int S, int S_pad, int group, float scale, long long wait_limit,
-                 uint32_t smem_bytes, int n_bh, int head_group, int heads_kv, int dv_tm) {
+                 uint32_t smem_bytes, int n_bh, int head_group, int heads_kv, int dv_tm,
+                 int v_tm, int do_tm) {
   constexpr int HD = 128;
   constexpr int CG = kCG3;
   constexpr int CPW = 64 / CG;  // query columns of a chunk per compute warp (16)
@@ -139,7 +140,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   if (r.is_tma && r.lane == 0) {
     mbar_expect_tx(kv_full, 2 * TB);
     load_tile<HD>(sK, &map_k, kv0, bh, kv_full);
-    load_tile_bh<HD>(sV, &map_v, kv0, bh, heads_kv, kv_full);
+    load_tile_bh<HD>(sV, &map_v, kv0, bh, heads_kv, v_tm, kv_full);
     int it = 0, bhq = bh * group, git = 0;
     for (; git < n_git; ++git) {
       const int st = git & 1;
@@ -151,7 +152,7 @@ attn_bwd3_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (git >= 2) mbar_wait(do_empty + st, ((git >> 1) - 1) & 1, ctx, 731);
       if (!*ctx.abort_flag) {
         mbar_expect_tx(do_full + st, TB + 1024);
-        load_tile_bh<HD>(sDO0 + st * TB, &map_do, q0, bhq, heads_kv * group, do_full + st);
+        load_tile_bh<HD>(sDO0 + st * TB, &map_do, q0, bhq, heads_kv * group, do_tm, do_full + st);
         bulk_load_1d(s_stat + st * 256, lse2_pad + (size_t)bhq * S_pad + q0, 512, do_full + st);
         bulk_load_1d(s_stat + st * 256 + 128, delta_pad + (size_t)bhq * S_pad + q0, 512,
                      do_full + st);
@@ -446,7 +447,7 @@ template <int FMT>
 int launch3(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
             const CUtensorMap& mdo, const float* lse2_pad, const float* delta_pad, float* dq_acc,
             void* dq, void* dk, void* dv, int64_t B, int64_t H, int64_t Hkv, int64_t S,
-            int64_t S_pad, float scale, cudaStream_t stream, int dv_tm) {
+            int64_t S_pad, float scale, cudaStream_t stream, Layouts lay) {
   const size_t acc_bytes = (size_t)B * H * S_pad * 128 * sizeof(float);
   if (cudaMemsetAsync(dq_acc, 0, acc_bytes, stream) != cudaSuccess) {
     cudaGetLastError();
@@ -462,7 +463,7 @@ int launch3(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                                           (int)S, (int)S_pad, (int)(H / Hkv), scale,
                                           wait_limit_cycles2(), (uint32_t)smem, (int)(B * Hkv),
                                           head_group_for((S_pad / kTile) * B * Hkv, B * Hkv), (int)Hkv,
-                                          dv_tm);
+                                          lay.dv_token_major, lay.v_token_major, lay.do_token_major);
   if (int rc = check_launch("causal_attention_bwd fused")) return rc;
   const int64_t vectors = B * H * S * 16;
   attn_bwd3_finish_kernel<FMT><<<(unsigned)((vectors + 255) / 256), 256, 0, stream>>>(
@@ -492,11 +493,11 @@ namespace attn_bwd {
 int launch_bwd3_128(int fmt, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                     const CUtensorMap& mdo, const float* lse2_pad, const float* delta_pad,
                     float* dq_acc, void* dq, void* dk, void* dv, int64_t B, int64_t H, int64_t Hkv,
-                    int64_t S, int64_t S_pad, float scale, cudaStream_t stream, int dv_token_major) {
+                    int64_t S, int64_t S_pad, float scale, cudaStream_t stream, Layouts lay) {
   return fmt == 1 ? launch3<1>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq_acc, dq, dk, dv, B, H, Hkv,
-                               S, S_pad, scale, stream, dv_token_major)
+                               S, S_pad, scale, stream, lay)
                   : launch3<0>(mq, mk, mv, mdo, lse2_pad, delta_pad, dq_acc, dq, dk, dv, B, H, Hkv,
-                               S, S_pad, scale, stream, dv_token_major);
+                               S, S_pad, scale, stream, lay);
 }
 
 }  // namespace attn_bwd

@@ -130,7 +130,7 @@ int reserve_smem(Kernel kernel, size_t bytes) {
 int launch_bwd3_128(int fmt, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                     const CUtensorMap& mdo, const float* lse2_pad, const float* delta_pad,
                     float* dq_acc, void* dq, void* dk, void* dv, int64_t B, int64_t H, int64_t Hkv,
-                    int64_t S, int64_t S_pad, float scale, cudaStream_t stream, int dv_token_major);
+                    int64_t S, int64_t S_pad, float scale, cudaStream_t stream, Layouts lay);
 
 }  // namespace attn_bwd
 }  // namespace evg

@@ -35,7 +35,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                  const __grid_constant__ CUtensorMap map_v, void* __restrict__ o_ptr,
                  float* __restrict__ lse_ptr, int S, int group, float scale_log2,
                  long long wait_limit, int n_pairs, int n_bh, int head_group, int heads,
-                 int o_tm) {
+                 int o_tm, int v_tm) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t TB = tile_bytes<HD>();
   BlockSetup bs = carve(smem_raw, 6 * TB);
@@ -97,7 +97,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         load_tile<HD>(sK[st], &map_k, j * kTile, bh_kv, k_full + st);
         if (j >= 2) mbar_wait(v_empty + st, ((j >> 1) - 1) & 1, ctx, 702);
         mbar_expect_tx(v_full + st, TB);
-        load_tile_bh<HD>(sV[st], &map_v, j * kTile, bh_kv, heads / group, v_full + st);
+        load_tile_bh<HD>(sV[st], &map_v, j * kTile, bh_kv, heads / group, v_tm, v_full + st);
       }
     }
   } else if (warp == 1) {
@@ -298,7 +298,7 @@ int launch_fwd2(const void* q, const void* k, const void* v, void* o, float* lse
   CUtensorMap mq, mk, mv;
   if (!encode_tile_map_16bit(&mq, q, FMT, HD, S, B * H, kTile) ||
       !encode_tile_map_16bit(&mk, k, FMT, HD, S, B * Hkv, kTile) ||
-      !encode_tile_map_16bit_4d(&mv, v, FMT, HD, S, Hkv, B, kTile, lay.v_token_major != 0))
+      !encode_bh_map(&mv, v, FMT, HD, S, Hkv, B, lay.v_token_major))
     return fail(EVG_ELAUNCH, "causal_attention_fwd: cuTensorMapEncodeTiled failed");
   const size_t smem = 6 * tile_bytes<HD>() + kControlBytes + 1024;
   auto kern = attn_fwd2_kernel<HD, FMT>;
@@ -315,7 +315,7 @@ int launch_fwd2(const void* q, const void* k, const void* v, void* o, float* lse
   kern<<<grid, kFwd2Threads, smem, stream>>>(mq, mk, mv, o, lse, (int)S, (int)(H / Hkv),
                                              scale * kLog2e, limit, (int)n_pairs, (int)(B * H),
                                              head_group_for(n_pairs * B * H, B * H), (int)H,
-                                             lay.o_token_major);
+                                             lay.o_token_major, lay.v_token_major);
   return check_launch("causal_attention_fwd");
 }
 
