@@ -13,11 +13,13 @@ constexpr int kThreads = 256;
 
 // Gate activations: value and derivative in float32.
 struct Silu {  // ops/level1/swiglu/forward_ref.py:9
+  // (The reciprocal is the fast one, two ulp: an IEEE division costs the forward an
+  // eighth of its time, and the result is rounded to 16 bits or compared at 1e-5.)
   __device__ static __forceinline__ float value(float a) {
-    return a * (1.0f / (1.0f + __expf(-a)));
+    return a * __fdividef(1.0f, 1.0f + __expf(-a));
   }
   __device__ static __forceinline__ void both(float a, float& val, float& der) {
-    const float sg = 1.0f / (1.0f + __expf(-a));
+    const float sg = __fdividef(1.0f, 1.0f + __expf(-a));
     val = a * sg;
     der = sg * (1.0f + a * (1.0f - sg));
   }
