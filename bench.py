@@ -1217,10 +1217,10 @@ TRAFFIC_NCU = {
                "sources": TRAFFIC_SOURCES["rmsnorm"], "digest": "cae7476223bb"},
     "fused_add_rms_norm": {"bytes": 975700000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
                           "sources": TRAFFIC_SOURCES["fused_add_rms_norm"], "digest": "30e168a60c7e"},
-    "geglu": {"bytes": 4293000000, "profile": "profiles/geglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
-             "sources": TRAFFIC_SOURCES["geglu"], "digest": "bb456aae4e70"},
-    "swiglu": {"bytes": 4317000000, "profile": "profiles/swiglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
-              "sources": TRAFFIC_SOURCES["swiglu"], "digest": "bb456aae4e70"},
+    "geglu": {"bytes": 4306000000, "profile": "profiles/geglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
+             "sources": TRAFFIC_SOURCES["geglu"], "digest": "70fc4295b6b2"},
+    "swiglu": {"bytes": 4307000000, "profile": "profiles/swiglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
+              "sources": TRAFFIC_SOURCES["swiglu"], "digest": "70fc4295b6b2"},
     "softmax_vocab": {"bytes": 2858000000, "profile": "profiles/softmax_bf16_512x128256.md (512 rows, scaled x 8)",
                      "sources": TRAFFIC_SOURCES["softmax_vocab"], "digest": "9f8abf4a231e"},
     "softmax": {"bytes": 33600000, "profile": "profiles/softmax_f32_4096x1024.md",
