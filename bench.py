@@ -1211,18 +1211,18 @@ TRAFFIC_SOURCES = {
 TRAFFIC_NCU = {
     # python bench.py --source-digest NAME prints the digest of a workload's kernel sources as
     # they are now; an entry whose digest no longer matches is reported as stale, not used
-    "layernorm": {"bytes": 382200000, "profile": "profiles/layernorm_bf16_16384x4096.md",
-                 "sources": TRAFFIC_SOURCES["layernorm"], "digest": "cae7476223bb"},
-    "rmsnorm": {"bytes": 674500000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
-               "sources": TRAFFIC_SOURCES["rmsnorm"], "digest": "cae7476223bb"},
-    "fused_add_rms_norm": {"bytes": 975700000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
-                          "sources": TRAFFIC_SOURCES["fused_add_rms_norm"], "digest": "30e168a60c7e"},
+    "layernorm": {"bytes": 381800000, "profile": "profiles/layernorm_bf16_16384x4096.md",
+                 "sources": TRAFFIC_SOURCES["layernorm"], "digest": "47f7f19b396c"},
+    "rmsnorm": {"bytes": 678900000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
+               "sources": TRAFFIC_SOURCES["rmsnorm"], "digest": "47f7f19b396c"},
+    "fused_add_rms_norm": {"bytes": 973300000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
+                          "sources": TRAFFIC_SOURCES["fused_add_rms_norm"], "digest": "d70cdba26a8c"},
     "geglu": {"bytes": 4306000000, "profile": "profiles/geglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
              "sources": TRAFFIC_SOURCES["geglu"], "digest": "70fc4295b6b2"},
     "swiglu": {"bytes": 4307000000, "profile": "profiles/swiglu_bf16_4096x14336.md (4096 rows, scaled x 8)",
               "sources": TRAFFIC_SOURCES["swiglu"], "digest": "70fc4295b6b2"},
-    "softmax_vocab": {"bytes": 2858000000, "profile": "profiles/softmax_bf16_512x128256.md (512 rows, scaled x 8)",
-                     "sources": TRAFFIC_SOURCES["softmax_vocab"], "digest": "9f8abf4a231e"},
+    "softmax_vocab": {"bytes": 2859000000, "profile": "profiles/softmax_bf16_512x128256.md (512 rows, scaled x 8)",
+                     "sources": TRAFFIC_SOURCES["softmax_vocab"], "digest": "73990a043930"},
     "softmax": {"bytes": 33600000, "profile": "profiles/softmax_f32_4096x1024.md",
                "sources": TRAFFIC_SOURCES["softmax"], "digest": "1c5eac59092e"},
     "rope": {"bytes": 840800000, "profile": "profiles/rope_bf16_qk_2x4096x32x128.md (batch 2, scaled x 4)",
