@@ -20,7 +20,8 @@ namespace {
 // their 16-bit form in shared memory, because float32 copies of both for a row of
 // 8192+ columns leave room for one block per SM only.
 template <typename T, int G, int VPT, bool LN, bool WBP = false>
-__global__ void __launch_bounds__(rowcfg_max_threads(G), G > 512 ? 1 : 2)
+__global__ void __launch_bounds__(G > 256 ? rowcfg_max_threads(G) : 256,
+                                  G > 512 ? 1 : (G > 256 ? 2 : 3))
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
                 T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                 int64_t rows, int cols, float eps) {
@@ -60,16 +61,30 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __res
   __syncthreads();
   const float inv_cols = 1.0f / (float)cols;
 
-  for (int64_t row = (int64_t)blockIdx.x * groups + gid; row < rows;
-       row += (int64_t)gridDim.x * groups) {
-    const T* xr = x + row * cols;
-    float xf[VPT][N];
+  // The next row of the group is on its way while this one is reduced and written:
+  // its vectors are requested before the first reduction and unpacked a row later.
+  const int64_t row_step = (int64_t)gridDim.x * groups;
+  uint4 nxt[VPT];
+  {
+    const int64_t row0 = (int64_t)blockIdx.x * groups + gid;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int idx = lig + k * G;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (idx < nvec) v = ld_vec(xr + (size_t)idx * N);
-      unpack<T>(v, xf[k]);  // padded vectors unpack to zeros
+      nxt[k] = make_uint4(0, 0, 0, 0);
+      if (row0 < rows && idx < nvec) nxt[k] = ld_vec(x + row0 * cols + (size_t)idx * N);
+    }
+  }
+  for (int64_t row = (int64_t)blockIdx.x * groups + gid; row < rows; row += row_step) {
+    float xf[VPT][N];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) unpack<T>(nxt[k], xf[k]);  // padded vectors unpack to zeros
+    if (row + row_step < rows) {
+      const T* xn = x + (row + row_step) * cols;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int idx = lig + k * G;
+        if (idx < nvec) nxt[k] = ld_vec(xn + (size_t)idx * N);
+      }
     }
     float mu = 0.f;
     if constexpr (LN) {
@@ -186,6 +201,7 @@ int launch_norm_fwd(const void* x, const void* w, const void* b, void* y, float*
                       (!LN || aligned16(b)) && hidden < (int64_t)1 << 31;
   RowCfg cfg;
   if (vec_ok && !tune("rows.force_generic") && pick_rowcfg(op, hidden / N, cfg)) {
+    if (cfg.G <= 256 && cfg.threads > 256) cfg.threads = 256;  // the kernel's launch bound
     const int groups = cfg.threads / cfg.G;
     constexpr bool kCanPack = LN && sizeof(T) == 2;
     const bool packed = kCanPack && cfg.G >= 512;
