@@ -318,6 +318,7 @@ add_rms_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   }
   // After a timeout every wait above fell through, so the last copies may still be
   // in flight: give them time to land before the block's shared memory is given up.
+  grid_dependents_go();  // the column reduce may be launched behind this grid now
   if (tid == 0 && *(volatile int*)abort_flag) settle_after_abort();
   float* pw = partial + (size_t)blockIdx.x * cols;
 #pragma unroll
@@ -597,9 +598,7 @@ int launch_add_rms_bwd(const void* dy, const void* x, const void* r, const void*
   if ((int64_t)blocks * hidden * (int64_t)sizeof(float) > workspace_bytes)
     return fail(EVG_EWORKSPACE, "%s: internal: partial rows exceed workspace", op);
   if (dweight || out_f32) {
-    dim3 grid((unsigned)((hidden + 31) / 32), 1);
-    colreduce_kernel<T><<<grid, dim3(32, 32), 0, stream>>>(partial, blocks, hidden, (T*)dweight,
-                                                           (T*)nullptr, out_f32);
+    launch_colreduce<T>(partial, blocks, hidden, (T*)dweight, (T*)nullptr, out_f32, 1, stream);
     rc = check_launch("fused_add_rmsnorm_bwd colreduce");
   }
   return rc;

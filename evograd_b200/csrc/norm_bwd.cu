@@ -345,6 +345,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
       parity ^= 1;
     }
   }
+  grid_dependents_go();
   // After a timeout every wait above fell through, so the last copies may still be
   // in flight: give them time to land before the block's shared memory is given up.
   if (tid == 0 && *(volatile int*)abort_flag) settle_after_abort();
@@ -368,6 +369,238 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
         }
       }
     }
+  }
+}
+
+// Tile-ring variant for rows of fewer than 256 vectors: consecutive rows are
+// contiguous in memory, so one ring stage holds a TILE of R = 256 / G whole rows
+// of x and of dy, brought in by two bulk copies; group g of the block (G threads,
+// VPT vectors per thread) works on row g of the tile. The bytes in flight per SM
+// are set by the ring depth and not by registers or occupancy, which lets a
+// thread own 16 or 24 elements of a row (the per-row reduction, barrier and
+// statistics are paid once per thread and row) with two blocks per SM, the shape
+// that the one-row ring above runs at for wide rows. A thread's columns never
+// change, so its weight vectors stay in registers. The one block barrier per
+// tile serves the per-group reductions and releases the stage for refilling.
+template <typename T, int G, int VPT, bool LN, int THREADS = 256>
+__global__ void __launch_bounds__(THREADS,
+                                  VPT > 1 ? 2 : (LN && sizeof(T) == 2) ? 3 : 4)
+norm_bwd_tile_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                          const T* __restrict__ w, const float* __restrict__ mean,
+                          const float* __restrict__ rstd, T* __restrict__ dx,
+                          float* __restrict__ partial, int64_t rows, int cols, int stages,
+                          long long wait_limit) {
+  using namespace umma;
+  static_assert(G % 32 == 0 && THREADS % G == 0, "groups are whole warps, blocks whole groups");
+  constexpr int WARPS = THREADS / 32;
+  constexpr int R = THREADS / G;  // rows per tile
+  constexpr int W = G / 32;       // warps per group
+  constexpr int N = Vec<T>::N;
+  constexpr int P = N / 2;
+  constexpr int NV = LN ? 2 : 1;
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  const int tid = threadIdx.x;
+  const int gid = tid / G, lig = tid % G;
+  const int nvec = cols / N;
+  const uint32_t row_bytes = (uint32_t)cols * sizeof(T);
+  const uint32_t tile_bytes = R * row_bytes;
+  // smem: [stages][2][tile_bytes] ring | mbarriers | [2][NV][WARPS] scratch | abort flag
+  uint8_t* ring = ring_raw;
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + (size_t)stages * 2 * tile_bytes);
+  float* scratch = reinterpret_cast<float*>(full + 16);
+  int* abort_flag = reinterpret_cast<int*>(scratch + 2 * NV * WARPS);
+  int phase = 0;
+
+  const int64_t n_tiles = (rows + R - 1) / R;
+  const int64_t first = blockIdx.x;
+  const int64_t n_mine = first < n_tiles ? (n_tiles - first + gridDim.x - 1) / gridDim.x : 0;
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const WaitCtx ctx{abort_flag, &g_norm_device_status, wait_limit};
+  auto issue = [&](int64_t i) {
+    const int s = (int)(i % stages);
+    const int64_t row0 = (first + i * gridDim.x) * R;
+    const int64_t left = rows - row0;
+    const uint32_t bytes = (left < R ? (uint32_t)left : (uint32_t)R) * row_bytes;
+    uint8_t* dst = ring + (size_t)s * 2 * tile_bytes;
+    mbar_expect_tx(&full[s], 2 * bytes);
+    bulk_load_1d(dst, x + row0 * cols, bytes, &full[s]);
+    bulk_load_1d(dst + tile_bytes, dy + row0 * cols, bytes, &full[s]);
+  };
+  if (tid == 0)
+    for (int64_t i = 0; i < stages && i < n_mine; ++i) issue(i);
+
+  f32x2 wp[VPT][P], acc_w[VPT][P], acc_b[LN ? VPT : 1][P];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int idx = lig + k * G;
+    float f[N];
+    uint4 wv = make_uint4(0, 0, 0, 0);
+    if (idx < nvec) wv = *reinterpret_cast<const uint4*>(w + (size_t)idx * N);
+    unpack<T>(wv, f);
+#pragma unroll
+    for (int j = 0; j < P; ++j) {
+      wp[k][j] = f2_make(f[2 * j], f[2 * j + 1]);
+      acc_w[k][j] = 0ull;
+      if constexpr (LN) acc_b[k][j] = 0ull;
+    }
+  }
+  const float inv_cols = 1.0f / (float)cols;
+  const int64_t row_step = (int64_t)gridDim.x * R;
+  int64_t row = first * R + gid;
+  float rs_next = 0.f, mu_next = 0.f;
+  if (n_mine > 0 && row < rows) {
+    rs_next = rstd[row];
+    if constexpr (LN) mu_next = mean[row];
+  }
+
+  int s = 0;
+  uint32_t parity = 0;
+  for (int64_t i = 0; i < n_mine; ++i) {
+    const float rs = rs_next;
+    const float nmr = LN ? -mu_next * rs : 0.f;
+    const bool row_ok = row < rows;
+    rs_next = 0.f;
+    if (i + 1 < n_mine && row + row_step < rows) {  // statistics of the next tile's row
+      rs_next = rstd[row + row_step];
+      if constexpr (LN) mu_next = mean[row + row_step];
+    }
+    mbar_wait(&full[s], parity, ctx, 402);
+    const uint8_t* sx = ring + (size_t)s * 2 * tile_bytes + (size_t)gid * row_bytes;
+    const f32x2 rs2 = f2_splat(rs), nmr2 = f2_splat(nmr);
+    f32x2 xh[VPT][P], gy[VPT][P];
+    f32x2 c0 = 0ull, c1 = 0ull;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = lig + k * G;
+      uint4 xv = make_uint4(0, 0, 0, 0), gv = make_uint4(0, 0, 0, 0);
+      if (row_ok && idx < nvec) {  // rows past the end and padded lanes count as dy = 0
+        xv = *reinterpret_cast<const uint4*>(sx + (size_t)idx * 16);
+        gv = *reinterpret_cast<const uint4*>(sx + tile_bytes + (size_t)idx * 16);
+      }
+      float xf[N], gf[N];
+      unpack<T>(xv, xf);
+      unpack<T>(gv, gf);
+#pragma unroll
+      for (int j = 0; j < P; ++j) {
+        const f32x2 xp = f2_make(xf[2 * j], xf[2 * j + 1]);
+        gy[k][j] = f2_make(gf[2 * j], gf[2 * j + 1]);
+        xh[k][j] = LN ? f2_fma(xp, rs2, nmr2) : f2_mul(xp, rs2);
+        const f32x2 g = f2_mul(gy[k][j], wp[k][j]);
+        c0 = f2_fma(g, xh[k][j], c0);
+        if constexpr (LN) c1 = f2_add(c1, g);
+      }
+    }
+    float c[NV];
+    {
+      float lo, hi;
+      f2_split(c0, lo, hi);
+      c[0] = lo + hi;
+      if constexpr (LN) {
+        f2_split(c1, lo, hi);
+        c[1] = lo + hi;
+      }
+    }
+    // Sum over the group: shuffles inside a warp, then the group's W warps in a
+    // fixed order. Every thread of the block has read its vectors from stage s
+    // before it reaches the barrier, so the barrier also frees the stage.
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) c[v] += __shfl_xor_sync(0xffffffffu, c[v], off);
+    }
+    float* buf = scratch + phase * (NV * WARPS);
+    if constexpr (W > 1) {
+      if ((tid & 31) == 0) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) buf[v * WARPS + (tid >> 5)] = c[v];
+      }
+    }
+    __syncthreads();
+    if constexpr (W > 1) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        float sum = buf[v * WARPS + gid * W];
+#pragma unroll
+        for (int q = 1; q < W; ++q) sum += buf[v * WARPS + gid * W + q];
+        c[v] = sum;
+      }
+      phase ^= 1;
+    }
+    if (tid == 0 && i + stages < n_mine) issue(i + stages);
+    // dx = rs*g - rs*mean(g) - rs*mean(g*xh)*xh
+    const f32x2 a_x = f2_splat(-rs * (c[0] * inv_cols));
+    const f32x2 a_0 = f2_splat(LN ? -rs * (c[1] * inv_cols) : 0.f);
+    T* dr = dx + row * cols;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = lig + k * G;
+      float o[N];
+#pragma unroll
+      for (int j = 0; j < P; ++j) {
+        const f32x2 g = f2_mul(gy[k][j], wp[k][j]);
+        const f32x2 op = f2_fma(xh[k][j], a_x, f2_fma(g, rs2, a_0));
+        f2_split(op, o[2 * j], o[2 * j + 1]);
+        acc_w[k][j] = f2_fma(gy[k][j], xh[k][j], acc_w[k][j]);
+        if constexpr (LN) acc_b[k][j] = f2_add(acc_b[k][j], gy[k][j]);
+      }
+      if (row_ok && idx < nvec) st_vec(dr + (size_t)idx * N, pack<T>(o));
+    }
+    row += row_step;
+    if (++s == stages) {
+      s = 0;
+      parity ^= 1;
+    }
+  }
+  grid_dependents_go();
+  if (tid == 0 && *(volatile int*)abort_flag) settle_after_abort();
+  __syncthreads();
+  // Every copy has landed and been read: the ring now holds the [NV][cols] float32
+  // column buffer in which the block's groups are folded in group order.
+  float* colbuf = reinterpret_cast<float*>(ring);
+  for (int g = 0; g < R; ++g) {
+    if (gid == g) {
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        const int idx = lig + k * G;
+        if (idx < nvec) {
+#pragma unroll
+          for (int j = 0; j < P; ++j) {
+            float a0, a1;
+            f2_split(acc_w[k][j], a0, a1);
+            float* cw = colbuf + (size_t)idx * N + 2 * j;
+            if (g == 0) {
+              cw[0] = a0;
+              cw[1] = a1;
+            } else {
+              cw[0] += a0;
+              cw[1] += a1;
+            }
+            if constexpr (LN) {
+              f2_split(acc_b[k][j], a0, a1);
+              float* cb = cw + cols;
+              if (g == 0) {
+                cb[0] = a0;
+                cb[1] = a1;
+              } else {
+                cb[0] += a0;
+                cb[1] += a1;
+              }
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* pw = partial + (size_t)blockIdx.x * cols;
+  for (int c = tid; c < cols; c += THREADS) {
+    pw[c] = colbuf[c];
+    if constexpr (LN) pw[(size_t)gridDim.x * cols + c] = colbuf[cols + c];
   }
 }
 
@@ -474,10 +707,9 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
                       aligned16(w) && hidden < (int64_t)1 << 31;
   RowCfg cfg;
   bool launched = false;
-  // Rows of fewer than 256 vectors (under 4 KB) would leave half of a ring block's
-  // threads idle and pay its per-row barriers for little data: they go to the
-  // group kernel below, several rows per block at a time (measured at
-  // [65536, 1024] bf16: RMSNorm backward 0.45 -> 0.84 of HBM peak).
+  // Rows of fewer than 256 vectors (under 4 KB) would leave half of a one-row ring
+  // block's threads idle and pay its per-row barriers for little data: they go to
+  // the tile ring below, several rows per stage.
   const bool narrow_rows = vec_ok && hidden / N < 256;
   if (vec_ok && !narrow_rows && !tune("rows.force_generic") && !tune("norm_bwd.no_ring") &&
       !tune(LN ? "layernorm_bwd.group" : "rmsnorm_bwd.group")) {
@@ -490,13 +722,15 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
     const size_t fixed = (size_t)hidden * sizeof(float) + 16 * 8 + 2 * NV * 32 * sizeof(float) + 64;
     const size_t budget = (size_t)device_info().max_smem_optin;
     int stages = tune("norm_bwd.stages");
-    if (stages <= 0) stages = (int)((48 * 1024) / (2 * row_bytes));  // 3 for 8 KB rows
-    if (stages < 2) stages = 2;
+    // About 48 KB of rows in flight per block, and three stages where they fit
+    // ([4096, 8192] bf16: LayerNorm 46.4 -> 43.7 us, RMSNorm 41.0 -> 37.1 us against two).
+    if (stages <= 0) stages = (int)((48 * 1024) / (2 * row_bytes));
+    if (stages < 3) stages = 3;
     if (stages > 12) stages = 12;
     while (stages > 0 && fixed + (size_t)stages * 2 * row_bytes > budget) --stages;
     long long wait_limit = 2000000000ll;
     const int ring_cap = cap;
-    if (stages >= 2 && nvec <= 8 * ring_threads) {
+    if (stages >= 2 && nvec <= 8 * ring_threads) {  // (the budget loop above may leave two)
       const size_t smem = fixed + (size_t)stages * 2 * row_bytes;
 #define EVG_RING(t, v)                                                                           \
   if (!launched && ring_threads == t && nvec <= (int64_t)v * t) {                                \
@@ -513,34 +747,59 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
 #undef EVG_RING
     }
   }
-  // (16-bit RMSNorm rows measured better on the four-vector group shape below: 0.84 / 0.76.)
-  // (Rows of 129 ... 192 vectors fill three quarters of a 256-thread group; the
-  // three-vector shape of the general path has no idle lanes there.)
-  if (narrow_rows && (LN || sizeof(T) == 4) && !(hidden / N > 128 && hidden / N <= 192) &&
-      !tune("rows.force_generic") &&
+  // Tile ring for narrow rows (`norm_bwd.tile_ring` = 2 switches it off). Shape: up to 32
+  // vectors, one per thread of a warp; above, two (float32: or three) vectors per thread on
+  // the smallest group that holds the row. Measured on bf16, fraction of the copy bandwidth,
+  // group kernels -> tile ring: [65536, 1024] LayerNorm 0.70 -> 0.85, RMSNorm 0.85 -> 0.92;
+  // [49152, 1536] 0.72 -> 0.85, 0.85 -> 0.91; [131072, 512] 0.71 -> 0.83, 0.75 -> 0.91;
+  // [32768, 2040] 0.64 -> 0.86, 0.79 -> 0.96.
+  if (narrow_rows && !launched && tune("norm_bwd.tile_ring") != 2 &&
+      !tune("rows.force_generic") && !tune("norm_bwd.no_ring") &&
       !tune(LN ? "layernorm_bwd.group" : "rmsnorm_bwd.group")) {
-    // Rows of fewer than 256 vectors: ONE vector per thread (groups of 32 ... 256
-    // threads), so a thread keeps 8 or 16 column sums instead of 32 or 64, the
-    // kernel needs ~60 registers and four blocks share an SM ([65536, 1024] bf16
-    // LayerNorm backward: 0.65 of the copy bandwidth with two vectors per thread
-    // and two blocks per SM).
     const int nv = (int)(hidden / N);
-    const int G = nv <= 32 ? 32 : nv <= 64 ? 64 : nv <= 128 ? 128 : 256;
-    const int threads = 256, groups = threads / G;
-    const size_t smem =
-        ((size_t)groups * 2 * NV * (G / 32) + (size_t)(NV + 1) * hidden) * sizeof(float);
-#define EVG_XN(g)                                                                              \
-  if (!launched && G == g) {                                                                   \
-    auto kern = norm_bwd_kernel<T, g, 1, LN>;                                                  \
-    if (smem > 48 * 1024)                                                                      \
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-    blocks = persistent_grid(kern, threads, smem, rows, groups, cap);                          \
-    kern<<<blocks, threads, smem, stream>>>((const T*)dy, (const T*)x, (const T*)w, mean,      \
-                                            rstd, (T*)dx, partial, rows, (int)hidden);         \
+    int G = 32, V = 1, threads = 256;
+    if (nv > 128 && nv <= 192) {  // 96-thread groups, two vectors each: no idle lanes
+      G = 96;
+      V = 2;
+      threads = 192;  // (288 threads would leave 96 registers per thread: spills)
+    } else if (nv > 32) {
+      int best = 1 << 30;
+      for (int v = 2; v <= (sizeof(T) == 4 ? 3 : 2); ++v) {  // three 16-bit vectors spill
+        int g = 32;
+        while (g * v < nv) g *= 2;
+        if (g * v < best) {
+          best = g * v;
+          G = g;
+          V = v;
+        }
+      }
+    }
+    const size_t tile_pair = (size_t)2 * (threads / G) * hidden * sizeof(T);
+    int stages = tune("norm_bwd.stages");
+    // Ring bytes per block: two blocks of 48 KB, four of 40 KB, or three of 56 KB per SM
+    // (one 16-bit LayerNorm vector per thread needs ~70 registers).
+    const bool three = V == 1 && LN && sizeof(T) == 2;
+    if (stages <= 0) stages = (int)(((V > 1 ? 48 : three ? 56 : 40) * 1024) / tile_pair);
+    if (stages < 2) stages = 2;
+    if (stages > 12) stages = 12;
+    const size_t smem = (size_t)stages * tile_pair + 16 * 8 + 2 * NV * 16 * sizeof(float) + 64;
+    const long long wait_limit = 2000000000ll;
+#define EVG_TR(g, v, t)                                                                        \
+  if (!launched && G == g && V == v && threads == t) {                                         \
+    auto kern = norm_bwd_tile_ring_kernel<T, g, v, LN, t>;                                     \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+    blocks = persistent_grid(kern, t, smem, rows, t / g, cap);                                 \
+    kern<<<blocks, t, smem, stream>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd,      \
+                                      (T*)dx, partial, rows, (int)hidden, stages, wait_limit); \
     launched = true;                                                                           \
   }
-    EVG_XN(32) EVG_XN(64) EVG_XN(128) EVG_XN(256)
-#undef EVG_XN
+    EVG_TR(32, 1, 256)
+    EVG_TR(32, 2, 256) EVG_TR(64, 2, 256) EVG_TR(128, 2, 256)
+    EVG_TR(96, 2, 192)
+    if constexpr (sizeof(T) == 4) {
+      EVG_TR(32, 3, 256)
+    }
+#undef EVG_TR
   }
   if (!launched && vec_ok && !tune("rows.force_generic") &&
       pick_rowcfg(op, hidden / N, cfg, narrow_rows ? 256 : 512, LN)) {
@@ -584,9 +843,7 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
     return check_launch("norm_bwd colreduce + exchange");
   }
   if (dweight || dbias || out_f32) {
-    dim3 grid((unsigned)((hidden + 31) / 32), NV);
-    colreduce_kernel<T><<<grid, dim3(32, 32), 0, stream>>>(partial, blocks, hidden, (T*)dweight,
-                                                           (T*)dbias, out_f32);
+    launch_colreduce<T>(partial, blocks, hidden, (T*)dweight, (T*)dbias, out_f32, NV, stream);
     rc = check_launch("norm_bwd colreduce");
   }
   return rc;

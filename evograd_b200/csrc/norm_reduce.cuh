@@ -7,6 +7,20 @@
 namespace evg {
 
 #ifdef __CUDACC__
+// Programmatic dependent launch of stage 2 behind stage 1: the column-reduce grid
+// is launched while the row kernel's last blocks are still running (its blocks
+// become resident as the row kernel's blocks leave) and sleeps in
+// grid_dependency_wait() until the row kernel has completed and its writes are
+// visible; the launch latency between the two kernels is hidden. The row kernels
+// call grid_dependents_go() when their row loop is over. Without the launch
+// attribute both instructions do nothing.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependents_go() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Stage 2: out[c] = sum_p partial[p][c]. Block = 32 columns x 32 row slices;
 // a slice adds its rows p = y, y+32, ... with four independent accumulators
 // (so four loads are in flight per thread), the slices are then added in
@@ -20,6 +34,7 @@ colreduce_kernel(const float* __restrict__ partial, int blocks, int64_t cols, T*
   const float* src = partial + (size_t)which * blocks * cols;
   const int64_t col = (int64_t)blockIdx.x * 32 + threadIdx.x;
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  grid_dependency_wait();
   if (col < cols) {
     int p = threadIdx.y;
     for (; p + 96 < blocks; p += 128) {
@@ -125,5 +140,26 @@ inline int max_partial_blocks(int64_t hidden = (int64_t)1 << 40) {
   if (per_sm <= 0) per_sm = hidden <= 2048 ? 4 : 2;
   return device_info().sm_count * per_sm;
 }
+
+
+#ifdef __CUDACC__
+// Launches stage 2 as a programmatic dependent of the kernel before it in `stream`
+// (`norm_bwd.no_pdl` = 1: as a plain launch).
+template <typename T>
+inline void launch_colreduce(const float* partial, int blocks, int64_t cols, T* out_w, T* out_b,
+                             float* out_f32, int parts, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((cols + 31) / 32), (unsigned)parts);
+  cfg.blockDim = dim3(32, 32);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tune("norm_bwd.no_pdl") ? 0 : 1;
+  cudaLaunchKernelEx(&cfg, colreduce_kernel<T>, partial, blocks, cols, out_w, out_b, out_f32);
+}
+#endif
 
 }  // namespace evg

@@ -57,6 +57,11 @@ CASES = {
         ((17, 1000), ("bfloat16", "float32")), ((1, 8192), ("float32",)), ((3, 40000), ("float32",)),
         ((4096, 1024), ("bfloat16",)), ((333, 5120), ("bfloat16", "float16")),
         ((97, 12288), ("bfloat16",)), ((65, 6144), ("float32",)),
+        # rows of fewer than 256 vectors: one case per shape of the backward's tile ring
+        # (group x vectors per thread), with row counts that leave the last tile ragged
+        ((2049, 64), ("bfloat16",)), ((1001, 768), ("bfloat16",)), ((4099, 1536), ("bfloat16", "float16")),
+        ((777, 2040), ("bfloat16",)), ((1234, 1032), ("float16",)), ((515, 768), ("float32",)),
+        ((515, 384), ("float32",)), ((3, 1024), ("bfloat16",)),
     ) for dt in dts],
     "rmsnorm": [(dict(rows=r, hidden=h), dt) for (r, h), dts in (
         ((8, 64), ("float32",)), ((17, 128), ("float32",)), ((32, 256), ("float16", "bfloat16")),
@@ -64,6 +69,9 @@ CASES = {
         ((17, 4096), ("bfloat16",)), ((4096, 8192), ("bfloat16",)), ((17, 127), ("float32", "float16")),
         ((17, 513), ("float16",)), ((17, 1000), ("float32",)), ((2, 24576), ("bfloat16",)),
         ((333, 5120), ("bfloat16",)), ((97, 12288), ("bfloat16",)),
+        ((2049, 64), ("bfloat16",)), ((1001, 768), ("float16",)), ((4099, 1536), ("bfloat16",)),
+        ((777, 2040), ("bfloat16",)), ((515, 768), ("float32",)), ((515, 384), ("float32",)),
+        ((3, 1024), ("bfloat16",)),
     ) for dt in dts],
     "swiglu": [(dict(rows=r, cols=c), dt) for (r, c), dts in (
         ((8, 64), ("float32",)), ((17, 128), ("float32",)), ((32, 256), ("float16", "bfloat16")),
@@ -123,6 +131,7 @@ def test_parameter_gradients_are_bit_reproducible(op):
 @pytest.mark.parametrize("op", ["layernorm", "rmsnorm", "softmax"])
 @pytest.mark.parametrize("knobs", [
     {"rows.force_generic": 1}, {"norm_bwd.no_ring": 1}, {"norm_bwd.stages": 2},
+    {"norm_bwd.tile_ring": 2}, {"norm_bwd.no_pdl": 1},
     {"group": 64, "vpt": 8}, {"group": 256, "vpt": 2}, {"group": 512, "vpt": 1}, {"group": 256, "vpt": 3},
     {"group": 128, "vpt": 4, "threads": 512}, {"group": 32, "vpt": 4, "threads": 128},
 ])
