@@ -29,7 +29,7 @@ const char* const kTuneKeys[] = {
     "rmsnorm_bwd.threads",      "rope.generic",           "norm_bwd.no_ring",
     "norm_bwd.stages",         "norm_bwd.ring_threads",      "attention.wait_limit",
     "softmax.no_cluster",       "softmax.cluster",        "softmax.cluster_stages", "softmax.cluster_threads", "evoattention.no_stage", "evoattention.no_tc",
-    "attention.two_kernel_bwd", "norm_bwd.tile_ring", "norm_bwd.no_pdl",
+    "attention.two_kernel_bwd", "norm_bwd.tile_ring", "norm_bwd.no_pdl", "norm_bwd.narrow_colreduce",
 };
 }  // namespace
 

@@ -188,6 +188,12 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
   constexpr int N = Vec<T>::N;
   constexpr int Q = N / 4;
   constexpr int NV = LN ? 2 : 1;
+  // LayerNorm with eight vectors per thread: 128 registers of column sums leave no
+  // room for x-hat and dy of the whole row (255 registers and spills). The row is
+  // then read from the ring twice, once for the row sums and once for dx and the
+  // column sums, and the stage is given back after the second pass.
+  constexpr bool TWO_PASS = LN && VPT * THREADS >= 2048;
+  constexpr int KEEP = TWO_PASS ? 1 : VPT;
   extern __shared__ __align__(128) uint8_t ring_raw[];
   const int tid = threadIdx.x;
   const int nvec = cols / N;
@@ -271,15 +277,12 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
     const uint8_t* sg = sx + row_bytes;
     const f32x2 rs2 = f2_splat(rs), nmr2 = f2_splat(nmr);
 
-    f32x2 xh[VPT][P], gy[VPT][P];
-    f32x2 c0 = 0ull, c1 = 0ull;  // sum g*xh, sum g (g = dy*w), per pair lane
-#pragma unroll
-    for (int k = 0; k < VPT; ++k) {
+    f32x2 xh[KEEP][P], gy[KEEP][P];
+    // x-hat and dy of vector k of this thread, from the ring stage
+    auto fetch = [&](int k, f32x2 (&xo)[P], f32x2 (&go)[P]) {
       const int idx = tid + k * THREADS;
-      const bool ok = idx < nvec;
-      const int sidx = ok ? idx : 0;
       uint4 xv = make_uint4(0, 0, 0, 0), gv = make_uint4(0, 0, 0, 0);
-      if (ok) {
+      if (idx < nvec) {
         xv = *reinterpret_cast<const uint4*>(sx + (size_t)idx * 16);
         gv = *reinterpret_cast<const uint4*>(sg + (size_t)idx * 16);
       }
@@ -287,17 +290,29 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
       unpack<T>(xv, xf);
       unpack<T>(gv, gf);  // padded vectors have dy = 0 and add nothing below
 #pragma unroll
+      for (int pi = 0; pi < P; ++pi) {
+        const f32x2 xp = f2_make(xf[2 * pi], xf[2 * pi + 1]);
+        go[pi] = f2_make(gf[2 * pi], gf[2 * pi + 1]);
+        xo[pi] = LN ? f2_fma(xp, rs2, nmr2) : f2_mul(xp, rs2);
+      }
+    };
+    f32x2 c0 = 0ull, c1 = 0ull;  // sum g*xh, sum g (g = dy*w), per pair lane
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int idx = tid + k * THREADS;
+      const int sidx = idx < nvec ? idx : 0;
+      f32x2(&xk)[P] = xh[TWO_PASS ? 0 : k];
+      f32x2(&gk)[P] = gy[TWO_PASS ? 0 : k];
+      fetch(k, xk, gk);
+#pragma unroll
       for (int qq = 0; qq < Q; ++qq) {
         const float4 wv = w4[qq * nvec + sidx];
         const f32x2 wp[2] = {f2_make(wv.x, wv.y), f2_make(wv.z, wv.w)};
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int pi = 2 * qq + h;
-          const f32x2 xp = f2_make(xf[2 * pi], xf[2 * pi + 1]);
-          gy[k][pi] = f2_make(gf[2 * pi], gf[2 * pi + 1]);
-          xh[k][pi] = LN ? f2_fma(xp, rs2, nmr2) : f2_mul(xp, rs2);
-          const f32x2 g = f2_mul(gy[k][pi], wp[h]);
-          c0 = f2_fma(g, xh[k][pi], c0);
+          const f32x2 g = f2_mul(gk[pi], wp[h]);
+          c0 = f2_fma(g, xk[pi], c0);
           if constexpr (LN) c1 = f2_add(c1, g);
         }
       }
@@ -313,13 +328,17 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
       }
     }
     block_allreduce_sum_fixed<NV, THREADS / 32>(c, scratch, phase);  // all done with stage s
-    if (tid == 0 && i + stages < n_mine) issue(i + stages);
+    if constexpr (!TWO_PASS)
+      if (tid == 0 && i + stages < n_mine) issue(i + stages);
     // dx = rs*g - rs*mean(g) - rs*mean(g*xh)*xh
     const f32x2 a_x = f2_splat(-rs * (c[0] * inv_cols));
     const f32x2 a_0 = f2_splat(LN ? -rs * (c[1] * inv_cols) : 0.f);
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int idx = tid + k * THREADS;
+      f32x2(&xk)[P] = xh[TWO_PASS ? 0 : k];
+      f32x2(&gk)[P] = gy[TWO_PASS ? 0 : k];
+      if constexpr (TWO_PASS) fetch(k, xk, gk);
       if (idx < nvec) {
         float o[N];
 #pragma unroll
@@ -329,15 +348,19 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T*
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int pi = 2 * qq + h;
-            const f32x2 g = f2_mul(gy[k][pi], wp[h]);
-            const f32x2 op = f2_fma(xh[k][pi], a_x, f2_fma(g, rs2, a_0));
+            const f32x2 g = f2_mul(gk[pi], wp[h]);
+            const f32x2 op = f2_fma(xk[pi], a_x, f2_fma(g, rs2, a_0));
             f2_split(op, o[2 * pi], o[2 * pi + 1]);
-            acc_w[k][pi] = f2_fma(gy[k][pi], xh[k][pi], acc_w[k][pi]);
-            if constexpr (LN) acc_b[k][pi] = f2_add(acc_b[k][pi], gy[k][pi]);
+            acc_w[k][pi] = f2_fma(gk[pi], xk[pi], acc_w[k][pi]);
+            if constexpr (LN) acc_b[k][pi] = f2_add(acc_b[k][pi], gk[pi]);
           }
         }
         st_vec(dr + (size_t)idx * N, pack<T>(o));
       }
+    }
+    if constexpr (TWO_PASS) {
+      __syncthreads();  // the second pass has read stage s too
+      if (tid == 0 && i + stages < n_mine) issue(i + stages);
     }
     dr += row_step;
     if (++s == stages) {

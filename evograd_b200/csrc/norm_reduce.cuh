@@ -21,39 +21,61 @@ __device__ __forceinline__ void grid_dependents_go() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-// Stage 2: out[c] = sum_p partial[p][c]. Block = 32 columns x 32 row slices;
-// a slice adds its rows p = y, y+32, ... with four independent accumulators
-// (so four loads are in flight per thread), the slices are then added in
-// order. Fixed order throughout: bit-reproducible. gridDim.y = dweight / dbias.
-template <typename T>
+// Stage 2: out[c] = sum_p partial[p][c]. Block = 32 column groups x 32 row
+// slices; a thread owns CV adjacent columns (one 4-, 8- or 16-byte load per row)
+// and its slice adds rows p = y, y+32, ... with four independent accumulators
+// per column (so four loads are in flight per thread); the slices are then added
+// in order. The order of additions for a column does not depend on CV: fixed
+// throughout, bit-reproducible. gridDim.y = dweight / dbias. Wide rows with few
+// partial rows take CV = 2 or 4: a quarter of the blocks, each load four times
+// as wide ([2048, 16384] LayerNorm: 1024 blocks of 4.6 rows per thread before).
+template <typename T, int CV>
 __global__ void __launch_bounds__(1024)
 colreduce_kernel(const float* __restrict__ partial, int blocks, int64_t cols, T* out_w, T* out_b,
                  float* out_f32) {
-  __shared__ float tile[32][33];
+  struct __align__(4 * CV) Cols {
+    float v[CV];
+  };
+  __shared__ float tile[32][32 * CV + 1];
   const int which = blockIdx.y;
   const float* src = partial + (size_t)which * blocks * cols;
-  const int64_t col = (int64_t)blockIdx.x * 32 + threadIdx.x;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  const int64_t col0 = ((int64_t)blockIdx.x * 32 + threadIdx.x) * CV;
+  float s0[CV], s1[CV], s2[CV], s3[CV];
+#pragma unroll
+  for (int j = 0; j < CV; ++j) s0[j] = s1[j] = s2[j] = s3[j] = 0.f;
   grid_dependency_wait();
-  if (col < cols) {
+  if (col0 < cols) {  // cols is a multiple of CV: the whole group is inside
+    auto row = [&](int p) { return *reinterpret_cast<const Cols*>(src + (size_t)p * cols + col0); };
     int p = threadIdx.y;
     for (; p + 96 < blocks; p += 128) {
-      s0 += src[(size_t)p * cols + col];
-      s1 += src[(size_t)(p + 32) * cols + col];
-      s2 += src[(size_t)(p + 64) * cols + col];
-      s3 += src[(size_t)(p + 96) * cols + col];
-    }
-    for (; p < blocks; p += 32) s0 += src[(size_t)p * cols + col];
-  }
-  tile[threadIdx.y][threadIdx.x] = (s0 + s1) + (s2 + s3);
-  __syncthreads();
-  if (threadIdx.y == 0 && col < cols) {
-    float t = tile[0][threadIdx.x];
+      const Cols a = row(p), b = row(p + 32), c = row(p + 64), d = row(p + 96);
 #pragma unroll
-    for (int i = 1; i < 32; ++i) t += tile[i][threadIdx.x];
+      for (int j = 0; j < CV; ++j) {
+        s0[j] += a.v[j];
+        s1[j] += b.v[j];
+        s2[j] += c.v[j];
+        s3[j] += d.v[j];
+      }
+    }
+    for (; p < blocks; p += 32) {
+      const Cols a = row(p);
+#pragma unroll
+      for (int j = 0; j < CV; ++j) s0[j] += a.v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < CV; ++j)
+    tile[threadIdx.y][threadIdx.x * CV + j] = (s0[j] + s1[j]) + (s2[j] + s3[j]);
+  __syncthreads();
+  const int t = threadIdx.y * 32 + threadIdx.x;  // one thread per column of the block
+  const int64_t col = (int64_t)blockIdx.x * 32 * CV + t;
+  if (t < 32 * CV && col < cols) {
+    float sum = tile[0][t];
+#pragma unroll
+    for (int i = 1; i < 32; ++i) sum += tile[i][t];
     T* out = which == 0 ? out_w : out_b;
-    if (out) out[col] = from_f32<T>(t);
-    if (out_f32) out_f32[(size_t)which * cols + col] = t;
+    if (out) out[col] = from_f32<T>(sum);
+    if (out_f32) out_f32[(size_t)which * cols + col] = sum;
   }
 }
 
@@ -148,8 +170,18 @@ inline int max_partial_blocks(int64_t hidden = (int64_t)1 << 40) {
 template <typename T>
 inline void launch_colreduce(const float* partial, int blocks, int64_t cols, T* out_w, T* out_b,
                              float* out_f32, int parts, cudaStream_t stream) {
+  // Columns per thread: four while that leaves a block per SM, two while it leaves
+  // one and a half (measured on bf16 LayerNorm backward, one column per thread ->
+  // this choice: [2048, 16384] 49.4 -> 45.9 us with four, [4096, 8192] 40.9 -> 40.3 us
+  // with two; [8192, 5120] with two, 160 blocks, was 0.8 us slower).
+  const int sms = device_info().sm_count;
+  int cv = 1;
+  if (!tune("norm_bwd.narrow_colreduce")) {
+    if (cols % 4 == 0 && (cols / 128) * parts >= sms) cv = 4;
+    else if (cols % 2 == 0 && 2 * (cols / 64) * parts >= 3 * sms) cv = 2;
+  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)((cols + 31) / 32), (unsigned)parts);
+  cfg.gridDim = dim3((unsigned)((cols + 32 * cv - 1) / (32 * cv)), (unsigned)parts);
   cfg.blockDim = dim3(32, 32);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
@@ -158,7 +190,9 @@ inline void launch_colreduce(const float* partial, int blocks, int64_t cols, T* 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = tune("norm_bwd.no_pdl") ? 0 : 1;
-  cudaLaunchKernelEx(&cfg, colreduce_kernel<T>, partial, blocks, cols, out_w, out_b, out_f32);
+  auto kern = cv == 4 ? colreduce_kernel<T, 4> : cv == 2 ? colreduce_kernel<T, 2>
+                                                         : colreduce_kernel<T, 1>;
+  cudaLaunchKernelEx(&cfg, kern, partial, blocks, cols, out_w, out_b, out_f32);
 }
 #endif
 

@@ -62,6 +62,8 @@ CASES = {
         ((2049, 64), ("bfloat16",)), ((1001, 768), ("bfloat16",)), ((4099, 1536), ("bfloat16", "float16")),
         ((777, 2040), ("bfloat16",)), ((1234, 1032), ("float16",)), ((515, 768), ("float32",)),
         ((515, 384), ("float32",)), ((3, 1024), ("bfloat16",)),
+        # eight vectors per thread: the backward reads the ring stage twice
+        ((97, 16384), ("bfloat16",)), ((33, 13000), ("float16",)), ((40, 8192), ("float32",)),
     ) for dt in dts],
     "rmsnorm": [(dict(rows=r, hidden=h), dt) for (r, h), dts in (
         ((8, 64), ("float32",)), ((17, 128), ("float32",)), ((32, 256), ("float16", "bfloat16")),
@@ -267,6 +269,26 @@ def test_float32_partials_for_sharded_parameter_gradients():
     assert torch.equal(dx, dx2)
     assert torch.equal(ops.cast_from_f32(dwdb[0], torch.bfloat16), dw)
     assert torch.equal(ops.cast_from_f32(dwdb[1], torch.bfloat16), db)
+
+
+@pytest.mark.parametrize("rows,hidden", [(300, 16384), (200, 8192), (64, 4096)])
+def test_column_reduce_width_does_not_change_a_bit(rows, hidden):
+    """Stage 2 of dweight/dbias takes 4, 2 or 1 columns per thread by shape; the order of the
+    additions for a column is the same in each, so the results are too."""
+    from evograd_b200 import _cabi, ops
+
+    inputs = to_device(ao.make_inputs("layernorm", dict(rows=rows, hidden=hidden), "bfloat16"))
+    y, mean, rstd = ops.layernorm_fwd(inputs["x"], inputs["weight"], inputs["bias"], 1e-5)
+    got = {}
+    try:
+        for knob in (1, 0):
+            _cabi.tune_set("norm_bwd.narrow_colreduce", knob)
+            got[knob] = ops.layernorm_bwd(inputs["dy"], inputs["x"], inputs["weight"], mean, rstd,
+                                          partials_f32=True)[:2]
+    finally:
+        _cabi.tune_set("norm_bwd.narrow_colreduce", 0)
+    for a, b in zip(got[0], got[1]):
+        assert torch.equal(a, b)
 
 
 def test_bad_arguments_raise():
