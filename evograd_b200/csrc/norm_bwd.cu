@@ -860,9 +860,19 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
     dim3 grid((unsigned)((hidden + 31) / 32), NV);
     int* status = nullptr;
     cudaGetSymbolAddress((void**)&status, g_norm_device_status);
-    colreduce_exchange_kernel<T><<<grid, dim3(32, 32), 0, stream>>>(
-        partial, blocks, hidden, (T*)dweight, (T*)dbias, xchg->peers, xchg->lay, xchg->n_ranks,
-        xchg->rank, xchg->wait_limit, status);
+    // a programmatic dependent of the row kernel, like the single-GPU stage 2
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(32, 32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tune("norm_bwd.no_pdl") ? 0 : 1;
+    cudaLaunchKernelEx(&cfg, colreduce_exchange_kernel<T>, (const float*)partial, blocks,
+                       (int64_t)hidden, (T*)dweight, (T*)dbias, xchg->peers, xchg->lay,
+                       xchg->n_ranks, xchg->rank, xchg->wait_limit, status);
     return check_launch("norm_bwd colreduce + exchange");
   }
   if (dweight || dbias || out_f32) {

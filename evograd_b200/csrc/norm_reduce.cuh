@@ -104,6 +104,7 @@ colreduce_exchange_kernel(const float* __restrict__ partial, int blocks, int64_t
   const float* src = partial + (size_t)which * blocks * cols;
   const int64_t col = (int64_t)blockIdx.x * 32 + threadIdx.x;
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  grid_dependency_wait();  // the row kernel's partial rows are complete and visible
   if (col < cols) {
     int p = threadIdx.y;
     for (; p + 96 < blocks; p += 128) {
