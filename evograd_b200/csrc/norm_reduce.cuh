@@ -155,12 +155,12 @@ colreduce_exchange_kernel(const float* __restrict__ partial, int blocks, int64_t
 
 // Persistent blocks (= partial rows of the column reduction) the backward
 // kernels may launch: SMs x `norm_bwd.blocks_per_sm`; by default 2, and 4 for
-// rows of at most 2048 elements, whose kernels keep few values per thread, fit
+// rows of at most 3072 elements, whose kernels keep few values per thread, fit
 // four blocks on an SM and need them to hide their load latency (a partial row
-// is then at most 8 KB).
+// is then at most 12 KB). A bound: kernels that fit fewer blocks launch fewer.
 inline int max_partial_blocks(int64_t hidden = (int64_t)1 << 40) {
   int per_sm = tune("norm_bwd.blocks_per_sm");
-  if (per_sm <= 0) per_sm = hidden <= 2048 ? 4 : 2;
+  if (per_sm <= 0) per_sm = hidden <= 3072 ? 4 : 2;
   return device_info().sm_count * per_sm;
 }
 

@@ -64,6 +64,8 @@ CASES = {
         ((515, 384), ("float32",)), ((3, 1024), ("bfloat16",)),
         # eight vectors per thread: the backward reads the ring stage twice
         ((97, 16384), ("bfloat16",)), ((33, 13000), ("float16",)), ((40, 8192), ("float32",)),
+        # 257 ... 384 vectors: 128-thread ring blocks, three vectors per thread
+        ((1000, 3072), ("bfloat16",)), ((333, 2560), ("float16",)), ((257, 1536), ("float32",)),
     ) for dt in dts],
     "rmsnorm": [(dict(rows=r, hidden=h), dt) for (r, h), dts in (
         ((8, 64), ("float32",)), ((17, 128), ("float32",)), ((32, 256), ("float16", "bfloat16")),
@@ -73,7 +75,7 @@ CASES = {
         ((333, 5120), ("bfloat16",)), ((97, 12288), ("bfloat16",)),
         ((2049, 64), ("bfloat16",)), ((1001, 768), ("float16",)), ((4099, 1536), ("bfloat16",)),
         ((777, 2040), ("bfloat16",)), ((515, 768), ("float32",)), ((515, 384), ("float32",)),
-        ((3, 1024), ("bfloat16",)),
+        ((3, 1024), ("bfloat16",)), ((1000, 3072), ("bfloat16",)), ((257, 1536), ("float32",)),
     ) for dt in dts],
     "swiglu": [(dict(rows=r, cols=c), dt) for (r, c), dts in (
         ((8, 64), ("float32",)), ((17, 128), ("float32",)), ((32, 256), ("float16", "bfloat16")),
