@@ -1211,10 +1211,10 @@ TRAFFIC_SOURCES = {
 TRAFFIC_NCU = {
     # python bench.py --source-digest NAME prints the digest of a workload's kernel sources as
     # they are now; an entry whose digest no longer matches is reported as stale, not used
-    "layernorm": {"bytes": 382100000, "profile": "profiles/layernorm_bf16_16384x4096.md",
-                 "sources": TRAFFIC_SOURCES["layernorm"], "digest": "92abd331920e"},
-    "rmsnorm": {"bytes": 676100000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
-               "sources": TRAFFIC_SOURCES["rmsnorm"], "digest": "92abd331920e"},
+    "layernorm": {"bytes": 382200000, "profile": "profiles/layernorm_bf16_16384x4096.md",
+                 "sources": TRAFFIC_SOURCES["layernorm"], "digest": "eeb8977e8240"},
+    "rmsnorm": {"bytes": 674900000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
+               "sources": TRAFFIC_SOURCES["rmsnorm"], "digest": "eeb8977e8240"},
     "fused_add_rms_norm": {"bytes": 971700000, "profile": "profiles/rmsnorm_and_fused_add_bf16_8192x4096.md (8192 rows, scaled x 4)",
                           "sources": TRAFFIC_SOURCES["fused_add_rms_norm"], "digest": "dd18f66879bf"},
     "geglu": {"bytes": 4306000000, "profile": "profiles/geglu_bf16_4096x14336.md (4096 rows, scaled x 8)",

@@ -693,6 +693,17 @@ int read_norm_status(int reset) {
 }
 const bool g_norm_status_registered = (register_device_status(read_norm_status), true);
 
+// The fewest blocks that walk `rows` (in tiles of `per_tile`) in the same number of rounds as
+// `blocks` would: every round is then full. Measured on the tile ring ([65536, 1024] bf16:
+// RMSNorm backward 65.3 -> 63.1 us, LayerNorm 71.8 -> 71.0 us); on the one-row ring and the
+// forward kernels the same choice was neutral or slower, so they keep the full count.
+inline int even_rounds(int blocks, int64_t rows, int per_tile) {
+  const int64_t tiles = (rows + per_tile - 1) / per_tile;
+  if (blocks < 1 || tiles <= blocks) return blocks;
+  const int64_t rounds = (tiles + blocks - 1) / blocks;
+  return (int)((tiles + rounds - 1) / rounds);
+}
+
 struct BwdPlan {
   bool generic = false;
   RowCfg cfg;
@@ -820,7 +831,7 @@ int launch_norm_bwd(const void* dy, const void* x, const void* w, const float* m
   if (!launched && G == g && V == v && threads == t) {                                         \
     auto kern = norm_bwd_tile_ring_kernel<T, g, v, LN, t>;                                     \
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-    blocks = persistent_grid(kern, t, smem, rows, t / g, cap);                                 \
+    blocks = even_rounds(persistent_grid(kern, t, smem, rows, t / g, cap), rows, t / g);       \
     kern<<<blocks, t, smem, stream>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd,      \
                                       (T*)dx, partial, rows, (int)hidden, stages, wait_limit); \
     launched = true;                                                                           \
